@@ -1,0 +1,1177 @@
+// engine.cu -- host side of libcheckers_b200.so: context, registry, the batched
+// compress / restore pipelines, analysis, file images, and the C ABI declared
+// in include/checkers_b200.h.  Device code is in kernels.cuh.
+//
+// How the reference's per-tensor, mutex-serialised loop
+// (ANSCompressor::compress_and_save_all, src/ANSCompressor.cpp:1014-1401 in the
+// Checkers tree: >= 8 stream syncs and 3 device-to-host copies per tensor) is
+// re-shaped here: all tensors of a rank go through each stage in ONE launch --
+//   split_hist_kernel   (low bytes -> final .mant data layout, histograms)
+//   one D2H of all histograms, table normalisation on host threads, one H2D
+//   rans_encode_kernel  (one CTA per tensor, 256 lanes)
+//   lane_scan_kernel / tensor_scan_kernel / compact_kernel
+//                       (payload laid out exactly as the .ansc data section)
+// so the host synchronises twice per checkpoint instead of per tensor, and the
+// file images are filled by three large copies.
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <chrono>
+#include <cstdio>
+#include <cstring>
+#include <filesystem>
+#include <fstream>
+#include <map>
+#include <string>
+#include <thread>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/checkers_b200.h"
+#include "clusters.hpp"
+#include "kernels.cuh"
+#include "tables.hpp"
+
+namespace chk {
+
+// ------------------------------------------------------------------ errors
+struct Error {
+    int code;
+    std::string msg;
+};
+static thread_local std::string g_last_error;
+
+#define CHK_CUDA(call)                                                                              \
+    do {                                                                                            \
+        cudaError_t e_ = (call);                                                                    \
+        if (e_ != cudaSuccess)                                                                      \
+            throw Error{CHK_ERR_CUDA, std::string(#call) + ": " + cudaGetErrorString(e_)};          \
+    } while (0)
+
+static inline uint32_t elem_size(uint8_t dt) {
+    switch (dt) {
+        case CHK_F32: return 4;
+        case CHK_BF16: return 2;
+        case CHK_F16: return 2;
+        case CHK_I8: return 1;
+        case CHK_I32: return 4;
+        default: return 0;
+    }
+}
+static inline uint32_t sidecar_per_elem(uint8_t dt) {
+    switch (dt) {
+        case CHK_BF16:
+        case CHK_F16: return 1;
+        case CHK_F32: return 2;
+        default: return 0;
+    }
+}
+
+// ------------------------------------------------------------------ file layout constants
+constexpr uint32_t kStatesMagic = 0x414E5343u, kStatesVersion = 2;
+constexpr uint32_t kMantMagic = 0x4D414E54u, kMantVersion = 2;
+constexpr uint32_t kDictMagic = 0x44494354u, kDictVersion = 1;
+constexpr size_t kStatesEntry = 4648, kMantEntry = 288, kDictEntry = 2308, kFileHeader = 16;
+
+// ------------------------------------------------------------------ buffers
+struct DevBuf {
+    void* p = nullptr;
+    size_t cap = 0;
+};
+struct PinBuf {
+    void* p = nullptr;
+    size_t cap = 0;
+    size_t size = 0;
+};
+
+struct Tensor {
+    std::string name;
+    void* ptr;
+    uint64_t n_elem;
+    uint8_t dtype, category;
+};
+
+struct WorkItem {
+    size_t idx;  // registry index
+    uint64_t bytes;
+    uint32_t es, spe;
+    bool owns;
+    int table;  // table index in .dict order
+    std::string anchor_name;
+};
+
+struct Context {
+    int device = 0, rank = 0, local_rank = 0;
+    cudaStream_t stream = nullptr;
+    cudaMemPool_t pool = nullptr;
+    cudaEvent_t ev[8] = {};
+    std::vector<Tensor> tensors;
+    uint32_t histogram_bins = 256;
+
+    bool have_clusters = false;
+    ClusterMap clusters;
+    std::vector<StatsOut> stats;
+
+    bool repair_tables = false, verify_zero_lanes = false;
+    bool enc_attr_set = false, dec_attr_set = false;
+    int host_threads = 0;
+
+    // device buffers (grow-only, from the context's pool)
+    DevBuf d_descs, d_tiles, d_hist, d_sidecar, d_scratch, d_hdrs, d_wpos, d_loff, d_psize, d_poff, d_payload, d_enc,
+        d_freq, d_cum, d_status, d_stats_desc, d_stats_out;
+    // pinned host staging
+    PinBuf h_hist, h_hdrs, h_poff, h_descs, h_status, h_enc, h_stats;
+    PinBuf img[3];  // states, mantissa, tables
+
+    // result of the last compression
+    std::vector<WorkItem> work;
+    std::vector<FreqTable> tables;
+    std::vector<TensorDesc> descs;  // host copy, payload_off / flags filled in
+    bool have_resident = false, have_images = false;
+    chk_summary summary{};
+    uint64_t restored = 0;
+
+    std::map<std::string, double> timing;
+    uint64_t launches = 0;
+};
+
+static void dev_ensure(Context* c, DevBuf& b, size_t bytes) {
+    bytes = (bytes + 255) & ~(size_t)255;
+    if (bytes == 0) bytes = 256;
+    if (b.cap >= bytes) return;
+    if (b.p) CHK_CUDA(cudaFreeAsync(b.p, c->stream));
+    b.p = nullptr;
+    b.cap = 0;
+    // grow with some slack so near-equal batches reuse the allocation
+    const size_t want = bytes + bytes / 16;
+    CHK_CUDA(cudaMallocFromPoolAsync(&b.p, want, c->pool, c->stream));
+    b.cap = want;
+}
+static void pin_ensure(PinBuf& b, size_t bytes) {
+    b.size = bytes;
+    if (bytes == 0) bytes = 16;
+    if (b.cap >= bytes) return;
+    if (b.p) cudaFreeHost(b.p);
+    b.p = nullptr;
+    b.cap = 0;
+    const size_t want = bytes + bytes / 16;
+    CHK_CUDA(cudaHostAlloc(&b.p, want, cudaHostAllocDefault));
+    b.cap = want;
+}
+
+static double ms_between(cudaEvent_t a, cudaEvent_t b) {
+    float ms = 0;
+    cudaEventElapsedTime(&ms, a, b);
+    return ms;
+}
+static double wall_ms(std::chrono::steady_clock::time_point t0) {
+    return std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+}
+
+template <typename F>
+static void parallel_for(size_t n, int threads, F&& fn) {
+    if (threads <= 0) threads = (int)std::thread::hardware_concurrency();
+    if (threads < 1) threads = 1;
+    if ((size_t)threads > n) threads = (int)n;
+    if (threads <= 1) {
+        for (size_t i = 0; i < n; ++i) fn(i);
+        return;
+    }
+    std::atomic<size_t> next{0};
+    std::vector<std::thread> pool;
+    for (int t = 0; t < threads; ++t)
+        pool.emplace_back([&] {
+            for (;;) {
+                const size_t i0 = next.fetch_add(16);
+                if (i0 >= n) break;
+                const size_t i1 = i0 + 16 < n ? i0 + 16 : n;
+                for (size_t i = i0; i < i1; ++i) fn(i);
+            }
+        });
+    for (auto& th : pool) th.join();
+}
+
+// ------------------------------------------------------------------ work list
+// Order, ownership and sharing rules of compress_and_save_all
+// (src/ANSCompressor.cpp:1056-1078, :1210, :1239-1261, :1352-1371).
+static void build_work(Context* c) {
+    c->work.clear();
+    std::unordered_map<int, bool> seen;
+    std::unordered_map<int, int> cluster_table;
+    int n_tables = 0;
+    for (size_t i = 0; i < c->tensors.size(); ++i) {
+        const Tensor& t = c->tensors[i];
+        if (!t.ptr || t.n_elem == 0) continue;
+        int cid = -1;
+        if (c->have_clusters) {
+            auto it = c->clusters.tensor_to_cluster.find(t.name);
+            if (it != c->clusters.tensor_to_cluster.end()) cid = it->second;
+        }
+        const bool single = cid == -1;
+        bool anchor = false;
+        if (!single && !seen[cid]) {
+            seen[cid] = true;
+            anchor = true;
+        }
+        const uint32_t es = elem_size(t.dtype);
+        const uint64_t bytes = t.n_elem * es;
+        if (bytes == 0) continue;  // unknown dtype: never produces a result (:1133)
+        WorkItem w;
+        w.idx = i;
+        w.bytes = bytes;
+        w.es = es;
+        w.spe = sidecar_per_elem(t.dtype);
+        w.owns = anchor || single;
+        if (w.owns) {
+            w.table = n_tables++;
+            if (!single) cluster_table[cid] = w.table;
+        } else {
+            auto it = cluster_table.find(cid);
+            if (it == cluster_table.end()) continue;  // its anchor produced no table (the reference waits forever)
+            w.table = it->second;
+            auto an = c->clusters.cluster_anchor.find(cid);
+            if (an != c->clusters.cluster_anchor.end()) w.anchor_name = an->second;
+        }
+        if (bytes >= (1ull << 32))
+            throw Error{CHK_ERR_CAPACITY, "tensor '" + t.name + "' is 4 GiB or larger; lane offsets are 32-bit"};
+        c->work.push_back(std::move(w));
+    }
+    // whether a table is built with the full alphabet: owner that is a cluster anchor
+    c->tables.assign(n_tables, FreqTable{});
+}
+
+static bool is_cluster_anchor(const Context* c, const WorkItem& w) {
+    if (!w.owns || !c->have_clusters) return false;
+    auto it = c->clusters.tensor_to_cluster.find(c->tensors[w.idx].name);
+    return it != c->clusters.tensor_to_cluster.end() && it->second != -1;
+}
+
+static void put_name(uint8_t* dst, const std::string& s) {
+    std::memset(dst, 0, 256);
+    std::memcpy(dst, s.data(), s.size() < 255 ? s.size() : 255);
+}
+template <typename T>
+static void put(uint8_t* dst, T v) {
+    std::memcpy(dst, &v, sizeof(T));
+}
+template <typename T>
+static T get(const uint8_t* src) {
+    T v;
+    std::memcpy(&v, src, sizeof(T));
+    return v;
+}
+static std::string get_name(const uint8_t* p) {
+    size_t n = 0;
+    while (n < 256 && p[n]) ++n;
+    return std::string(reinterpret_cast<const char*>(p), n);
+}
+
+// ------------------------------------------------------------------ compress
+static void compress(Context* c, bool host_images) {
+    const auto t_total = std::chrono::steady_clock::now();
+    CHK_CUDA(cudaSetDevice(c->device));
+    c->have_resident = c->have_images = false;
+    c->summary = chk_summary{};
+    build_work(c);
+    const size_t W = c->work.size();
+    const size_t T = c->tables.size();
+    cudaStream_t s = c->stream;
+
+    c->descs.assign(W, TensorDesc{});
+    std::vector<uint32_t> tile_start(W + 1, 0);
+    unsigned long long sidecar_total = 0, scratch_total = 0, bytes_total = 0;
+    size_t n_sidecars = 0;
+    for (size_t i = 0; i < W; ++i) {
+        const WorkItem& w = c->work[i];
+        TensorDesc& d = c->descs[i];
+        d.src = static_cast<const uint8_t*>(c->tensors[w.idx].ptr);
+        d.dst = nullptr;
+        d.n_bytes = w.bytes;
+        d.es = w.es;
+        d.spe = w.spe;
+        d.table_idx = (uint32_t)w.table;
+        d.sidecar_off = sidecar_total;
+        d.scratch_off = scratch_total;
+        const unsigned long long c_max = (w.bytes + 255) / 256;
+        d.chunk_stride = (uint32_t)((2 * c_max + 15) & ~15ull);
+        d.flags = w.owns ? kFlagNeedHist : 0u;
+        if ((reinterpret_cast<uintptr_t>(d.src) & 15) == 0 && (sidecar_total & 15) == 0) d.flags |= kFlagAligned;
+        sidecar_total += (unsigned long long)c->tensors[w.idx].n_elem * w.spe;
+        scratch_total += 256ull * d.chunk_stride;
+        bytes_total += w.bytes;
+        n_sidecars += w.spe > 0;
+        tile_start[i + 1] = tile_start[i] + (uint32_t)((w.bytes + kSplitTileBytes - 1) / kSplitTileBytes);
+    }
+
+    if (W == 0) {
+        c->have_resident = true;
+        if (host_images) {
+            const size_t sizes[3] = {kFileHeader, kFileHeader, kFileHeader};
+            const uint32_t magic[3] = {kStatesMagic, kMantMagic, kDictMagic};
+            const uint32_t ver[3] = {kStatesVersion, kMantVersion, kDictVersion};
+            for (int k = 0; k < 3; ++k) {
+                pin_ensure(c->img[k], sizes[k]);
+                uint8_t* p = static_cast<uint8_t*>(c->img[k].p);
+                put<uint32_t>(p, magic[k]);
+                put<uint32_t>(p + 4, ver[k]);
+                put<uint32_t>(p + 8, (uint32_t)(c->rank < 0 ? 0 : c->rank));
+                put<uint32_t>(p + 12, 0);
+            }
+            c->have_images = true;
+            c->summary.states_bytes = c->summary.mantissa_bytes = c->summary.dict_bytes = kFileHeader;
+        }
+        return;
+    }
+
+    dev_ensure(c, c->d_descs, W * sizeof(TensorDesc));
+    dev_ensure(c, c->d_tiles, (W + 1) * 4);
+    dev_ensure(c, c->d_hist, W * 1024);
+    dev_ensure(c, c->d_sidecar, sidecar_total + 64);
+    dev_ensure(c, c->d_scratch, scratch_total + 64);
+    dev_ensure(c, c->d_hdrs, W * 4096);
+    dev_ensure(c, c->d_wpos, W * 1024);
+    dev_ensure(c, c->d_loff, W * 1024);
+    dev_ensure(c, c->d_psize, W * 8);
+    dev_ensure(c, c->d_poff, (W + 1) * 8);
+    dev_ensure(c, c->d_payload, bytes_total + 64);
+    dev_ensure(c, c->d_enc, T * 256 * sizeof(EncEntry));
+    dev_ensure(c, c->d_freq, T * 256 * 4);
+    dev_ensure(c, c->d_cum, T * 257 * 4);
+    dev_ensure(c, c->d_status, 256);
+    pin_ensure(c->h_hist, W * 1024);
+    pin_ensure(c->h_hdrs, W * 4096);
+    pin_ensure(c->h_poff, (W + 1) * 8);
+    pin_ensure(c->h_descs, W * sizeof(TensorDesc));
+    pin_ensure(c->h_status, 256);
+    pin_ensure(c->h_enc, T * (256 * sizeof(EncEntry) + 256 * 4 + 257 * 4));
+
+    std::memcpy(c->h_descs.p, c->descs.data(), W * sizeof(TensorDesc));
+    CHK_CUDA(cudaEventRecord(c->ev[0], s));
+    CHK_CUDA(cudaMemcpyAsync(c->d_descs.p, c->h_descs.p, W * sizeof(TensorDesc), cudaMemcpyHostToDevice, s));
+    CHK_CUDA(cudaMemcpyAsync(c->d_tiles.p, tile_start.data(), (W + 1) * 4, cudaMemcpyHostToDevice, s));
+    CHK_CUDA(cudaMemsetAsync(c->d_hist.p, 0, W * 1024, s));
+    CHK_CUDA(cudaMemsetAsync(c->d_status.p, 0, 256, s));
+
+    // ---- stage 1: low bytes out, histograms
+    {
+        const uint32_t total_tiles = tile_start[W];
+        const uint32_t grid = total_tiles < 148u * 8u ? total_tiles : 148u * 8u;
+        split_hist_kernel<<<grid, 256, 0, s>>>(static_cast<const TensorDesc*>(c->d_descs.p),
+                                               static_cast<const uint32_t*>(c->d_tiles.p), (uint32_t)W, total_tiles,
+                                               static_cast<uint8_t*>(c->d_sidecar.p),
+                                               static_cast<uint32_t*>(c->d_hist.p));
+        CHK_CUDA(cudaGetLastError());
+        c->launches++;
+    }
+    CHK_CUDA(cudaEventRecord(c->ev[1], s));
+    CHK_CUDA(cudaMemcpyAsync(c->h_hist.p, c->d_hist.p, W * 1024, cudaMemcpyDeviceToHost, s));
+    CHK_CUDA(cudaStreamSynchronize(s));
+
+    // ---- tables on the host
+    const auto t_tab = std::chrono::steady_clock::now();
+    EncEntry* h_enc = static_cast<EncEntry*>(c->h_enc.p);
+    uint32_t* h_freq = reinterpret_cast<uint32_t*>(h_enc + T * 256);
+    uint32_t* h_cum = h_freq + T * 256;
+    {
+        std::vector<size_t> owners;
+        for (size_t i = 0; i < W; ++i)
+            if (c->work[i].owns) owners.push_back(i);
+        const uint32_t* hist_all = static_cast<const uint32_t*>(c->h_hist.p);
+        parallel_for(owners.size(), c->host_threads, [&](size_t k) {
+            const size_t i = owners[k];
+            const WorkItem& w = c->work[i];
+            uint32_t h[256];
+            std::memcpy(h, hist_all + i * 256, 1024);
+            // the zeroed low bytes of every element are part of the codec input
+            h[0] += (uint32_t)((uint64_t)c->tensors[w.idx].n_elem * w.spe);
+            const bool full = is_cluster_anchor(c, w);
+            FreqTable& ft = c->tables[w.table];
+            normalize_histogram(h, full, full && c->repair_tables, ft);
+            build_enc_entries(ft, h_enc + (size_t)w.table * 256);
+            std::memcpy(h_freq + (size_t)w.table * 256, ft.norm_freq, 1024);
+            std::memcpy(h_cum + (size_t)w.table * 257, ft.cum_freq, 1028);
+        });
+    }
+    c->timing["table_ms"] = wall_ms(t_tab);
+
+    CHK_CUDA(cudaMemcpyAsync(c->d_enc.p, h_enc, T * 256 * sizeof(EncEntry), cudaMemcpyHostToDevice, s));
+    CHK_CUDA(cudaMemcpyAsync(c->d_freq.p, h_freq, T * 256 * 4, cudaMemcpyHostToDevice, s));
+    CHK_CUDA(cudaMemcpyAsync(c->d_cum.p, h_cum, T * 257 * 4, cudaMemcpyHostToDevice, s));
+    CHK_CUDA(cudaEventRecord(c->ev[2], s));
+
+    // ---- stage 2: encode
+    {
+        if (!c->enc_attr_set) {
+            CHK_CUDA(cudaFuncSetAttribute(rans_encode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          (int)kEncSmemBytes));
+            c->enc_attr_set = true;
+        }
+        const uint32_t grid = (uint32_t)(W < 148u * 64u ? W : 148u * 64u);
+        rans_encode_kernel<<<grid, 256, kEncSmemBytes, s>>>(
+            static_cast<const TensorDesc*>(c->d_descs.p), static_cast<const EncEntry*>(c->d_enc.p),
+            static_cast<uint8_t*>(c->d_scratch.p), static_cast<LaneHeader*>(c->d_hdrs.p),
+            static_cast<uint32_t*>(c->d_wpos.p), (uint32_t)W, static_cast<uint32_t*>(c->d_status.p));
+        CHK_CUDA(cudaGetLastError());
+        c->launches++;
+    }
+    CHK_CUDA(cudaEventRecord(c->ev[3], s));
+
+    // ---- stage 3: offsets + compaction into the data-section layout
+    {
+        const uint32_t g1 = (uint32_t)(W < 4096 ? W : 4096);
+        lane_scan_kernel<<<g1, 256, 0, s>>>(static_cast<TensorDesc*>(c->d_descs.p),
+                                            static_cast<LaneHeader*>(c->d_hdrs.p),
+                                            static_cast<unsigned long long*>(c->d_psize.p),
+                                            static_cast<uint32_t*>(c->d_loff.p), (uint32_t)W);
+        CHK_CUDA(cudaGetLastError());
+        tensor_scan_kernel<<<1, 1024, 0, s>>>(static_cast<TensorDesc*>(c->d_descs.p),
+                                              static_cast<const unsigned long long*>(c->d_psize.p),
+                                              static_cast<unsigned long long*>(c->d_poff.p), (uint32_t)W);
+        CHK_CUDA(cudaGetLastError());
+        const unsigned long long warps = (unsigned long long)W * 256;
+        const unsigned long long blocks = (warps + 7) / 8;
+        const uint32_t g3 = (uint32_t)(blocks < 148ull * 16 ? blocks : 148ull * 16);
+        compact_kernel<<<g3, 256, 0, s>>>(static_cast<const TensorDesc*>(c->d_descs.p),
+                                          static_cast<const LaneHeader*>(c->d_hdrs.p),
+                                          static_cast<const uint32_t*>(c->d_wpos.p),
+                                          static_cast<const uint32_t*>(c->d_loff.p),
+                                          static_cast<const uint8_t*>(c->d_scratch.p),
+                                          static_cast<uint8_t*>(c->d_payload.p), (uint32_t)W);
+        CHK_CUDA(cudaGetLastError());
+        c->launches += 3;
+    }
+    CHK_CUDA(cudaEventRecord(c->ev[4], s));
+    CHK_CUDA(cudaMemcpyAsync(c->h_poff.p, c->d_poff.p, (W + 1) * 8, cudaMemcpyDeviceToHost, s));
+    CHK_CUDA(cudaMemcpyAsync(c->h_descs.p, c->d_descs.p, W * sizeof(TensorDesc), cudaMemcpyDeviceToHost, s));
+    CHK_CUDA(cudaMemcpyAsync(c->h_status.p, c->d_status.p, 4, cudaMemcpyDeviceToHost, s));
+    if (host_images)
+        CHK_CUDA(cudaMemcpyAsync(c->h_hdrs.p, c->d_hdrs.p, W * 4096, cudaMemcpyDeviceToHost, s));
+    CHK_CUDA(cudaStreamSynchronize(s));
+
+    c->timing["split_hist_ms"] = ms_between(c->ev[0], c->ev[1]);
+    c->timing["encode_ms"] = ms_between(c->ev[2], c->ev[3]);
+    c->timing["compact_ms"] = ms_between(c->ev[3], c->ev[4]);
+    c->timing["compress_device_ms"] =
+        c->timing["split_hist_ms"] + c->timing["encode_ms"] + c->timing["compact_ms"];
+
+    if (*static_cast<const uint32_t*>(c->h_status.p) & kErrBarrierTimeout)
+        throw Error{CHK_ERR_TIMEOUT, "encode: an asynchronous tile copy did not complete"};
+
+    std::memcpy(c->descs.data(), c->h_descs.p, W * sizeof(TensorDesc));
+    const unsigned long long* poff = static_cast<const unsigned long long*>(c->h_poff.p);
+    const unsigned long long payload_total = poff[W];
+    c->have_resident = true;
+
+    c->summary.n_tensors = W;
+    c->summary.n_tables = T;
+    c->summary.original_bytes = bytes_total;
+    c->summary.states_bytes = kFileHeader + W * kStatesEntry + payload_total;
+    c->summary.mantissa_bytes = kFileHeader + n_sidecars * kMantEntry + sidecar_total;
+    c->summary.dict_bytes = kFileHeader + T * kDictEntry;
+
+    if (host_images) {
+        const uint32_t rank_u = (uint32_t)(c->rank < 0 ? 0 : c->rank);
+        CHK_CUDA(cudaEventRecord(c->ev[5], s));
+        // states image (write_rank_states_file, src/ANSCompressor.cpp:751-816)
+        pin_ensure(c->img[0], c->summary.states_bytes);
+        uint8_t* st = static_cast<uint8_t*>(c->img[0].p);
+        const size_t st_data = kFileHeader + W * kStatesEntry;
+        if (payload_total)
+            CHK_CUDA(cudaMemcpyAsync(st + st_data, c->d_payload.p, payload_total, cudaMemcpyDeviceToHost, s));
+        // mantissa image (write_rank_mantissa_file, :839-887)
+        pin_ensure(c->img[1], c->summary.mantissa_bytes);
+        uint8_t* mt = static_cast<uint8_t*>(c->img[1].p);
+        const size_t mt_data = kFileHeader + n_sidecars * kMantEntry;
+        if (sidecar_total)
+            CHK_CUDA(cudaMemcpyAsync(mt + mt_data, c->d_sidecar.p, sidecar_total, cudaMemcpyDeviceToHost, s));
+        // tables image (write_rank_tables_file, :903-931)
+        pin_ensure(c->img[2], c->summary.dict_bytes);
+        uint8_t* dc = static_cast<uint8_t*>(c->img[2].p);
+
+        put<uint32_t>(st, kStatesMagic);
+        put<uint32_t>(st + 4, kStatesVersion);
+        put<uint32_t>(st + 8, rank_u);
+        put<uint32_t>(st + 12, (uint32_t)W);
+        put<uint32_t>(mt, kMantMagic);
+        put<uint32_t>(mt + 4, kMantVersion);
+        put<uint32_t>(mt + 8, rank_u);
+        put<uint32_t>(mt + 12, (uint32_t)n_sidecars);
+        put<uint32_t>(dc, kDictMagic);
+        put<uint32_t>(dc + 4, kDictVersion);
+        put<uint32_t>(dc + 8, rank_u);
+        put<uint32_t>(dc + 12, (uint32_t)T);
+
+        const LaneHeader* hdrs = static_cast<const LaneHeader*>(c->h_hdrs.p);
+        size_t m_i = 0;
+        for (size_t i = 0; i < W; ++i) {
+            const WorkItem& w = c->work[i];
+            const Tensor& t = c->tensors[w.idx];
+            uint8_t* e = st + kFileHeader + i * kStatesEntry;
+            put_name(e, t.name);
+            const LaneHeader* lh = hdrs + i * 256;
+            bool is_raw = lh[0].byte_count == (uint32_t)w.bytes;  // derived from the lane pattern (:787-789)
+            for (int l = 1; l < 256 && is_raw; ++l) is_raw = lh[l].byte_count == 0;
+            e[256] = t.dtype;
+            e[257] = is_raw ? 1 : 0;
+            e[258] = w.owns ? 1 : 0;
+            std::memset(e + 259, 0, 5);
+            put<uint64_t>(e + 264, w.bytes);
+            put<uint64_t>(e + 272, t.n_elem);
+            put<uint64_t>(e + 280, poff[i]);
+            put<uint64_t>(e + 288, poff[i + 1] - poff[i]);
+            put_name(e + 296, w.anchor_name);
+            std::memcpy(e + 552, lh, 4096);
+            if (w.spe) {
+                uint8_t* m = mt + kFileHeader + m_i * kMantEntry;
+                put_name(m, t.name);
+                m[256] = t.dtype;
+                m[257] = (uint8_t)w.spe;
+                std::memset(m + 258, 0, 6);
+                put<uint64_t>(m + 264, t.n_elem);
+                put<uint64_t>(m + 272, c->descs[i].sidecar_off);
+                put<uint64_t>(m + 280, t.n_elem * w.spe);
+                ++m_i;
+            }
+            if (w.owns) {
+                uint8_t* d = dc + kFileHeader + (size_t)w.table * kDictEntry;
+                put_name(d, t.name);
+                std::memcpy(d + 256, c->tables[w.table].norm_freq, 1024);
+                std::memcpy(d + 1280, c->tables[w.table].cum_freq, 1028);
+            }
+        }
+        CHK_CUDA(cudaEventRecord(c->ev[6], s));
+        CHK_CUDA(cudaStreamSynchronize(s));
+        c->timing["d2h_ms"] = ms_between(c->ev[5], c->ev[6]);
+        c->have_images = true;
+    }
+    c->timing["compress_total_ms"] = wall_ms(t_total);
+}
+
+static void write_file(const std::string& path, const void* p, size_t n) {
+    std::FILE* f = std::fopen(path.c_str(), "wb");
+    if (!f) throw Error{CHK_ERR_IO, "cannot open for write: " + path};
+    const size_t w = n ? std::fwrite(p, 1, n, f) : 0;
+    const int rc = std::fclose(f);
+    if (w != n || rc != 0) throw Error{CHK_ERR_IO, "short write: " + path};
+}
+
+static void rank_paths(const Context* c, const std::string& dir, std::string out[3]) {
+    const std::string tag = "rank_" + std::to_string(c->rank < 0 ? 0 : c->rank);
+    out[0] = dir + "/" + tag + "_states.ansc";
+    out[1] = dir + "/mantissa/" + tag + "_mantissa.mant";
+    out[2] = dir + "/tables/" + tag + "_tables.dict";
+}
+
+static void compress_and_save(Context* c, const std::string& dir) {
+    namespace fs = std::filesystem;
+    std::error_code ec;
+    fs::create_directories(dir, ec);
+    fs::create_directories(dir + "/mantissa", ec);
+    fs::create_directories(dir + "/tables", ec);
+    if (ec) throw Error{CHK_ERR_IO, "cannot create output directories under " + dir};
+    if (c->tensors.empty()) return;  // nothing registered: directories only (src/ANSCompressor.cpp:1026-1029)
+    compress(c, true);
+    const auto t0 = std::chrono::steady_clock::now();
+    std::string paths[3];
+    rank_paths(c, dir, paths);
+    for (int k = 0; k < 3; ++k) write_file(paths[k], c->img[k].p, c->img[k].size);
+    c->timing["io_ms"] = wall_ms(t0);
+}
+
+// ------------------------------------------------------------------ restore
+static void run_decode(Context* c, size_t W, const uint8_t* d_payload, const uint8_t* d_sidecar,
+                       const uint32_t* d_freq, const uint32_t* d_cum, const LaneHeader* d_hdrs,
+                       const std::vector<std::string>& names) {
+    cudaStream_t s = c->stream;
+    dev_ensure(c, c->d_status, W * 4 + 256);
+    pin_ensure(c->h_status, W * 4 + 256);
+    CHK_CUDA(cudaMemsetAsync(c->d_status.p, 0, W * 4, s));
+    if (!c->dec_attr_set) {
+        CHK_CUDA(cudaFuncSetAttribute(rans_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (int)kDecSmemBytes));
+        c->dec_attr_set = true;
+    }
+    CHK_CUDA(cudaEventRecord(c->ev[1], s));
+    const uint32_t grid = (uint32_t)(W < 148u * 64u ? W : 148u * 64u);
+    rans_decode_kernel<<<grid, 256, kDecSmemBytes, s>>>(static_cast<const TensorDesc*>(c->d_descs.p), d_freq, d_cum,
+                                                        d_hdrs, d_payload, d_sidecar, (uint32_t)W,
+                                                        c->verify_zero_lanes ? 1u : 0u,
+                                                        static_cast<uint32_t*>(c->d_status.p));
+    CHK_CUDA(cudaGetLastError());
+    c->launches++;
+    CHK_CUDA(cudaEventRecord(c->ev[2], s));
+    CHK_CUDA(cudaMemcpyAsync(c->h_status.p, c->d_status.p, W * 4, cudaMemcpyDeviceToHost, s));
+    CHK_CUDA(cudaStreamSynchronize(s));
+    c->timing["decode_ms"] = ms_between(c->ev[1], c->ev[2]);
+    const uint32_t* st = static_cast<const uint32_t*>(c->h_status.p);
+    for (size_t i = 0; i < W; ++i)
+        if (st[i])
+            throw Error{CHK_ERR_DECODE, "tensor '" + names[i] + "' failed its stream check (" +
+                                            ((st[i] & kErrEndState) ? "end state " : "") +
+                                            ((st[i] & kErrEndPointer) ? "stream length" : "") + ")"};
+    c->restored = W;
+}
+
+static void decompress_resident(Context* c, void* const* dst) {
+    const auto t_total = std::chrono::steady_clock::now();
+    CHK_CUDA(cudaSetDevice(c->device));
+    if (!c->have_resident) throw Error{CHK_ERR_INVALID, "no device-resident compressed state: call chk_compress first"};
+    c->restored = 0;
+    std::vector<TensorDesc> run;
+    std::vector<size_t> src_index;
+    std::vector<std::string> names;
+    for (size_t i = 0; i < c->work.size(); ++i) {
+        const WorkItem& w = c->work[i];
+        void* target = dst ? dst[w.idx] : c->tensors[w.idx].ptr;
+        if (!target) continue;
+        TensorDesc d = c->descs[i];
+        if (!(d.flags & kFlagRaw) && c->tables[w.table].sum != kM)
+            throw Error{CHK_ERR_FORMAT, "table of '" + c->tensors[w.idx].name + "' sums to " +
+                                            std::to_string(c->tables[w.table].sum) +
+                                            ", not 4096: the stream cannot be decoded"};
+        d.dst = static_cast<uint8_t*>(target);
+        d.src = nullptr;
+        d.flags &= ~kFlagAligned;
+        if ((reinterpret_cast<uintptr_t>(target) & 15) == 0 && (d.sidecar_off & 15) == 0) d.flags |= kFlagAligned;
+        run.push_back(d);
+        src_index.push_back(i);
+        names.push_back(c->tensors[w.idx].name);
+    }
+    const size_t W = run.size();
+    if (W == 0) return;
+    // lane headers of the selected tensors must be contiguous per descriptor index
+    const bool all = W == c->work.size();
+    if (!all) throw Error{CHK_ERR_INVALID, "chk_decompress_resident: partial restore is not supported; pass all targets"};
+    pin_ensure(c->h_descs, W * sizeof(TensorDesc));
+    std::memcpy(c->h_descs.p, run.data(), W * sizeof(TensorDesc));
+    dev_ensure(c, c->d_descs, W * sizeof(TensorDesc));
+    CHK_CUDA(cudaMemcpyAsync(c->d_descs.p, c->h_descs.p, W * sizeof(TensorDesc), cudaMemcpyHostToDevice, c->stream));
+    run_decode(c, W, static_cast<const uint8_t*>(c->d_payload.p), static_cast<const uint8_t*>(c->d_sidecar.p),
+               static_cast<const uint32_t*>(c->d_freq.p), static_cast<const uint32_t*>(c->d_cum.p),
+               static_cast<const LaneHeader*>(c->d_hdrs.p), names);
+    c->timing["decompress_total_ms"] = wall_ms(t_total);
+}
+
+static void decompress_images(Context* c, const uint8_t* st, size_t st_n, const uint8_t* mt, size_t mt_n,
+                              const uint8_t* dc, size_t dc_n) {
+    const auto t_total = std::chrono::steady_clock::now();
+    CHK_CUDA(cudaSetDevice(c->device));
+    c->restored = 0;
+    c->have_resident = false;  // device buffers are about to be reused
+    if (st_n < kFileHeader || get<uint32_t>(st) != kStatesMagic || get<uint32_t>(st + 4) != kStatesVersion)
+        throw Error{CHK_ERR_FORMAT, "states file: bad magic or version"};
+    if (mt_n < kFileHeader || get<uint32_t>(mt) != kMantMagic || get<uint32_t>(mt + 4) != kMantVersion)
+        throw Error{CHK_ERR_FORMAT, "mantissa file: bad magic or version"};
+    if (dc_n < kFileHeader || get<uint32_t>(dc) != kDictMagic || get<uint32_t>(dc + 4) != kDictVersion)
+        throw Error{CHK_ERR_FORMAT, "tables file: bad magic or version"};
+    const size_t n_st = get<uint32_t>(st + 12), n_mt = get<uint32_t>(mt + 12), n_dc = get<uint32_t>(dc + 12);
+    const size_t st_data = kFileHeader + n_st * kStatesEntry;
+    const size_t mt_data = kFileHeader + n_mt * kMantEntry;
+    if (st_n < st_data) throw Error{CHK_ERR_FORMAT, "states file: truncated index"};
+    if (mt_n < mt_data) throw Error{CHK_ERR_FORMAT, "mantissa file: truncated index"};
+    if (dc_n < kFileHeader + n_dc * kDictEntry) throw Error{CHK_ERR_FORMAT, "tables file: truncated"};
+    const size_t payload_total = st_n - st_data, sidecar_total = mt_n - mt_data;
+
+    std::unordered_map<std::string, size_t> reg, side, tab;
+    for (size_t i = 0; i < c->tensors.size(); ++i) reg.emplace(c->tensors[i].name, i);
+    for (size_t i = 0; i < n_mt; ++i) side.emplace(get_name(mt + kFileHeader + i * kMantEntry), i);
+    for (size_t i = 0; i < n_dc; ++i) tab.emplace(get_name(dc + kFileHeader + i * kDictEntry), i);
+
+    std::vector<TensorDesc> run;
+    std::vector<size_t> entry_of;
+    std::vector<std::string> names;
+    for (size_t i = 0; i < n_st; ++i) {
+        const uint8_t* e = st + kFileHeader + i * kStatesEntry;
+        const std::string name = get_name(e);
+        auto r = reg.find(name);
+        if (r == reg.end()) continue;
+        const Tensor& t = c->tensors[r->second];
+        if (!t.ptr) continue;
+        const uint8_t dtype = e[256];
+        const bool is_raw = e[257] != 0, owns = e[258] != 0;
+        const uint64_t bytes = get<uint64_t>(e + 264), n_elem = get<uint64_t>(e + 272);
+        const uint64_t off = get<uint64_t>(e + 280), size = get<uint64_t>(e + 288);
+        const uint32_t es = elem_size(dtype), spe = sidecar_per_elem(dtype);
+        if (es == 0 || bytes != n_elem * es) throw Error{CHK_ERR_FORMAT, "entry '" + name + "': inconsistent sizes"};
+        if (t.dtype != dtype || t.n_elem != n_elem)
+            throw Error{CHK_ERR_INVALID, "tensor '" + name + "': registered dtype/size differs from the checkpoint"};
+        if (off + size > payload_total) throw Error{CHK_ERR_FORMAT, "entry '" + name + "': payload out of range"};
+        if (is_raw && size != bytes) throw Error{CHK_ERR_FORMAT, "entry '" + name + "': raw payload size mismatch"};
+        TensorDesc d{};
+        d.dst = static_cast<uint8_t*>(t.ptr);
+        d.n_bytes = bytes;
+        d.es = es;
+        d.spe = spe;
+        d.payload_off = off;
+        d.flags = is_raw ? kFlagRaw : 0u;
+        if (!is_raw) {
+            const std::string key = owns ? name : get_name(e + 296);
+            auto tb = tab.find(key);
+            if (tb == tab.end()) throw Error{CHK_ERR_FORMAT, "entry '" + name + "': table '" + key + "' not in tables file"};
+            d.table_idx = (uint32_t)tb->second;
+            const uint8_t* te = dc + kFileHeader + tb->second * kDictEntry;
+            const uint32_t sum = get<uint32_t>(te + 1280 + 256 * 4);
+            if (sum != kM)
+                throw Error{CHK_ERR_FORMAT, "table '" + key + "' sums to " + std::to_string(sum) +
+                                                ", not 4096: the stream cannot be decoded"};
+            // lane ranges must lie inside this tensor's payload
+            const LaneHeader* lh = reinterpret_cast<const LaneHeader*>(e + 552);
+            for (int l = 0; l < 256; ++l) {
+                LaneHeader h;
+                std::memcpy(&h, lh + l, sizeof(h));
+                if ((uint64_t)h.buf_offset + h.byte_count > size)
+                    throw Error{CHK_ERR_FORMAT, "entry '" + name + "': lane " + std::to_string(l) + " out of range"};
+            }
+        }
+        if (spe) {
+            auto sd = side.find(name);
+            if (sd == side.end()) throw Error{CHK_ERR_FORMAT, "entry '" + name + "': no sidecar in mantissa file"};
+            const uint8_t* m = mt + kFileHeader + sd->second * kMantEntry;
+            const uint64_t moff = get<uint64_t>(m + 272), msz = get<uint64_t>(m + 280);
+            if (msz != n_elem * spe || moff + msz > sidecar_total)
+                throw Error{CHK_ERR_FORMAT, "entry '" + name + "': sidecar out of range"};
+            d.sidecar_off = moff;
+        }
+        if ((reinterpret_cast<uintptr_t>(d.dst) & 15) == 0 && (d.sidecar_off & 15) == 0) d.flags |= kFlagAligned;
+        run.push_back(d);
+        entry_of.push_back(i);
+        names.push_back(name);
+    }
+    const size_t W = run.size();
+    if (W == 0) return;
+
+    cudaStream_t s = c->stream;
+    dev_ensure(c, c->d_descs, W * sizeof(TensorDesc));
+    dev_ensure(c, c->d_payload, payload_total + 64);
+    dev_ensure(c, c->d_sidecar, sidecar_total + 64);
+    dev_ensure(c, c->d_hdrs, W * 4096);
+    dev_ensure(c, c->d_freq, n_dc * 256 * 4 + 4);
+    dev_ensure(c, c->d_cum, n_dc * 257 * 4 + 4);
+    pin_ensure(c->h_descs, W * sizeof(TensorDesc));
+    std::memcpy(c->h_descs.p, run.data(), W * sizeof(TensorDesc));
+
+    CHK_CUDA(cudaEventRecord(c->ev[0], s));
+    CHK_CUDA(cudaMemcpyAsync(c->d_descs.p, c->h_descs.p, W * sizeof(TensorDesc), cudaMemcpyHostToDevice, s));
+    if (payload_total) CHK_CUDA(cudaMemcpyAsync(c->d_payload.p, st + st_data, payload_total, cudaMemcpyHostToDevice, s));
+    if (sidecar_total) CHK_CUDA(cudaMemcpyAsync(c->d_sidecar.p, mt + mt_data, sidecar_total, cudaMemcpyHostToDevice, s));
+    // lane headers: one strided copy per run of consecutive entries
+    for (size_t k = 0; k < W;) {
+        size_t j = k + 1;
+        while (j < W && entry_of[j] == entry_of[j - 1] + 1) ++j;
+        CHK_CUDA(cudaMemcpy2DAsync(static_cast<uint8_t*>(c->d_hdrs.p) + k * 4096, 4096,
+                                   st + kFileHeader + entry_of[k] * kStatesEntry + 552, kStatesEntry, 4096, j - k,
+                                   cudaMemcpyHostToDevice, s));
+        k = j;
+    }
+    if (n_dc) {
+        CHK_CUDA(cudaMemcpy2DAsync(c->d_freq.p, 1024, dc + kFileHeader + 256, kDictEntry, 1024, n_dc,
+                                   cudaMemcpyHostToDevice, s));
+        CHK_CUDA(cudaMemcpy2DAsync(c->d_cum.p, 1028, dc + kFileHeader + 1280, kDictEntry, 1028, n_dc,
+                                   cudaMemcpyHostToDevice, s));
+    }
+    CHK_CUDA(cudaEventRecord(c->ev[3], s));
+    run_decode(c, W, static_cast<const uint8_t*>(c->d_payload.p), static_cast<const uint8_t*>(c->d_sidecar.p),
+               static_cast<const uint32_t*>(c->d_freq.p), static_cast<const uint32_t*>(c->d_cum.p),
+               static_cast<const LaneHeader*>(c->d_hdrs.p), names);
+    c->timing["h2d_ms"] = ms_between(c->ev[0], c->ev[3]);
+    c->timing["decompress_total_ms"] = wall_ms(t_total);
+}
+
+static void read_file(const std::string& path, PinBuf& out) {
+    std::FILE* f = std::fopen(path.c_str(), "rb");
+    if (!f) throw Error{CHK_ERR_IO, "cannot open: " + path};
+    std::fseek(f, 0, SEEK_END);
+    const long n = std::ftell(f);
+    std::fseek(f, 0, SEEK_SET);
+    if (n < 0) {
+        std::fclose(f);
+        throw Error{CHK_ERR_IO, "cannot size: " + path};
+    }
+    pin_ensure(out, (size_t)n);
+    const size_t r = n ? std::fread(out.p, 1, (size_t)n, f) : 0;
+    std::fclose(f);
+    if (r != (size_t)n) throw Error{CHK_ERR_IO, "short read: " + path};
+}
+
+static void load_and_decompress(Context* c, const std::string& dir) {
+    const auto t0 = std::chrono::steady_clock::now();
+    std::string paths[3];
+    rank_paths(c, dir, paths);
+    for (int k = 0; k < 3; ++k) read_file(paths[k], c->img[k]);
+    c->have_images = false;
+    c->timing["io_ms"] = wall_ms(t0);
+    decompress_images(c, static_cast<const uint8_t*>(c->img[0].p), c->img[0].size,
+                      static_cast<const uint8_t*>(c->img[1].p), c->img[1].size,
+                      static_cast<const uint8_t*>(c->img[2].p), c->img[2].size);
+}
+
+// ------------------------------------------------------------------ analysis
+static void analyze(Context* c) {
+    CHK_CUDA(cudaSetDevice(c->device));
+    const size_t N = c->tensors.size();
+    c->stats.assign(N, StatsOut{});
+    if (N == 0) return;
+    cudaStream_t s = c->stream;
+    std::vector<StatsDesc> d(N);
+    for (size_t i = 0; i < N; ++i) {
+        const Tensor& t = c->tensors[i];
+        d[i] = StatsDesc{elem_size(t.dtype) ? t.ptr : nullptr, t.n_elem, t.dtype, c->histogram_bins};
+    }
+    dev_ensure(c, c->d_stats_desc, N * sizeof(StatsDesc));
+    dev_ensure(c, c->d_stats_out, N * sizeof(StatsOut));
+    pin_ensure(c->h_stats, N * sizeof(StatsOut));
+    CHK_CUDA(cudaMemcpyAsync(c->d_stats_desc.p, d.data(), N * sizeof(StatsDesc), cudaMemcpyHostToDevice, s));
+    CHK_CUDA(cudaMemsetAsync(c->d_stats_out.p, 0, N * sizeof(StatsOut), s));
+    CHK_CUDA(cudaEventRecord(c->ev[0], s));
+    const uint32_t grid = (uint32_t)(N < 148u * 64u ? N : 148u * 64u);
+    tensor_stats_kernel<<<grid, 256, 0, s>>>(static_cast<const StatsDesc*>(c->d_stats_desc.p),
+                                             static_cast<StatsOut*>(c->d_stats_out.p), (uint32_t)N);
+    CHK_CUDA(cudaGetLastError());
+    c->launches++;
+    CHK_CUDA(cudaEventRecord(c->ev[1], s));
+    CHK_CUDA(cudaMemcpyAsync(c->h_stats.p, c->d_stats_out.p, N * sizeof(StatsOut), cudaMemcpyDeviceToHost, s));
+    CHK_CUDA(cudaStreamSynchronize(s));
+    c->timing["analyze_stats_ms"] = ms_between(c->ev[0], c->ev[1]);
+    std::memcpy(c->stats.data(), c->h_stats.p, N * sizeof(StatsOut));
+
+    const auto t0 = std::chrono::steady_clock::now();
+    std::vector<std::string> names(N);
+    std::vector<float> fps(N * 5);
+    for (size_t i = 0; i < N; ++i) {
+        names[i] = c->tensors[i].name;
+        std::memcpy(&fps[i * 5], c->stats[i].fingerprint, 20);
+    }
+    c->clusters = build_clusters(names, fps);
+    c->have_clusters = true;
+    c->timing["analyze_cluster_ms"] = wall_ms(t0);
+}
+
+}  // namespace chk
+
+// ====================================================================== C ABI
+using namespace chk;
+struct chk_context : chk::Context {};
+
+#define CHK_API_BEGIN try {
+#define CHK_API_END                                   \
+    }                                                 \
+    catch (const chk::Error& e) {                     \
+        chk::g_last_error = e.msg;                    \
+        return e.code;                                \
+    }                                                 \
+    catch (const std::exception& e) {                 \
+        chk::g_last_error = e.what();                 \
+        return CHK_ERR_INVALID;                       \
+    }                                                 \
+    return CHK_OK;
+
+#define CHK_REQUIRE(cond, msg) \
+    if (!(cond)) throw chk::Error { CHK_ERR_INVALID, msg }
+
+extern "C" {
+
+const char* chk_last_error(void) { return chk::g_last_error.c_str(); }
+
+int chk_context_create(int device, int rank, int local_rank, chk_context** out) {
+    CHK_API_BEGIN
+    CHK_REQUIRE(out, "out is NULL");
+    int n = 0;
+    CHK_CUDA(cudaGetDeviceCount(&n));
+    CHK_REQUIRE(device >= 0 && device < n, "no such CUDA device");
+    CHK_CUDA(cudaSetDevice(device));
+    auto* c = new chk_context();
+    c->device = device;
+    c->rank = rank;
+    c->local_rank = local_rank;
+    try {
+        CHK_CUDA(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
+        cudaMemPoolProps props{};
+        props.allocType = cudaMemAllocationTypePinned;
+        props.handleTypes = cudaMemHandleTypeNone;
+        props.location.type = cudaMemLocationTypeDevice;
+        props.location.id = device;
+        CHK_CUDA(cudaMemPoolCreate(&c->pool, &props));
+        uint64_t keep = UINT64_MAX;
+        CHK_CUDA(cudaMemPoolSetAttribute(c->pool, cudaMemPoolAttrReleaseThreshold, &keep));
+        for (auto& e : c->ev) CHK_CUDA(cudaEventCreate(&e));
+    } catch (...) {
+        delete c;
+        throw;
+    }
+    *out = c;
+    CHK_API_END
+}
+
+int chk_context_destroy(chk_context* c) {
+    CHK_API_BEGIN
+    if (!c) return CHK_OK;
+    cudaSetDevice(c->device);
+    if (c->stream) cudaStreamSynchronize(c->stream);
+    DevBuf* bufs[] = {&c->d_descs, &c->d_tiles, &c->d_hist, &c->d_sidecar, &c->d_scratch, &c->d_hdrs,
+                      &c->d_wpos, &c->d_loff, &c->d_psize, &c->d_poff, &c->d_payload, &c->d_enc,
+                      &c->d_freq, &c->d_cum, &c->d_status, &c->d_stats_desc, &c->d_stats_out};
+    for (DevBuf* b : bufs)
+        if (b->p) cudaFreeAsync(b->p, c->stream);
+    if (c->stream) cudaStreamSynchronize(c->stream);
+    PinBuf* pins[] = {&c->h_hist, &c->h_hdrs, &c->h_poff, &c->h_descs, &c->h_status, &c->h_enc, &c->h_stats,
+                      &c->img[0], &c->img[1], &c->img[2]};
+    for (PinBuf* b : pins)
+        if (b->p) cudaFreeHost(b->p);
+    for (auto& e : c->ev)
+        if (e) cudaEventDestroy(e);
+    if (c->pool) cudaMemPoolDestroy(c->pool);
+    if (c->stream) cudaStreamDestroy(c->stream);
+    delete c;
+    CHK_API_END
+}
+
+int chk_reset(chk_context* c) {
+    CHK_API_BEGIN
+    CHK_REQUIRE(c, "context is NULL");
+    c->tensors.clear();
+    c->clusters = ClusterMap{};
+    c->have_clusters = false;
+    c->stats.clear();
+    c->work.clear();
+    c->tables.clear();
+    c->descs.clear();
+    c->have_resident = c->have_images = false;
+    c->summary = chk_summary{};
+    c->restored = 0;
+    CHK_API_END
+}
+
+int chk_set_histogram_bins(chk_context* c, uint32_t bins) {
+    CHK_API_BEGIN
+    CHK_REQUIRE(c, "context is NULL");
+    c->histogram_bins = bins;
+    CHK_API_END
+}
+
+int chk_register_tensor(chk_context* c, const char* name, const void* ptr, uint64_t n, uint8_t dtype, uint8_t cat) {
+    CHK_API_BEGIN
+    CHK_REQUIRE(c && name, "context or name is NULL");
+    c->tensors.push_back(Tensor{name, const_cast<void*>(ptr), n, dtype, cat});
+    c->have_resident = false;
+    CHK_API_END
+}
+
+int chk_tensor_count(chk_context* c, uint64_t* count) {
+    CHK_API_BEGIN
+    CHK_REQUIRE(c && count, "NULL argument");
+    *count = c->tensors.size();
+    CHK_API_END
+}
+
+int chk_set_option(chk_context* c, const char* key, int64_t value) {
+    CHK_API_BEGIN
+    CHK_REQUIRE(c && key, "NULL argument");
+    const std::string k(key);
+    if (k == "repair_tables")
+        c->repair_tables = value != 0;
+    else if (k == "verify_zero_lanes")
+        c->verify_zero_lanes = value != 0;
+    else if (k == "host_threads")
+        c->host_threads = (int)value;
+    else
+        throw chk::Error{CHK_ERR_INVALID, "unknown option: " + k};
+    CHK_API_END
+}
+
+int chk_analyze(chk_context* c) {
+    CHK_API_BEGIN
+    CHK_REQUIRE(c, "context is NULL");
+    analyze(c);
+    CHK_API_END
+}
+
+int chk_get_tensor_stats(chk_context* c, uint64_t i, uint32_t hist[256], float moments[4], float minmax[2],
+                         float fingerprint[5]) {
+    CHK_API_BEGIN
+    CHK_REQUIRE(c, "context is NULL");
+    CHK_REQUIRE(i < c->stats.size(), "no statistics for that index: call chk_analyze first");
+    const StatsOut& o = c->stats[i];
+    if (hist) std::memcpy(hist, o.hist, 1024);
+    if (moments) std::memcpy(moments, o.moments, 16);
+    if (minmax) std::memcpy(minmax, o.minmax, 8);
+    if (fingerprint) std::memcpy(fingerprint, o.fingerprint, 20);
+    CHK_API_END
+}
+
+int chk_get_cluster_ids(chk_context* c, int32_t* ids, uint64_t cap, int32_t* n_clusters) {
+    CHK_API_BEGIN
+    CHK_REQUIRE(c, "context is NULL");
+    CHK_REQUIRE(cap >= c->tensors.size() || !ids, "capacity too small");
+    if (ids)
+        for (size_t i = 0; i < c->tensors.size(); ++i) {
+            auto it = c->clusters.tensor_to_cluster.find(c->tensors[i].name);
+            ids[i] = (c->have_clusters && it != c->clusters.tensor_to_cluster.end()) ? it->second : -1;
+        }
+    if (n_clusters) *n_clusters = c->have_clusters ? c->clusters.n_clusters : 0;
+    CHK_API_END
+}
+
+int chk_get_cluster_anchor(chk_context* c, int32_t cluster, char name_out[256]) {
+    CHK_API_BEGIN
+    CHK_REQUIRE(c && name_out, "NULL argument");
+    auto it = c->clusters.cluster_anchor.find(cluster);
+    CHK_REQUIRE(c->have_clusters && it != c->clusters.cluster_anchor.end(), "no such cluster");
+    std::memset(name_out, 0, 256);
+    std::strncpy(name_out, it->second.c_str(), 255);
+    CHK_API_END
+}
+
+int chk_set_cluster_info(chk_context* c, uint64_t n, const char* const* names, const int32_t* ids, int32_t n_clusters,
+                         const char* const* anchors) {
+    CHK_API_BEGIN
+    CHK_REQUIRE(c, "context is NULL");
+    CHK_REQUIRE(n == 0 || (names && ids), "names/ids are NULL");
+    ClusterMap m;
+    for (uint64_t i = 0; i < n; ++i) m.tensor_to_cluster[names[i]] = ids[i] < 0 ? -1 : ids[i];
+    for (int32_t k = 0; k < n_clusters; ++k)
+        if (anchors && anchors[k]) m.cluster_anchor[k] = anchors[k];
+    m.n_clusters = n_clusters;
+    c->clusters = std::move(m);
+    c->have_clusters = true;
+    CHK_API_END
+}
+
+int chk_compress_and_save(chk_context* c, const char* dir) {
+    CHK_API_BEGIN
+    CHK_REQUIRE(c && dir, "NULL argument");
+    compress_and_save(c, dir);
+    CHK_API_END
+}
+
+int chk_compress(chk_context* c, int host_images) {
+    CHK_API_BEGIN
+    CHK_REQUIRE(c, "context is NULL");
+    compress(c, host_images != 0);
+    CHK_API_END
+}
+
+int chk_get_image(chk_context* c, int which, const void** data, uint64_t* size) {
+    CHK_API_BEGIN
+    CHK_REQUIRE(c && data && size, "NULL argument");
+    CHK_REQUIRE(which >= 0 && which < 3, "which must be 0, 1 or 2");
+    CHK_REQUIRE(c->have_images, "no host images: call chk_compress(ctx, 1) first");
+    *data = c->img[which].p;
+    *size = c->img[which].size;
+    CHK_API_END
+}
+
+int chk_get_summary(chk_context* c, chk_summary* out) {
+    CHK_API_BEGIN
+    CHK_REQUIRE(c && out, "NULL argument");
+    *out = c->summary;
+    CHK_API_END
+}
+
+int chk_load_and_decompress(chk_context* c, const char* dir) {
+    CHK_API_BEGIN
+    CHK_REQUIRE(c && dir, "NULL argument");
+    load_and_decompress(c, dir);
+    CHK_API_END
+}
+
+int chk_decompress_images(chk_context* c, const void* st, uint64_t st_n, const void* mt, uint64_t mt_n, const void* dc,
+                          uint64_t dc_n) {
+    CHK_API_BEGIN
+    CHK_REQUIRE(c && st && mt && dc, "NULL argument");
+    decompress_images(c, static_cast<const uint8_t*>(st), st_n, static_cast<const uint8_t*>(mt), mt_n,
+                      static_cast<const uint8_t*>(dc), dc_n);
+    CHK_API_END
+}
+
+int chk_decompress_resident(chk_context* c, void* const* dst) {
+    CHK_API_BEGIN
+    CHK_REQUIRE(c, "context is NULL");
+    decompress_resident(c, dst);
+    CHK_API_END
+}
+
+int chk_restored_count(chk_context* c, uint64_t* count) {
+    CHK_API_BEGIN
+    CHK_REQUIRE(c && count, "NULL argument");
+    *count = c->restored;
+    CHK_API_END
+}
+
+int chk_split(chk_context* c, const void* d_src, uint64_t n_elem, uint8_t dtype, void* d_masked, void* d_sidecar) {
+    CHK_API_BEGIN
+    CHK_REQUIRE(c && d_src && d_masked, "NULL argument");
+    const uint32_t es = elem_size(dtype), spe = sidecar_per_elem(dtype);
+    CHK_REQUIRE(es && spe, "dtype has no low-byte split");
+    CHK_REQUIRE(d_sidecar, "sidecar is NULL");
+    if (n_elem == 0) return CHK_OK;
+    CHK_CUDA(cudaSetDevice(c->device));
+    const unsigned long long nb = n_elem * es;
+    const uint32_t vec = ((reinterpret_cast<uintptr_t>(d_src) | reinterpret_cast<uintptr_t>(d_masked)) & 15) == 0 &&
+                         (reinterpret_cast<uintptr_t>(d_sidecar) & 7) == 0;
+    const unsigned long long want = (nb / 16 + 255) / 256 + 1;
+    const uint32_t grid = (uint32_t)(want < 148ull * 16 ? want : 148ull * 16);
+    split_kernel<<<grid, 256, 0, c->stream>>>(static_cast<const uint8_t*>(d_src), nb, es, spe,
+                                              static_cast<uint8_t*>(d_masked), static_cast<uint8_t*>(d_sidecar), vec);
+    CHK_CUDA(cudaGetLastError());
+    c->launches++;
+    CHK_CUDA(cudaStreamSynchronize(c->stream));
+    CHK_API_END
+}
+
+int chk_byte_histogram(chk_context* c, const void* d_data, uint64_t n_bytes, uint32_t hist_out[256]) {
+    CHK_API_BEGIN
+    CHK_REQUIRE(c && hist_out, "NULL argument");
+    std::memset(hist_out, 0, 1024);
+    if (n_bytes == 0) return CHK_OK;
+    CHK_REQUIRE(d_data, "data is NULL");
+    CHK_CUDA(cudaSetDevice(c->device));
+    dev_ensure(c, c->d_hist, 1024);
+    CHK_CUDA(cudaMemsetAsync(c->d_hist.p, 0, 1024, c->stream));
+    const unsigned long long want = (n_bytes / 16 + 255) / 256 + 1;
+    const uint32_t grid = (uint32_t)(want < 148ull * 8 ? want : 148ull * 8);
+    byte_histogram_kernel<<<grid, 256, 0, c->stream>>>(static_cast<const uint8_t*>(d_data), n_bytes,
+                                                       static_cast<uint32_t*>(c->d_hist.p));
+    CHK_CUDA(cudaGetLastError());
+    c->launches++;
+    CHK_CUDA(cudaMemcpyAsync(hist_out, c->d_hist.p, 1024, cudaMemcpyDeviceToHost, c->stream));
+    CHK_CUDA(cudaStreamSynchronize(c->stream));
+    CHK_API_END
+}
+
+int chk_normalize_histogram(const uint32_t hist[256], int full, int repair, uint32_t norm_freq[256],
+                            uint32_t cum_freq[257], uint32_t x_max[256], uint32_t* sum_out) {
+    CHK_API_BEGIN
+    CHK_REQUIRE(hist && norm_freq && cum_freq, "NULL argument");
+    FreqTable t;
+    normalize_histogram(hist, full != 0, repair != 0, t);
+    std::memcpy(norm_freq, t.norm_freq, 1024);
+    std::memcpy(cum_freq, t.cum_freq, 1028);
+    if (x_max)
+        for (int s = 0; s < 256; ++s) x_max[s] = t.norm_freq[s] << 19;
+    if (sum_out) *sum_out = t.sum;
+    CHK_API_END
+}
+
+int chk_get_timing(chk_context* c, const char* key, double* ms) {
+    CHK_API_BEGIN
+    CHK_REQUIRE(c && key && ms, "NULL argument");
+    auto it = c->timing.find(key);
+    *ms = it == c->timing.end() ? 0.0 : it->second;
+    CHK_API_END
+}
+
+int chk_get_stream(chk_context* c, void** stream_out) {
+    CHK_API_BEGIN
+    CHK_REQUIRE(c && stream_out, "NULL argument");
+    *stream_out = c->stream;
+    CHK_API_END
+}
+
+int chk_kernel_launches(chk_context* c, uint64_t* count) {
+    CHK_API_BEGIN
+    CHK_REQUIRE(c && count, "NULL argument");
+    *count = c->launches;
+    CHK_API_END
+}
+
+}  // extern "C"

@@ -1,0 +1,142 @@
+/*
+ * checkers_b200.h -- C ABI of the B200 checkpoint-compression library
+ * (libcheckers_b200.so).
+ *
+ * The Checkers reference exposes this path as three pybind11 functions backed
+ * by a process-wide registry; it has no C ABI.  Each entry point below names
+ * the reference interface it stands in for (file:line inside the Checkers
+ * tree), so a binding for the reference's own front end can be written one to
+ * one.  Plain pointers and sizes only; no exceptions cross this boundary:
+ * every function returns CHK_OK (0) or a negative CHK_ERR_* code and leaves a
+ * message for chk_last_error() on the calling thread.
+ *
+ * Tensors are BORROWED device pointers, exactly as in the reference
+ * (src/TensorResource.cpp:16-33): they must stay valid and unchanged from
+ * registration until the call that uses them returns.  All work of a context
+ * is issued on the device given at creation; a context is not thread-safe.
+ */
+#ifndef CHECKERS_B200_H
+#define CHECKERS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CHK_OK 0
+#define CHK_ERR_INVALID (-1)  /* bad argument or call order */
+#define CHK_ERR_CUDA (-2)     /* a CUDA runtime call failed */
+#define CHK_ERR_IO (-3)       /* file could not be read or written */
+#define CHK_ERR_FORMAT (-4)   /* file contents are not a valid checkpoint */
+#define CHK_ERR_DECODE (-5)   /* a stream failed its end-state / length check */
+#define CHK_ERR_TIMEOUT (-6)  /* a bounded device-side wait ran out */
+#define CHK_ERR_CAPACITY (-7) /* a size exceeds a stated fixed limit */
+
+/* DataType tags, include/checkers/TensorResource.hpp:30-37 */
+enum { CHK_F32 = 0, CHK_BF16 = 1, CHK_F16 = 2, CHK_I8 = 3, CHK_I32 = 4, CHK_DTYPE_UNKNOWN = 255 };
+/* TensorCategory tags, include/checkers/TensorResource.hpp:59-65 */
+enum { CHK_CAT_MODEL = 0, CHK_CAT_MASTER = 1, CHK_CAT_EXP_AVG = 2, CHK_CAT_EXP_AVG_SQ = 3, CHK_CAT_UNKNOWN = 255 };
+
+typedef struct chk_context chk_context;
+
+/* Per-rank totals of the last compression; the six numbers every rank
+ * contributes to the all-gathered manifest. */
+typedef struct {
+    uint64_t n_tensors;
+    uint64_t n_tables;
+    uint64_t states_bytes;   /* size of rank_<r>_states.ansc */
+    uint64_t mantissa_bytes; /* size of rank_<r>_mantissa.mant */
+    uint64_t dict_bytes;     /* size of rank_<r>_tables.dict */
+    uint64_t original_bytes; /* uncompressed bytes of the tensors written */
+} chk_summary;
+
+const char* chk_last_error(void);
+
+/* ---- context and registry ------------------------------------------------
+ * chk_context_create + chk_register_tensor replace
+ * checkers::initialize_context (src/api.cpp:899-1031) minus its DeepSpeed
+ * object walk: the caller hands over what that walk would have found
+ * (name, device pointer, element count, dtype; src/api.cpp:789-850,
+ * MemoryManager::submit_tensor src/MemoryManager.cpp:218-250).  Records keep
+ * submission order, which is the order of every output file. */
+int chk_context_create(int device, int rank, int local_rank, chk_context** out);
+int chk_context_destroy(chk_context* ctx);
+int chk_reset(chk_context* ctx); /* MemoryManager::reset: forget tensors, clusters, results */
+int chk_set_histogram_bins(chk_context* ctx, uint32_t bins); /* initialize_context(histogram_bins=) */
+int chk_register_tensor(chk_context* ctx, const char* name, const void* device_ptr, uint64_t num_elements,
+                        uint8_t dtype, uint8_t category);
+int chk_tensor_count(chk_context* ctx, uint64_t* count);
+/* Options: "repair_tables" (0/1; shared tables are renormalised until they sum
+ * to 4096 -- a deviation from the reference that keeps them decodable),
+ * "verify_zero_lanes" (0/1; decode also checks the lanes that only carry
+ * zeroed low bytes), "host_threads" (threads for table normalisation, 0 = all). */
+int chk_set_option(chk_context* ctx, const char* key, int64_t value);
+
+/* ---- analysis: checkers::analyze_tensors, src/api.cpp:1033-1253 ----------
+ * tensor_stats_kernel (src/TensorAnalyzer.cpp:64-229), fingerprints
+ * (:271-292) and the per-category union-find clustering (:440-598). */
+int chk_analyze(chk_context* ctx);
+int chk_get_tensor_stats(chk_context* ctx, uint64_t index, uint32_t hist[256], float moments[4], float minmax[2],
+                         float fingerprint[5]);
+/* cluster_id[i] for every registered tensor (-1 = singleton); *n_clusters out. */
+int chk_get_cluster_ids(chk_context* ctx, int32_t* cluster_id, uint64_t capacity, int32_t* n_clusters);
+int chk_get_cluster_anchor(chk_context* ctx, int32_t cluster, char name_out[256]);
+/* MemoryManager::set_cluster_info (include/checkers/MemoryManager.hpp:180):
+ * install a cluster map from outside.  ids[i] < 0 marks names[i] a singleton. */
+int chk_set_cluster_info(chk_context* ctx, uint64_t n, const char* const* names, const int32_t* ids,
+                         int32_t n_clusters, const char* const* anchor_names);
+
+/* ---- codec: checkers::compress_and_save, src/api.cpp:1255-1299 -----------
+ * ANSCompressor::compress_and_save_all (src/ANSCompressor.cpp:1014-1401):
+ * writes <dir>/rank_<r>_states.ansc, <dir>/mantissa/rank_<r>_mantissa.mant and
+ * <dir>/tables/rank_<r>_tables.dict in the reference's layout (:751-931). */
+int chk_compress_and_save(chk_context* ctx, const char* output_dir);
+/* Same pipeline, results kept in memory.  host_images != 0 also builds the
+ * three file images in pinned host memory (fetch with chk_get_image);
+ * otherwise the compressed state stays on the device for chk_decompress_resident. */
+int chk_compress(chk_context* ctx, int host_images);
+/* which: 0 states, 1 mantissa, 2 tables.  Pointers stay valid until the next
+ * compress call on this context. */
+int chk_get_image(chk_context* ctx, int which, const void** data, uint64_t* size);
+int chk_get_summary(chk_context* ctx, chk_summary* out);
+
+/* ---- restore (the reference ships no reader; inverse of the above) -------
+ * Every tensor found in the files whose name is registered in this context is
+ * decoded into the registered pointer (size and dtype must match). */
+int chk_load_and_decompress(chk_context* ctx, const char* input_dir);
+int chk_decompress_images(chk_context* ctx, const void* states, uint64_t states_size, const void* mantissa,
+                          uint64_t mantissa_size, const void* tables, uint64_t tables_size);
+/* Decode the device-resident result of the last chk_compress.  dst[i] (device
+ * pointer, one per registered tensor, may be NULL to skip) receives tensor i;
+ * dst == NULL restores into the registered pointers. */
+int chk_decompress_resident(chk_context* ctx, void* const* dst);
+/* Number of tensors restored by the last decompress call. */
+int chk_restored_count(chk_context* ctx, uint64_t* count);
+
+/* ---- stage-level entry points (device pointers; one tensor) --------------
+ * extract_mantissa_kernel (src/ANSCompressor.cpp:258-279, host :945-1009),
+ * byte_histogram_kernel (:109-126, host :393-411),
+ * normalize_histogram (:416-503; host arithmetic, no device involved). */
+int chk_split(chk_context* ctx, const void* d_src, uint64_t num_elements, uint8_t dtype, void* d_masked,
+              void* d_sidecar);
+int chk_byte_histogram(chk_context* ctx, const void* d_data, uint64_t n_bytes, uint32_t hist_out[256]);
+int chk_normalize_histogram(const uint32_t hist[256], int ensure_full_alphabet, int repair, uint32_t norm_freq[256],
+                            uint32_t cum_freq[257], uint32_t x_max[256], uint32_t* sum_out);
+
+/* ---- timing: the reference's [TIMING] / per-tensor ms fields -------------
+ * Keys: split_hist_ms, table_ms, encode_ms, compact_ms, compress_device_ms,
+ * d2h_ms, io_ms, compress_total_ms, h2d_ms, decode_ms, decompress_total_ms,
+ * analyze_stats_ms, analyze_cluster_ms.  Device spans are CUDA-event times. */
+int chk_get_timing(chk_context* ctx, const char* key, double* ms);
+/* The CUDA stream (cudaStream_t) all of this context's work is issued on, so a
+ * caller can order its own work or record events against it. */
+int chk_get_stream(chk_context* ctx, void** stream_out);
+/* Kernels launched by this context since creation. */
+int chk_kernel_launches(chk_context* ctx, uint64_t* count);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -807,4 +807,74 @@ int64_t orc_load_tensor(const char* dir, int rank, const char* name, uint8_t* ou
     return -11;
 }
 
+int orc_roundtrip_timed(size_t n, const void* const* data, const uint64_t* num_elements, const uint8_t* dtypes,
+                        int n_threads, double seconds_out[2], uint64_t bytes_out[3]) {
+    struct Item {
+        std::vector<uint8_t> payload, sidecar;
+        orc_lane_header lanes[256];
+        uint32_t nf[256], cf[257], xm[256];
+        int raw = 0;
+    };
+    std::vector<Item> items(n);
+    const int nt = clamp_threads(n_threads);
+    uint64_t orig = 0, pay = 0, side = 0;
+    int bad = 0;
+    auto now = [] {
+#ifdef _OPENMP
+        return omp_get_wtime();
+#else
+        return (double)clock() / CLOCKS_PER_SEC;
+#endif
+    };
+    const double t0 = now();
+#pragma omp parallel for schedule(dynamic, 1) num_threads(nt) reduction(+ : orig, pay, side)
+    for (long i = 0; i < (long)n; ++i) {
+        Item& it = items[i];
+        const int dt = dtypes[i];
+        const uint32_t es = orc_elem_size(dt), spe = orc_sidecar_per_elem(dt);
+        const size_t B = (size_t)num_elements[i] * es;
+        const uint8_t* src = (const uint8_t*)data[i];
+        std::vector<uint8_t> masked;
+        const uint8_t* in = src;
+        if (spe) {
+            masked.resize(B);
+            it.sidecar.resize((size_t)num_elements[i] * spe);
+            orc_split(src, num_elements[i], es, spe, masked.data(), it.sidecar.data());
+            in = masked.data();
+        }
+        uint32_t h[256];
+        orc_byte_histogram(in, B, h);
+        orc_normalize(h, 0, it.nf, it.cf, it.xm);
+        it.payload.resize(std::max(((B + 255) / 256) * 2 * 256, B));
+        size_t sz = orc_compress_tensor(in, B, it.nf, it.cf, it.xm, it.lanes, it.payload.data(), &it.raw, 1);
+        it.payload.resize(sz);
+        orig += B;
+        pay += sz;
+        side += it.sidecar.size();
+    }
+    const double t1 = now();
+#pragma omp parallel for schedule(dynamic, 1) num_threads(nt) reduction(+ : bad)
+    for (long i = 0; i < (long)n; ++i) {
+        Item& it = items[i];
+        const int dt = dtypes[i];
+        const uint32_t es = orc_elem_size(dt), spe = orc_sidecar_per_elem(dt);
+        const size_t B = (size_t)num_elements[i] * es;
+        std::vector<uint8_t> masked(B), out(B);
+        int rc = orc_decode_tensor(it.payload.data(), it.payload.size(), it.lanes, it.raw, it.nf, it.cf, B,
+                                   masked.data(), 1);
+        if (spe)
+            orc_merge(masked.data(), it.sidecar.data(), num_elements[i], es, spe, out.data());
+        else
+            out.swap(masked);
+        if (rc != 0 || std::memcmp(out.data(), data[i], B) != 0) bad += 1;
+    }
+    const double t2 = now();
+    seconds_out[0] = t1 - t0;
+    seconds_out[1] = t2 - t1;
+    bytes_out[0] = orig;
+    bytes_out[1] = pay;
+    bytes_out[2] = side;
+    return bad ? -1 : 0;
+}
+
 }  // extern "C"

@@ -126,6 +126,15 @@ int64_t orc_load_tensor(const char* dir, int rank, const char* name, uint8_t* ou
  * copied into names_out (n_cap * 256 bytes) when non-NULL. */
 int64_t orc_list_tensors(const char* dir, int rank, char* names_out, size_t n_cap);
 
+/* Timed CPU baseline: the whole hot path over n host tensors with `n_threads`
+ * OpenMP threads, one tensor per thread at a time (split, histogram, table,
+ * 256 lanes, compaction; then decode and merge, checked against the input).
+ * seconds_out[0] = compress, [1] = decompress; bytes_out[0] = original bytes,
+ * [1] = payload bytes, [2] = sidecar bytes.  Returns 0, or -1 if a round trip
+ * did not reproduce its input. */
+int orc_roundtrip_timed(size_t n, const void* const* data, const uint64_t* num_elements, const uint8_t* dtypes,
+                        int n_threads, double seconds_out[2], uint64_t bytes_out[3]);
+
 #ifdef __cplusplus
 }
 #endif

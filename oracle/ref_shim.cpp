@@ -238,7 +238,7 @@ void ref_byte_histogram(const uint8_t* data, size_t n, uint32_t hist[256]) {
 // therefore built inside a padded arena so the stray writes stay in memory this
 // harness owns.
 struct PaddedTable {
-    alignas(64) unsigned char room[sizeof(ANSFreqTable) + (1 << 16)];
+    alignas(64) unsigned char room[sizeof(ANSFreqTable) + (8 << 20)];
 };
 
 uint32_t ref_normalize(const uint32_t hist[256], int full, uint32_t nf[256], uint32_t cf[257], uint32_t xm[256]) {

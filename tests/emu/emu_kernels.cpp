@@ -1,0 +1,140 @@
+// emu_kernels.cpp -- the library's kernel source run on the CPU block emulator.
+// Test-only: lets the CPU suite check every kernel's index arithmetic against
+// the oracle.  Build: g++ -std=c++17 -O1 -I checkers_b200/csrc -shared -fPIC.
+#include "cuda_emu.hpp"
+//
+#include "kernels.cuh"
+#include "tables.hpp"
+
+#include <vector>
+
+using namespace chk;
+
+namespace {
+struct Batch {
+    std::vector<TensorDesc> descs;
+    std::vector<uint32_t> tile_start;
+    unsigned long long sidecar_total = 0, scratch_total = 0, bytes_total = 0;
+};
+
+Batch make_batch(size_t n, const uint8_t* const* srcs, uint8_t* const* dsts, const uint64_t* n_bytes,
+                 const uint32_t* es, const uint32_t* spe, const uint32_t* table_idx, const uint8_t* need_hist) {
+    Batch b;
+    b.descs.resize(n);
+    b.tile_start.resize(n + 1);
+    b.tile_start[0] = 0;
+    for (size_t i = 0; i < n; ++i) {
+        TensorDesc& d = b.descs[i];
+        std::memset(&d, 0, sizeof(d));
+        d.src = srcs ? srcs[i] : nullptr;
+        d.dst = dsts ? dsts[i] : nullptr;
+        d.n_bytes = n_bytes[i];
+        d.es = es[i];
+        d.spe = spe[i];
+        d.table_idx = table_idx ? table_idx[i] : (uint32_t)i;
+        d.sidecar_off = b.sidecar_total;
+        d.scratch_off = b.scratch_total;
+        const unsigned long long c_max = (d.n_bytes + 255) / 256;
+        d.chunk_stride = (uint32_t)((2 * c_max + 15) & ~15ull);
+        d.flags = 0;
+        if (!need_hist || need_hist[i]) d.flags |= kFlagNeedHist;
+        const uintptr_t p = (uintptr_t)(srcs ? (const void*)srcs[i] : (const void*)dsts[i]);
+        if ((p & 15) == 0 && (d.sidecar_off & 15) == 0) d.flags |= kFlagAligned;
+        b.sidecar_total += (d.n_bytes / d.es) * d.spe;
+        b.scratch_total += 256ull * d.chunk_stride;
+        b.bytes_total += d.n_bytes;
+        b.tile_start[i + 1] = b.tile_start[i] + (uint32_t)((d.n_bytes + kSplitTileBytes - 1) / kSplitTileBytes);
+    }
+    return b;
+}
+}  // namespace
+
+extern "C" {
+
+void emu_split(const uint8_t* src, uint64_t n_bytes, uint32_t es, uint32_t spe, uint8_t* masked, uint8_t* sidecar,
+               uint32_t grid) {
+    const uint32_t vec = ((uintptr_t)src & 15) == 0 && ((uintptr_t)masked & 15) == 0 && ((uintptr_t)sidecar & 15) == 0;
+    emu::launch(grid, 256, 0, [&] { split_kernel(src, n_bytes, es, spe, masked, sidecar, vec); });
+}
+
+void emu_byte_histogram(const uint8_t* data, uint64_t n, uint32_t* hist, uint32_t grid) {
+    std::memset(hist, 0, 1024);
+    emu::launch(grid, 256, 0, [&] { byte_histogram_kernel(data, n, hist); });
+}
+
+// sidecar_out: concatenated low bytes; hist_out: n*256 counters (without the zeroed bytes)
+void emu_split_hist(size_t n, const uint8_t* const* srcs, const uint64_t* n_bytes, const uint32_t* es,
+                    const uint32_t* spe, const uint8_t* need_hist, uint8_t* sidecar_out, uint32_t* hist_out,
+                    uint32_t grid) {
+    Batch b = make_batch(n, srcs, nullptr, n_bytes, es, spe, nullptr, need_hist);
+    std::memset(hist_out, 0, n * 1024);
+    const uint32_t total = b.tile_start[n];
+    emu::launch(grid, 256, 0, [&] {
+        split_hist_kernel(b.descs.data(), b.tile_start.data(), (uint32_t)n, total, sidecar_out, hist_out);
+    });
+}
+
+// Full encode: lanes -> lane scan -> tensor scan -> compaction.
+// payload_off_out has n+1 entries; hdrs_out n*1024 words; raw_out n bytes.
+uint32_t emu_encode(size_t n, const uint8_t* const* srcs, const uint64_t* n_bytes, const uint32_t* es,
+                    const uint32_t* spe, const uint32_t* table_idx, size_t n_tables, const uint32_t* nf,
+                    const uint32_t* cf, uint8_t* payload_out, uint64_t* payload_off_out, uint32_t* hdrs_out,
+                    uint8_t* raw_out, uint32_t grid) {
+    Batch b = make_batch(n, srcs, nullptr, n_bytes, es, spe, table_idx, nullptr);
+    std::vector<EncEntry> enc(n_tables * 256);
+    for (size_t t = 0; t < n_tables; ++t) {
+        FreqTable ft;
+        std::memcpy(ft.norm_freq, nf + t * 256, 1024);
+        std::memcpy(ft.cum_freq, cf + t * 257, 1028);
+        build_enc_entries(ft, &enc[t * 256]);
+    }
+    std::vector<uint8_t> scratch(b.scratch_total + 64, 0xAA);
+    // keep lane regions 16-byte aligned like the device allocation
+    uint8_t* scr = (uint8_t*)(((uintptr_t)scratch.data() + 15) & ~(uintptr_t)15);
+    std::vector<LaneHeader> hdrs(n * 256);
+    std::vector<uint32_t> wpos(n * 256), loff(n * 256);
+    std::vector<unsigned long long> psize(n), poff(n + 1);
+    uint32_t status = 0;
+    emu::launch(grid, 256, kEncSmemBytes, [&] {
+        rans_encode_kernel(b.descs.data(), enc.data(), scr, hdrs.data(), wpos.data(), (uint32_t)n, &status);
+    });
+    emu::launch(grid, 256, 0, [&] { lane_scan_kernel(b.descs.data(), hdrs.data(), psize.data(), loff.data(), (uint32_t)n); });
+    emu::launch(1, 1024, 0, [&] { tensor_scan_kernel(b.descs.data(), psize.data(), poff.data(), (uint32_t)n); });
+    emu::launch(grid, 256, 0, [&] {
+        compact_kernel(b.descs.data(), hdrs.data(), wpos.data(), loff.data(), scr, payload_out, (uint32_t)n);
+    });
+    for (size_t i = 0; i <= n; ++i) payload_off_out[i] = poff[i];
+    std::memcpy(hdrs_out, hdrs.data(), n * 4096);
+    for (size_t i = 0; i < n; ++i) raw_out[i] = (b.descs[i].flags & kFlagRaw) ? 1 : 0;
+    return status;
+}
+
+// payload must be readable 64 bytes past its end and 16-byte aligned.
+void emu_decode(size_t n, uint8_t* const* dsts, const uint64_t* n_bytes, const uint32_t* es, const uint32_t* spe,
+                const uint32_t* table_idx, const uint32_t* nf, const uint32_t* cf, const uint32_t* hdrs,
+                const uint8_t* payload, const uint64_t* payload_off, const uint8_t* raw, const uint8_t* sidecar,
+                uint32_t check_zero_lanes, uint32_t* status_out, uint32_t grid) {
+    Batch b = make_batch(n, nullptr, dsts, n_bytes, es, spe, table_idx, nullptr);
+    for (size_t i = 0; i < n; ++i) {
+        b.descs[i].payload_off = payload_off[i];
+        if (raw[i]) b.descs[i].flags |= kFlagRaw;
+    }
+    std::memset(status_out, 0, n * 4);
+    emu::launch(grid, 256, kDecSmemBytes, [&] {
+        rans_decode_kernel(b.descs.data(), nf, cf, (const LaneHeader*)hdrs, payload, sidecar, (uint32_t)n,
+                           check_zero_lanes, status_out);
+    });
+}
+
+// outs: n * sizeof(StatsOut)/4 words
+void emu_stats(size_t n, const void* const* ptrs, const uint64_t* n_elem, const uint32_t* dtype, uint32_t bins,
+               void* outs, uint32_t grid) {
+    std::vector<StatsDesc> d(n);
+    for (size_t i = 0; i < n; ++i) d[i] = StatsDesc{ptrs[i], n_elem[i], dtype[i], bins};
+    std::memset(outs, 0, n * sizeof(StatsOut));
+    emu::launch(grid, 256, 0, [&] { tensor_stats_kernel(d.data(), (StatsOut*)outs, (uint32_t)n); });
+}
+
+uint32_t emu_stats_out_bytes() { return (uint32_t)sizeof(StatsOut); }
+
+}  // extern "C"

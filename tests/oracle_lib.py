@@ -146,6 +146,22 @@ class Oracle:
         if rc != 0:
             raise RuntimeError(f"orc_compress_and_save rc={rc}")
 
+    def roundtrip_timed(self, arrays, dtypes, threads=0):
+        """CPU baseline leg: returns (compress_s, decompress_s, original, payload, sidecar bytes)."""
+        n = len(arrays)
+        keep = [_u8(a) for a in arrays]
+        ptrs = (C.c_void_p * n)(*[a.ctypes.data for a in keep])
+        ne = np.array([a.size // ELEM_SIZE[d] for a, d in zip(keep, dtypes)], np.uint64)
+        dt = np.array(dtypes, np.uint8)
+        secs = (C.c_double * 2)()
+        nbytes = (C.c_uint64 * 3)()
+        self.lib.orc_roundtrip_timed.restype = C.c_int
+        rc = self.lib.orc_roundtrip_timed(C.c_size_t(n), ptrs, _p(ne, C.POINTER(C.c_uint64)), _p(dt), C.c_int(threads),
+                                          secs, nbytes)
+        if rc != 0:
+            raise RuntimeError("oracle round trip did not reproduce its input")
+        return secs[0], secs[1], nbytes[0], nbytes[1], nbytes[2]
+
     def list_tensors(self, d, rank=0):
         n = self.lib.orc_list_tensors(d.encode(), C.c_int(rank), None, C.c_size_t(0))
         if n < 0:

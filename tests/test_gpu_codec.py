@@ -1,0 +1,354 @@
+"""GPU parity tests: the CUDA path, called through the C ABI, against the CPU oracle.
+
+Bit-exact everywhere: integer/byte work, and the float statistics too (the
+kernel keeps the reference's accumulation order and fuses nothing)."""
+import os
+
+import numpy as np
+import pytest
+
+from oracle_lib import (BF16, ELEM_SIZE, F16, F32, I8, I32, SIDECAR_PER_ELEM, UNKNOWN, Oracle, synth)
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+
+
+@pytest.fixture(scope="module")
+def chk():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import checkers_b200
+    return checkers_b200
+
+
+def dev_bytes(arr, misalign=0):
+    """uint8 device tensor holding arr's bytes, optionally starting `misalign` bytes into its allocation."""
+    a = np.ascontiguousarray(arr).view(np.uint8).reshape(-1)
+    buf = torch.zeros(a.size + misalign + 64, dtype=torch.uint8, device="cuda")
+    view = buf[misalign:misalign + a.size]
+    view.copy_(torch.from_numpy(a.copy()))
+    return view
+
+
+def read_files(d, rank=0):
+    out = []
+    for rel in (f"rank_{rank}_states.ansc", f"mantissa/rank_{rank}_mantissa.mant", f"tables/rank_{rank}_tables.dict"):
+        with open(os.path.join(d, rel), "rb") as f:
+            out.append(f.read())
+    return out
+
+
+MIXED = [  # (name, kind, elements, misalign bytes)
+    ("layers.0.w", "bf16_weight", 262144, 0),
+    ("master_weights::layers.0.w", "f32_master", 262144, 0),
+    ("optimizer.exp_avg::layers.0.w", "f32_exp_avg", 262144, 0),
+    ("optimizer.exp_avg_sq::layers.0.w", "f32_exp_avg_sq", 262144, 0),
+    ("layers.0.norm", "bf16_norm_gain", 4096, 0),
+    ("odd.bf16", "bf16_weight", 70001, 0),
+    ("odd.f32", "f32_master", 10001, 0),
+    ("tiny.1", "f32_master", 1, 0),
+    ("tiny.3", "bf16_weight", 3, 0),
+    ("sub256", "i8", 255, 0),
+    ("exact256", "i8", 256, 0),
+    ("plus1", "i8", 257, 0),
+    ("bytes.65537", "i8", 65537, 0),
+    ("int32.t", "i32", 5000, 0),
+    ("half.t", "f16_weight", 33000, 0),
+    ("noise.f32", "f32_uniform_bits", 20000, 0),
+    ("misaligned.f32", "f32_master", 30000, 4),
+    ("misaligned.bf16", "bf16_weight", 30001, 2),
+    ("lognormal", "f32_exp_avg_sq_lognormal", 100000, 0),
+]
+
+
+def make_mixed(seed=0):
+    names, host, dev, dtypes = [], [], [], []
+    for i, (name, kind, n, mis) in enumerate(MIXED):
+        raw, dt = synth(kind, n, seed * 1000 + i)
+        names.append(name)
+        host.append(raw.copy())
+        dev.append(dev_bytes(raw, mis))
+        dtypes.append(dt)
+    return names, host, dev, dtypes
+
+
+def register_all(ctx, names, dev, dtypes):
+    for n, t, dt in zip(names, dev, dtypes):
+        ctx.register_pointer(n, t.data_ptr(), t.numel() // ELEM_SIZE[dt], dt)
+
+
+def test_stage_split_and_histogram(chk, oracle):
+    ctx = chk.Context(device=0)
+    for kind, n in [("bf16_weight", 100003), ("f32_master", 65536), ("f16_weight", 4097)]:
+        raw, dt = synth(kind, n, 7)
+        src = dev_bytes(raw)
+        masked = torch.zeros(raw.size + 64, dtype=torch.uint8, device="cuda")
+        side = torch.zeros(n * SIDECAR_PER_ELEM[dt] + 64, dtype=torch.uint8, device="cuda")
+        ctx.split(src.data_ptr(), n, dt, masked.data_ptr(), side.data_ptr())
+        m_ref, s_ref = oracle.split(raw, dt)
+        assert np.array_equal(masked[:raw.size].cpu().numpy(), m_ref)
+        assert np.array_equal(side[:s_ref.size].cpu().numpy(), s_ref)
+        h = ctx.byte_histogram(masked.data_ptr(), raw.size)
+        assert np.array_equal(h, oracle.byte_histogram(m_ref))
+        # misaligned source for the histogram
+        h2 = ctx.byte_histogram(masked.data_ptr() + 3, raw.size - 3)
+        assert np.array_equal(h2, oracle.byte_histogram(m_ref[3:]))
+    ctx.close()
+
+
+def test_normalize_matches_oracle(chk, oracle):
+    rng = np.random.default_rng(3)
+    for trial in range(200):
+        k = int(rng.integers(1, 257))
+        hist = np.zeros(256, np.uint32)
+        idx = rng.choice(256, k, replace=False)
+        hist[idx] = rng.integers(1, 10 ** int(rng.integers(1, 7)), k)
+        for full in (False, True):
+            for rep in (False, True):
+                a = chk.normalize_histogram(hist, full, rep)
+                b = oracle.normalize(hist, full, repaired=rep)
+                assert all(np.array_equal(x, y) for x, y in zip(a[:3], b[:3])) and a[3] == b[3]
+
+
+def test_files_identical_to_oracle_singletons(chk, oracle, tmp_path):
+    names, host, dev, dtypes = make_mixed()
+    # entries the reference drops: null pointer, zero elements, unknown dtype
+    ctx = chk.Context(device=0, rank=3)
+    ctx.register_pointer("null.ptr", 0, 100, F32)
+    register_all(ctx, names, dev, dtypes)
+    ctx.register_pointer("zero.elems", dev[0].data_ptr(), 0, F32)
+    ctx.register_pointer("unknown.dtype", dev[0].data_ptr(), 16, UNKNOWN)
+    out_gpu, out_cpu = str(tmp_path / "gpu"), str(tmp_path / "cpu")
+    ctx.compress_and_save(out_gpu)
+    oracle.compress_and_save(["null.ptr"] + names + ["zero.elems", "unknown.dtype"],
+                             [None] + host + [np.zeros(0, np.uint8), host[0][:16]],
+                             [F32] + dtypes + [F32, UNKNOWN], out_cpu, rank=3)
+    for a, b, what in zip(read_files(out_gpu, 3), read_files(out_cpu, 3), ("states", "mantissa", "tables")):
+        assert a == b, f"{what} file differs from the oracle's"
+    s = ctx.summary()
+    assert s["n_tensors"] == len(names) and s["states_bytes"] == len(read_files(out_gpu, 3)[0])
+
+    # restore into fresh buffers through the files
+    ctx2 = chk.Context(device=0, rank=3)
+    outs = [torch.zeros(t.numel() + 64, dtype=torch.uint8, device="cuda") for t in dev]
+    for n, o, t, dt in zip(names, outs, dev, dtypes):
+        ctx2.register_pointer(n, o.data_ptr(), t.numel() // ELEM_SIZE[dt], dt)
+    ctx2.set_option("verify_zero_lanes", 1)
+    assert ctx2.load_and_decompress(out_gpu) == len(names)
+    for o, h, n in zip(outs, host, names):
+        assert np.array_equal(o[:h.size].cpu().numpy(), h), n
+        assert int(o[h.size:].sum()) == 0, f"{n}: wrote past the tensor"
+    # and the oracle's reader accepts the GPU-written files
+    for n, h in zip(names, host):
+        assert np.array_equal(oracle.load_tensor(out_gpu, n, h.size, rank=3), h), n
+    ctx.close()
+    ctx2.close()
+
+
+def test_restore_misaligned_targets(chk, oracle, tmp_path):
+    names, host, dev, dtypes = make_mixed(seed=2)
+    out_cpu = str(tmp_path / "cpu")
+    oracle.compress_and_save(names, host, dtypes, out_cpu, rank=0)  # files written by the oracle
+    ctx = chk.Context(device=0, rank=0)
+    outs = []
+    for k, (n, h, dt) in enumerate(zip(names, host, dtypes)):
+        mis = (k % 4) * ELEM_SIZE[dt]
+        buf = torch.zeros(h.size + mis + 64, dtype=torch.uint8, device="cuda")
+        outs.append((buf, mis))
+        ctx.register_pointer(n, buf.data_ptr() + mis, h.size // ELEM_SIZE[dt], dt)
+    assert ctx.load_and_decompress(out_cpu) == len(names)
+    for (buf, mis), h, n in zip(outs, host, names):
+        got = buf.cpu().numpy()
+        assert np.array_equal(got[mis:mis + h.size], h), n
+        assert got[:mis].sum() == 0 and got[mis + h.size:].sum() == 0, f"{n}: wrote outside the tensor"
+    ctx.close()
+
+
+def _cluster_setup(oracle, names, host, dtypes):
+    fps = []
+    for h, dt in zip(host, dtypes):
+        _, mom, mm = oracle.tensor_stats(h, dt)
+        fps.append([mom[0], mom[1], mom[2], mom[3], np.float32(mm[1] - mm[0])])
+    cid, anchors = oracle.build_clusters(names, np.array(fps, np.float32))
+    return cid, [names[a] for a in anchors]
+
+
+def make_state(n_layers=6, n=32768, seed=11):
+    names, host, dtypes = [], [], []
+    for l in range(n_layers):
+        p = f"model.layers.{l}.mlp.weight"
+        for prefix, kind in (("", "bf16_weight"), ("master_weights::", "f32_master"),
+                             ("optimizer.exp_avg::", "f32_exp_avg"), ("optimizer.exp_avg_sq::", "f32_exp_avg_sq")):
+            raw, dt = synth(kind, n + 17 * l if l % 2 else n, seed * 100 + len(names))
+            names.append(prefix + p)
+            host.append(raw.copy())
+            dtypes.append(dt)
+    return names, host, dtypes
+
+
+@pytest.mark.parametrize("repair", [False, True])
+def test_files_identical_with_clusters(chk, oracle, tmp_path, repair):
+    names, host, dtypes = make_state()
+    dev = [dev_bytes(h) for h in host]
+    cid, anchors = _cluster_setup(oracle, names, host, dtypes)
+    assert len(anchors) >= 1, "test data should produce at least one cluster"
+    ctx = chk.Context(device=0, rank=1)
+    register_all(ctx, names, dev, dtypes)
+    ctx.set_cluster_info(names, cid, anchors)
+    ctx.set_option("repair_tables", int(repair))
+    out_gpu, out_cpu = str(tmp_path / "gpu"), str(tmp_path / "cpu")
+    ctx.compress_and_save(out_gpu)
+    oracle.compress_and_save(names, host, dtypes, out_cpu, rank=1, cluster_id=cid, anchor_names=anchors,
+                             repair_tables=repair)
+    for a, b, what in zip(read_files(out_gpu, 1), read_files(out_cpu, 1), ("states", "mantissa", "tables")):
+        assert a == b, f"{what} file differs from the oracle's (repair={repair})"
+    outs = [torch.zeros(h.size, dtype=torch.uint8, device="cuda") for h in host]
+    ctx2 = chk.Context(device=0, rank=1)
+    for n, o, h, dt in zip(names, outs, host, dtypes):
+        ctx2.register_pointer(n, o.data_ptr(), h.size // ELEM_SIZE[dt], dt)
+    if repair:
+        assert ctx2.load_and_decompress(out_gpu) == len(names)
+        for o, h, n in zip(outs, host, names):
+            assert np.array_equal(o.cpu().numpy(), h), n
+    else:
+        # The reference's shared tables for bf16 data do not sum to 4096: such
+        # streams are written identically but refused by the reader.
+        dict_bytes = read_files(out_gpu, 1)[2]
+        n_tab = int(np.frombuffer(dict_bytes[12:16], np.uint32)[0])
+        sums = [int(np.frombuffer(dict_bytes[16 + i * 2308 + 1280 + 1024:16 + i * 2308 + 1284 + 1024], np.uint32)[0])
+                for i in range(n_tab)]
+        if any(s != 4096 for s in sums):
+            with pytest.raises(chk.CheckersError) as ei:
+                ctx2.load_and_decompress(out_gpu)
+            assert ei.value.code == -4
+        else:
+            assert ctx2.load_and_decompress(out_gpu) == len(names)
+    ctx.close()
+    ctx2.close()
+
+
+def test_analysis_matches_oracle(chk, oracle):
+    names, host, dtypes = make_state(n_layers=5, n=20000, seed=5)
+    names += ["ints.i8", "ints.i32", "half"]
+    for kind in ("i8", "i32", "f16_weight"):
+        raw, dt = synth(kind, 9999, 77)
+        host.append(raw.copy())
+        dtypes.append(dt)
+    dev = [dev_bytes(h) for h in host]
+    ctx = chk.Context(device=0)
+    register_all(ctx, names, dev, dtypes)
+    ctx.analyze()
+    fps = []
+    for i, (h, dt) in enumerate(zip(host, dtypes)):
+        hist, mom, mm, fp = ctx.tensor_stats(i)
+        h_ref, mom_ref, mm_ref = oracle.tensor_stats(h, dt)
+        assert np.array_equal(hist, h_ref), names[i]
+        assert np.array_equal(mom.view(np.uint32), mom_ref.view(np.uint32)), (names[i], mom, mom_ref)
+        assert np.array_equal(mm.view(np.uint32), mm_ref.view(np.uint32)), names[i]
+        fps.append(fp)
+    cid_ref, anchors_ref = oracle.build_clusters(names, np.array(fps, np.float32))
+    cid, k = ctx.cluster_ids()
+    assert np.array_equal(cid, cid_ref) and k == len(anchors_ref)
+    for c in range(k):
+        assert ctx.cluster_anchor(c) == names[anchors_ref[c]]
+    # histogram_bins below 256 narrows the value histogram
+    ctx.set_histogram_bins(64)
+    ctx.analyze()
+    hist, _, _, _ = ctx.tensor_stats(0)
+    h_ref, _, _ = oracle.tensor_stats(host[0], dtypes[0], bins=64)
+    assert np.array_equal(hist, h_ref)
+    ctx.close()
+
+
+def test_config0_three_tensors_split_in_64(chk, oracle, tmp_path):
+    """The reference-scale CPU case: 3 x 16 Mi elements, each cut into 64 tensors of 256 Ki."""
+    per, parts = 262144, 64
+    kinds = [("w.{}", "bf16_weight"), ("optimizer.exp_avg::w.{}", "f32_exp_avg"),
+             ("optimizer.exp_avg_sq::w.{}", "f32_exp_avg_sq")]
+    names, host, dtypes = [], [], []
+    for fmt, kind in kinds:
+        raw, dt = synth(kind, per * parts, 0)
+        es = ELEM_SIZE[dt]
+        for i in range(parts):
+            names.append(fmt.format(i))
+            host.append(raw[i * per * es:(i + 1) * per * es].copy())
+            dtypes.append(dt)
+    dev = [dev_bytes(h) for h in host]
+    ctx = chk.Context(device=0)
+    register_all(ctx, names, dev, dtypes)
+    out_gpu, out_cpu = str(tmp_path / "gpu"), str(tmp_path / "cpu")
+    ctx.compress_and_save(out_gpu)
+    oracle.compress_and_save(names, host, dtypes, out_cpu)
+    for a, b, what in zip(read_files(out_gpu), read_files(out_cpu), ("states", "mantissa", "tables")):
+        assert a == b, f"{what} file differs from the oracle's"
+    # device-resident round trip into separate buffers
+    ctx.compress(host_images=False)
+    outs = [torch.zeros(h.size, dtype=torch.uint8, device="cuda") for h in host]
+    assert ctx.decompress_resident([o.data_ptr() for o in outs]) == len(names)
+    for o, d in zip(outs, dev):
+        assert torch.equal(o, d)
+    # in-memory images equal the files
+    ctx.compress(host_images=True)
+    for k, b in enumerate(read_files(out_gpu)):
+        assert ctx.image(k).tobytes() == b
+    ctx.close()
+
+
+def test_error_paths(chk, tmp_path):
+    ctx = chk.Context(device=0)
+    with pytest.raises(chk.CheckersError):
+        ctx.decompress_resident()  # nothing compressed yet
+    with pytest.raises(chk.CheckersError):
+        ctx.load_and_decompress(str(tmp_path / "missing"))
+    with pytest.raises(chk.CheckersError):
+        ctx.set_option("no_such_option", 1)
+    # empty registry: directories only, no files
+    out = str(tmp_path / "empty")
+    ctx.compress_and_save(out)
+    assert os.path.isdir(os.path.join(out, "mantissa")) and not os.path.exists(os.path.join(out, "rank_0_states.ansc"))
+    # corrupted file
+    raw, dt = synth("f32_master", 5000, 1)
+    t = dev_bytes(raw)
+    ctx.register_pointer("a", t.data_ptr(), 5000, dt)
+    good = str(tmp_path / "good")
+    ctx.compress_and_save(good)
+    p = os.path.join(good, "rank_0_states.ansc")
+    data = bytearray(open(p, "rb").read())
+    data[0] ^= 0xFF
+    open(p, "wb").write(bytes(data))
+    with pytest.raises(chk.CheckersError) as ei:
+        ctx.load_and_decompress(good)
+    assert ei.value.code == -4
+    data[0] ^= 0xFF
+    # flip a payload byte: the lane's end-state / length check must catch it
+    data[-100] ^= 0x55
+    open(p, "wb").write(bytes(data))
+    try:
+        ctx.load_and_decompress(good)
+        changed = not np.array_equal(t.cpu().numpy(), raw)
+        assert changed, "a corrupted payload decoded to the original bytes"
+    except chk.CheckersError as e:
+        assert e.code == -5
+    ctx.close()
+
+
+def test_front_end_api(chk, oracle, tmp_path):
+    names, host, dtypes = make_state(n_layers=2, n=8192, seed=9)
+    tensors = {}
+    for n, h, dt in zip(names, host, dtypes):
+        t = torch.from_numpy(h.copy()).cuda()
+        tensors[n] = t.view(torch.bfloat16) if dt == BF16 else t.view(torch.float32)
+    with pytest.raises(RuntimeError):
+        chk.initialize_context(tensors, histogram_bins=0)
+    chk.initialize_context(tensors, None, 256, 1)
+    chk.analyze_tensors()
+    out = str(tmp_path / "out")
+    chk.compress_and_save(out)
+    ctx = chk.current_context()
+    cid, k = ctx.cluster_ids()
+    anchors = [ctx.cluster_anchor(c) for c in range(k)]
+    out_cpu = str(tmp_path / "cpu")
+    oracle.compress_and_save(names, host, dtypes, out_cpu, cluster_id=cid, anchor_names=anchors)
+    for a, b in zip(read_files(out), read_files(out_cpu)):
+        assert a == b
