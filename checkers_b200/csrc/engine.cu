@@ -117,7 +117,7 @@ struct Context {
     int host_threads = 0;
 
     // device buffers (grow-only, from the context's pool)
-    DevBuf d_descs, d_tiles, d_hist, d_sidecar, d_scratch, d_hdrs, d_wpos, d_loff, d_psize, d_poff, d_payload, d_enc,
+    DevBuf d_descs, d_tiles, d_hist, d_sidecar, d_scratch, d_hdrs, d_lsrc, d_zrec, d_loff, d_psize, d_poff, d_payload, d_enc,
         d_freq, d_cum, d_status, d_stats_desc, d_stats_out;
     // pinned host staging
     PinBuf h_hist, h_hdrs, h_poff, h_descs, h_status, h_enc, h_stats;
@@ -297,7 +297,8 @@ static void compress(Context* c, bool host_images) {
         d.flags = w.owns ? kFlagNeedHist : 0u;
         if ((reinterpret_cast<uintptr_t>(d.src) & 15) == 0 && (sidecar_total & 15) == 0) d.flags |= kFlagAligned;
         sidecar_total += (unsigned long long)c->tensors[w.idx].n_elem * w.spe;
-        scratch_total += 256ull * d.chunk_stride;
+        // value-lane regions, plus one shared region for the lanes that only see zeroed bytes
+        scratch_total += (w.spe * 2 == w.es ? 129ull : 256ull) * d.chunk_stride;
         bytes_total += w.bytes;
         n_sidecars += w.spe > 0;
         tile_start[i + 1] = tile_start[i] + (uint32_t)((w.bytes + kSplitTileBytes - 1) / kSplitTileBytes);
@@ -329,7 +330,8 @@ static void compress(Context* c, bool host_images) {
     dev_ensure(c, c->d_sidecar, sidecar_total + 64);
     dev_ensure(c, c->d_scratch, scratch_total + 64);
     dev_ensure(c, c->d_hdrs, W * 4096);
-    dev_ensure(c, c->d_wpos, W * 1024);
+    dev_ensure(c, c->d_lsrc, W * 2048);
+    dev_ensure(c, c->d_zrec, W * sizeof(ZeroRec));
     dev_ensure(c, c->d_loff, W * 1024);
     dev_ensure(c, c->d_psize, W * 8);
     dev_ensure(c, c->d_poff, (W + 1) * 8);
@@ -350,7 +352,6 @@ static void compress(Context* c, bool host_images) {
     CHK_CUDA(cudaMemcpyAsync(c->d_descs.p, c->h_descs.p, W * sizeof(TensorDesc), cudaMemcpyHostToDevice, s));
     CHK_CUDA(cudaMemcpyAsync(c->d_tiles.p, tile_start.data(), (W + 1) * 4, cudaMemcpyHostToDevice, s));
     CHK_CUDA(cudaMemsetAsync(c->d_hist.p, 0, W * 1024, s));
-    CHK_CUDA(cudaMemsetAsync(c->d_status.p, 0, 256, s));
 
     // ---- stage 1: low bytes out, histograms
     {
@@ -406,13 +407,18 @@ static void compress(Context* c, bool host_images) {
                                           (int)kEncSmemBytes));
             c->enc_attr_set = true;
         }
-        const uint32_t grid = (uint32_t)(W < 148u * 64u ? W : 148u * 64u);
-        rans_encode_kernel<<<grid, 256, kEncSmemBytes, s>>>(
+        // the shared symbol-0 chain of every tensor first (one thread each), then the value lanes
+        zero_lane_kernel<<<(uint32_t)((W + 127) / 128), 128, 0, s>>>(
+            static_cast<const TensorDesc*>(c->d_descs.p), static_cast<const EncEntry*>(c->d_enc.p),
+            static_cast<uint8_t*>(c->d_scratch.p), static_cast<ZeroRec*>(c->d_zrec.p), (uint32_t)W);
+        CHK_CUDA(cudaGetLastError());
+        const uint32_t grid = (uint32_t)(W < 148u * 256u ? W : 148u * 256u);
+        rans_encode_kernel<<<grid, kTeam, kEncSmemBytes, s>>>(
             static_cast<const TensorDesc*>(c->d_descs.p), static_cast<const EncEntry*>(c->d_enc.p),
             static_cast<uint8_t*>(c->d_scratch.p), static_cast<LaneHeader*>(c->d_hdrs.p),
-            static_cast<uint32_t*>(c->d_wpos.p), (uint32_t)W, static_cast<uint32_t*>(c->d_status.p));
+            static_cast<unsigned long long*>(c->d_lsrc.p), static_cast<const ZeroRec*>(c->d_zrec.p), (uint32_t)W);
         CHK_CUDA(cudaGetLastError());
-        c->launches++;
+        c->launches += 2;
     }
     CHK_CUDA(cudaEventRecord(c->ev[3], s));
 
@@ -433,7 +439,7 @@ static void compress(Context* c, bool host_images) {
         const uint32_t g3 = (uint32_t)(blocks < 148ull * 16 ? blocks : 148ull * 16);
         compact_kernel<<<g3, 256, 0, s>>>(static_cast<const TensorDesc*>(c->d_descs.p),
                                           static_cast<const LaneHeader*>(c->d_hdrs.p),
-                                          static_cast<const uint32_t*>(c->d_wpos.p),
+                                          static_cast<const unsigned long long*>(c->d_lsrc.p),
                                           static_cast<const uint32_t*>(c->d_loff.p),
                                           static_cast<const uint8_t*>(c->d_scratch.p),
                                           static_cast<uint8_t*>(c->d_payload.p), (uint32_t)W);
@@ -443,7 +449,6 @@ static void compress(Context* c, bool host_images) {
     CHK_CUDA(cudaEventRecord(c->ev[4], s));
     CHK_CUDA(cudaMemcpyAsync(c->h_poff.p, c->d_poff.p, (W + 1) * 8, cudaMemcpyDeviceToHost, s));
     CHK_CUDA(cudaMemcpyAsync(c->h_descs.p, c->d_descs.p, W * sizeof(TensorDesc), cudaMemcpyDeviceToHost, s));
-    CHK_CUDA(cudaMemcpyAsync(c->h_status.p, c->d_status.p, 4, cudaMemcpyDeviceToHost, s));
     if (host_images)
         CHK_CUDA(cudaMemcpyAsync(c->h_hdrs.p, c->d_hdrs.p, W * 4096, cudaMemcpyDeviceToHost, s));
     CHK_CUDA(cudaStreamSynchronize(s));
@@ -453,9 +458,6 @@ static void compress(Context* c, bool host_images) {
     c->timing["compact_ms"] = ms_between(c->ev[3], c->ev[4]);
     c->timing["compress_device_ms"] =
         c->timing["split_hist_ms"] + c->timing["encode_ms"] + c->timing["compact_ms"];
-
-    if (*static_cast<const uint32_t*>(c->h_status.p) & kErrBarrierTimeout)
-        throw Error{CHK_ERR_TIMEOUT, "encode: an asynchronous tile copy did not complete"};
 
     std::memcpy(c->descs.data(), c->h_descs.p, W * sizeof(TensorDesc));
     const unsigned long long* poff = static_cast<const unsigned long long*>(c->h_poff.p);
@@ -592,8 +594,8 @@ static void run_decode(Context* c, size_t W, const uint8_t* d_payload, const uin
         c->dec_attr_set = true;
     }
     CHK_CUDA(cudaEventRecord(c->ev[1], s));
-    const uint32_t grid = (uint32_t)(W < 148u * 64u ? W : 148u * 64u);
-    rans_decode_kernel<<<grid, 256, kDecSmemBytes, s>>>(static_cast<const TensorDesc*>(c->d_descs.p), d_freq, d_cum,
+    const uint32_t grid = (uint32_t)(W < 148u * 256u ? W : 148u * 256u);
+    rans_decode_kernel<<<grid, kTeam, kDecSmemBytes, s>>>(static_cast<const TensorDesc*>(c->d_descs.p), d_freq, d_cum,
                                                         d_hdrs, d_payload, d_sidecar, (uint32_t)W,
                                                         c->verify_zero_lanes ? 1u : 0u,
                                                         static_cast<uint32_t*>(c->d_status.p));
@@ -908,7 +910,7 @@ int chk_context_destroy(chk_context* c) {
     cudaSetDevice(c->device);
     if (c->stream) cudaStreamSynchronize(c->stream);
     DevBuf* bufs[] = {&c->d_descs, &c->d_tiles, &c->d_hist, &c->d_sidecar, &c->d_scratch, &c->d_hdrs,
-                      &c->d_wpos, &c->d_loff, &c->d_psize, &c->d_poff, &c->d_payload, &c->d_enc,
+                      &c->d_lsrc, &c->d_zrec, &c->d_loff, &c->d_psize, &c->d_poff, &c->d_payload, &c->d_enc,
                       &c->d_freq, &c->d_cum, &c->d_status, &c->d_stats_desc, &c->d_stats_out};
     for (DevBuf* b : bufs)
         if (b->p) cudaFreeAsync(b->p, c->stream);

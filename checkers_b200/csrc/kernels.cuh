@@ -366,448 +366,11 @@ __global__ void __launch_bounds__(256) byte_histogram_kernel(const uint8_t* __re
     if (s) atomicAdd(&hist[tid], s);
 }
 
-// ------------------------------------------------------------------ rANS encode
-constexpr uint32_t kEncRows = 64;                      // rows of 256 bytes per input tile
-constexpr uint32_t kEncTileBytes = kEncRows * kLanes;  // 16 KiB
-// dynamic shared memory: 2 input tiles | 32-byte output ring per lane (word-interleaved) | table | 2 barriers
-constexpr uint32_t kEncSmemBytes = 2 * kEncTileBytes + 8 * kLanes * 4 + 256 * 16 + 16;
+}  // namespace chk
 
-// One CTA per tensor, one thread per lane.  Lane t encodes bytes t, t+256, ...
-// last to first (zeroed low bytes are never read: such lanes encode symbol 0).
-// Emitted bytes go backward through a 32-byte ring in shared memory and leave
-// for the lane's scratch region in aligned 16-byte stores; the byte sequence
-// and count per lane equal the reference kernel's.
-__global__ void __launch_bounds__(256) rans_encode_kernel(const TensorDesc* __restrict__ descs,
-                                                          const EncEntry* __restrict__ tables,
-                                                          uint8_t* __restrict__ scratch,
-                                                          LaneHeader* __restrict__ hdrs,
-                                                          uint32_t* __restrict__ lane_wpos, uint32_t n_tensors,
-                                                          uint32_t* __restrict__ status) {
-    CHK_DYN_SMEM(smem);
-    uint8_t* tile0 = smem;
-    uint8_t* ring = smem + 2 * kEncTileBytes;
-    uint4* tab = reinterpret_cast<uint4*>(ring + 8 * kLanes * 4);
-    unsigned long long* bars = reinterpret_cast<unsigned long long*>(tab + 256);
-    const uint32_t t = threadIdx.x;
+#include "rans_kernels.cuh"
 
-    if (t == 0) {
-        tile_barrier_init(&bars[0]);
-        tile_barrier_init(&bars[1]);
-    }
-    uint32_t phase0 = 0, phase1 = 0;  // parity to wait for on each barrier
-    __syncthreads();
-
-    for (uint32_t ti = blockIdx.x; ti < n_tensors; ti += gridDim.x) {
-        const TensorDesc d = descs[ti];
-        const unsigned long long B = d.n_bytes;
-        const bool vec = (d.flags & kFlagAligned) != 0;
-        const bool zero_lane = (t % d.es) < d.spe;
-        const unsigned long long c_max = (B + kLanes - 1) / kLanes;
-        const unsigned long long my_count = B > t ? (B - t + kLanes - 1) / kLanes : 0;
-        const uint32_t n_tiles = (uint32_t)((c_max + kEncRows - 1) / kEncRows);
-        uint8_t* const region = scratch + d.scratch_off + (size_t)t * d.chunk_stride;
-
-        {
-            const EncEntry e = tables[(size_t)d.table_idx * 256 + t];
-            tab[t] = make_uint4(e.rcp, e.freq_shift, e.bias, e.cmpl);
-        }
-
-        // Tile j holds tensor bytes [j*16K, j*16K + nb).  The 16-byte-aligned part
-        // arrives through the bulk copy; a ragged tail or a misaligned tensor is
-        // fetched with plain loads.
-        auto issue = [&](uint32_t j, uint32_t buf) {
-            const unsigned long long off = (unsigned long long)j * kEncTileBytes;
-            const uint32_t nb = (uint32_t)((B - off) < kEncTileBytes ? (B - off) : kEncTileBytes);
-            uint8_t* dstp = tile0 + buf * kEncTileBytes;
-            uint32_t bulk = vec ? (nb & ~15u) : 0u;
-            if (bulk && t == 0) tile_copy_async(dstp, d.src + off, bulk, &bars[buf]);
-            for (uint32_t i = bulk + t; i < nb; i += 256) dstp[i] = d.src[off + i];
-            return bulk;
-        };
-
-        uint32_t wpos = d.chunk_stride;         // lowest written byte of the lane region
-        uint32_t flushed = d.chunk_stride >> 4; // lowest 16-byte block already in global memory
-        uint32_t x = kL;
-
-        uint32_t bulk_cur = 0;
-        if (n_tiles) bulk_cur = issue(n_tiles - 1, (n_tiles - 1) & 1);
-        __syncthreads();  // table visible; plain-loaded tile bytes visible
-
-        for (uint32_t jj = n_tiles; jj-- > 0;) {
-            const uint32_t buf = jj & 1;
-            // prefetch the next (lower) tile into the other buffer; its previous
-            // reader finished before the __syncthreads that ended the last iteration
-            uint32_t bulk_next = 0;
-            if (jj > 0) bulk_next = issue(jj - 1, buf ^ 1);
-            if (bulk_cur) {
-                const uint32_t par = buf ? phase1 : phase0;
-                if (!tile_barrier_wait(&bars[buf], par)) atomicOr(status, kErrBarrierTimeout);
-                if (buf) phase1 ^= 1; else phase0 ^= 1;
-            }
-            const uint8_t* tile = tile0 + buf * kEncTileBytes;
-            const unsigned long long row0 = (unsigned long long)jj * kEncRows;
-            const uint32_t rows = (uint32_t)((c_max - row0) < kEncRows ? (c_max - row0) : kEncRows);
-
-            for (int g = (int)((rows + 7) >> 3) - 1; g >= 0; --g) {
-#pragma unroll
-                for (int u = 7; u >= 0; --u) {
-                    const uint32_t r = (uint32_t)g * 8 + (uint32_t)u;
-                    if (row0 + r < my_count) {
-                        const uint32_t sym = zero_lane ? 0u : tile[r * kLanes + t];
-                        const uint4 e = tab[sym];
-                        const uint32_t f = e.y & 0xFFFFu;
-                        if (f == 0) {  // symbol not in the table: raw escape byte, state untouched
-                            --wpos;
-                            ring[((wpos >> 2) & 7) * (kLanes * 4) + t * 4 + (wpos & 3)] = (uint8_t)sym;
-                        } else {
-                            const uint32_t xmax = e.y << 19;  // freq * 2^19; the shift field falls off the top
-                            const bool e1 = x >= xmax;
-                            const bool e2 = (x >> 8) >= xmax;
-                            if (e1) {
-                                --wpos;
-                                ring[((wpos >> 2) & 7) * (kLanes * 4) + t * 4 + (wpos & 3)] = (uint8_t)x;
-                            }
-                            if (e2) {
-                                --wpos;
-                                ring[((wpos >> 2) & 7) * (kLanes * 4) + t * 4 + (wpos & 3)] = (uint8_t)(x >> 8);
-                            }
-                            x >>= ((uint32_t)e1 + (uint32_t)e2) * 8;
-                            const uint32_t q = __umulhi(x, e.x) >> (e.y >> 16);
-                            x = x + q * e.w + e.z;
-                        }
-                    }
-                }
-                // at most 16 new bytes since the last check: at most one block completed
-                const uint32_t done_to = (wpos + 15) >> 4;
-                if (done_to < flushed) {
-                    const uint32_t b = flushed - 1;
-                    const uint32_t* rw = reinterpret_cast<const uint32_t*>(ring);
-                    uint4 v;
-                    v.x = rw[((b * 4 + 0) & 7) * kLanes + t];
-                    v.y = rw[((b * 4 + 1) & 7) * kLanes + t];
-                    v.z = rw[((b * 4 + 2) & 7) * kLanes + t];
-                    v.w = rw[((b * 4 + 3) & 7) * kLanes + t];
-                    *reinterpret_cast<uint4*>(region + (size_t)b * 16) = v;
-                    flushed = b;
-                }
-            }
-            bulk_cur = bulk_next;
-            __syncthreads();  // everyone is done with this tile; plain-loaded bytes of the next are visible
-        }
-
-        // bytes of the last, partial block
-        for (uint32_t p = wpos; p < (flushed << 4); ++p)
-            region[p] = ring[((p >> 2) & 7) * (kLanes * 4) + t * 4 + (p & 3)];
-
-        LaneHeader h;
-        h.final_state = x;
-        h.byte_count = d.chunk_stride - wpos;
-        h.buf_offset = 0;
-        h.pad = 0;
-        hdrs[(size_t)ti * kLanes + t] = h;
-        lane_wpos[(size_t)ti * kLanes + t] = wpos;
-        __syncthreads();  // table and ring are reused by the next tensor
-    }
-}
-
-// ------------------------------------------------------------------ offsets and compaction
-// Per tensor: exclusive prefix sum of the 256 lane byte counts, the passthrough
-// decision (total >= n_bytes), and the final on-disk lane headers.
-__global__ void __launch_bounds__(256) lane_scan_kernel(TensorDesc* __restrict__ descs,
-                                                        LaneHeader* __restrict__ hdrs,
-                                                        unsigned long long* __restrict__ payload_size,
-                                                        uint32_t* __restrict__ lane_off, uint32_t n_tensors) {
-    CHK_SHARED uint32_t warp_tot[8];
-    const uint32_t t = threadIdx.x, lane = t & 31, warp = t >> 5;
-    for (uint32_t ti = blockIdx.x; ti < n_tensors; ti += gridDim.x) {
-        LaneHeader h = hdrs[(size_t)ti * kLanes + t];
-        uint32_t v = h.byte_count;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const uint32_t n = __shfl_up_sync(0xffffffffu, v, o);
-            if (lane >= (uint32_t)o) v += n;
-        }
-        if (lane == 31) warp_tot[warp] = v;
-        __syncthreads();
-        uint32_t before = 0, total = 0;
-#pragma unroll
-        for (int w = 0; w < 8; ++w) {
-            if ((uint32_t)w < warp) before += warp_tot[w];
-            total += warp_tot[w];
-        }
-        const uint32_t excl = before + v - h.byte_count;
-        const unsigned long long B = descs[ti].n_bytes;
-        const bool raw = (unsigned long long)total >= B;
-        lane_off[(size_t)ti * kLanes + t] = excl;
-        if (raw) {
-            h.final_state = 0;
-            h.byte_count = t == 0 ? (uint32_t)B : 0u;
-            h.buf_offset = 0;
-        } else {
-            h.buf_offset = excl;
-        }
-        h.pad = 0;
-        hdrs[(size_t)ti * kLanes + t] = h;
-        if (t == 0) {
-            payload_size[ti] = raw ? B : (unsigned long long)total;
-            if (raw) descs[ti].flags |= kFlagRaw; else descs[ti].flags &= ~kFlagRaw;
-        }
-        __syncthreads();
-    }
-}
-
-// Exclusive prefix sum of the per-tensor payload sizes (one CTA); total in out[n].
-__global__ void __launch_bounds__(1024) tensor_scan_kernel(TensorDesc* __restrict__ descs,
-                                                           const unsigned long long* __restrict__ payload_size,
-                                                           unsigned long long* __restrict__ payload_off,
-                                                           uint32_t n_tensors) {
-    CHK_SHARED unsigned long long part[1024];
-    const uint32_t t = threadIdx.x;
-    const uint32_t per = (n_tensors + 1023) / 1024;
-    const uint32_t lo = t * per < n_tensors ? t * per : n_tensors;
-    const uint32_t hi = lo + per < n_tensors ? lo + per : n_tensors;
-    unsigned long long s = 0;
-    for (uint32_t i = lo; i < hi; ++i) s += payload_size[i];
-    part[t] = s;
-    __syncthreads();
-    if (t == 0) {
-        unsigned long long run = 0;
-        for (uint32_t i = 0; i < 1024; ++i) {
-            const unsigned long long v = part[i];
-            part[i] = run;
-            run += v;
-        }
-        payload_off[n_tensors] = run;
-    }
-    __syncthreads();
-    unsigned long long run = part[t];
-    for (uint32_t i = lo; i < hi; ++i) {
-        payload_off[i] = run;
-        descs[i].payload_off = run;
-        run += payload_size[i];
-    }
-}
-
-// Gather: one warp per (tensor, lane) moves that lane's bytes from scratch to
-// their place in the data section.  A passthrough tensor instead has its masked
-// bytes written, each warp taking 1/256 of the tensor.
-__global__ void __launch_bounds__(256) compact_kernel(const TensorDesc* __restrict__ descs,
-                                                      const LaneHeader* __restrict__ hdrs,
-                                                      const uint32_t* __restrict__ lane_wpos,
-                                                      const uint32_t* __restrict__ lane_off,
-                                                      const uint8_t* __restrict__ scratch,
-                                                      uint8_t* __restrict__ payload, uint32_t n_tensors) {
-    const uint32_t lane = threadIdx.x & 31;
-    const unsigned long long warps = ((unsigned long long)gridDim.x * blockDim.x) >> 5;
-    const unsigned long long total = (unsigned long long)n_tensors * kLanes;
-    for (unsigned long long w = (((unsigned long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5); w < total;
-         w += warps) {
-        const uint32_t ti = (uint32_t)(w >> 8), t = (uint32_t)(w & 255);
-        const TensorDesc d = descs[ti];
-        uint8_t* out = payload + d.payload_off;
-        if (d.flags & kFlagRaw) {
-            const unsigned long long per = (d.n_bytes + kLanes - 1) / kLanes;
-            const unsigned long long a = per * t;
-            const unsigned long long b = a + per < d.n_bytes ? a + per : d.n_bytes;
-            for (unsigned long long i = a + lane; i < b; i += 32)
-                out[i] = (i % d.es) < d.spe ? (uint8_t)0 : d.src[i];
-            continue;
-        }
-        const uint32_t cnt = hdrs[(size_t)ti * kLanes + t].byte_count;
-        const uint8_t* s = scratch + d.scratch_off + (size_t)t * d.chunk_stride + lane_wpos[(size_t)ti * kLanes + t];
-        uint8_t* o = out + lane_off[(size_t)ti * kLanes + t];
-        // align the destination, then move 16 bytes per thread per step
-        uint32_t head = (uint32_t)((16 - (reinterpret_cast<uintptr_t>(o) & 15)) & 15);
-        if (head > cnt) head = cnt;
-        if (lane < head) o[lane] = s[lane];
-        const uint32_t nvec = (cnt - head) >> 4;
-        const uint8_t* sv = s + head;
-        uint8_t* ov = o + head;
-        const uint32_t mis = (uint32_t)(reinterpret_cast<uintptr_t>(sv) & 3);
-        const uint32_t* sw = reinterpret_cast<const uint32_t*>(sv - mis);
-        for (uint32_t v = lane; v < nvec; v += 32) {
-            const uint32_t a0 = sw[v * 4 + 0], a1 = sw[v * 4 + 1], a2 = sw[v * 4 + 2], a3 = sw[v * 4 + 3];
-            uint4 r;
-            if (mis) {
-                const uint32_t a4 = sw[v * 4 + 4];
-                r.x = __funnelshift_r(a0, a1, mis * 8);
-                r.y = __funnelshift_r(a1, a2, mis * 8);
-                r.z = __funnelshift_r(a2, a3, mis * 8);
-                r.w = __funnelshift_r(a3, a4, mis * 8);
-            } else {
-                r = make_uint4(a0, a1, a2, a3);
-            }
-            *reinterpret_cast<uint4*>(ov + (size_t)v * 16) = r;
-        }
-        for (uint32_t i = head + (nvec << 4) + lane; i < cnt; i += 32) o[i] = s[i];
-    }
-}
-
-// ------------------------------------------------------------------ rANS decode
-constexpr uint32_t kDecRows = 64;
-constexpr uint32_t kDecTileBytes = kDecRows * kLanes;
-// decode table (4096 x u32) | output tile | 32-byte input ring per lane | cum[257]
-constexpr uint32_t kDecSmemBytes = kM * 4 + kDecTileBytes + 8 * kLanes * 4 + 260 * 4;
-
-// Decode table entry: symbol[0:8) | (freq-1)[8:20) | (slot - cum[symbol])[20:32)
-//
-// One CTA per tensor, one thread per lane.  A lane reads its stream forward in
-// aligned 16-byte pieces through a ring in shared memory; lanes that only ever
-// held zeroed low bytes are not decoded (their bytes come from the sidecar).
-// Decoded bytes are gathered per 16 KiB tile, OR-merged with the sidecar and
-// written to the destination with 16-byte stores.
-__global__ void __launch_bounds__(256) rans_decode_kernel(const TensorDesc* __restrict__ descs,
-                                                          const uint32_t* __restrict__ freq_tables,  // [T][256]
-                                                          const uint32_t* __restrict__ cum_tables,   // [T][257]
-                                                          const LaneHeader* __restrict__ hdrs,
-                                                          const uint8_t* __restrict__ payload,
-                                                          const uint8_t* __restrict__ sidecar, uint32_t n_tensors,
-                                                          uint32_t check_zero_lanes,
-                                                          uint32_t* __restrict__ status /* per tensor */) {
-    CHK_DYN_SMEM(smem);
-    uint32_t* dtab = reinterpret_cast<uint32_t*>(smem);
-    uint8_t* tile = smem + kM * 4;
-    uint8_t* ring = tile + kDecTileBytes;
-    uint32_t* cum = reinterpret_cast<uint32_t*>(ring + 8 * kLanes * 4);
-    const uint32_t t = threadIdx.x;
-
-    for (uint32_t ti = blockIdx.x; ti < n_tensors; ti += gridDim.x) {
-        const TensorDesc d = descs[ti];
-        const unsigned long long B = d.n_bytes;
-        const bool vec = (d.flags & kFlagAligned) != 0;
-
-        if (d.flags & kFlagRaw) {  // payload is the masked tensor
-            const uint8_t* in = payload + d.payload_off;
-            for (unsigned long long i = t; i < B; i += 256) {
-                const uint32_t j = (uint32_t)(i % d.es);
-                d.dst[i] = j < d.spe ? sidecar[d.sidecar_off + (i / d.es) * d.spe + j] : in[i];
-            }
-            continue;
-        }
-
-        // ---- build the slot table
-        const uint32_t* fq = freq_tables + (size_t)d.table_idx * 256;
-        const uint32_t* cq = cum_tables + (size_t)d.table_idx * 257;
-        cum[t] = cq[t];
-        if (t == 0) cum[256] = cq[256];
-        __syncthreads();
-        for (uint32_t slot = t; slot < kM; slot += 256) {
-            uint32_t lo = 0, hi = 256;  // last s with cum[s] <= slot
-            while (hi - lo > 1) {
-                const uint32_t mid = (lo + hi) >> 1;
-                if (cum[mid] <= slot) lo = mid; else hi = mid;
-            }
-            const uint32_t f = fq[lo];
-            dtab[slot] = lo | ((f - 1) << 8) | ((slot - cum[lo]) << 20);
-        }
-
-        const bool zero_lane = (t % d.es) < d.spe;
-        const bool active = !zero_lane || check_zero_lanes;
-        const unsigned long long c_max = (B + kLanes - 1) / kLanes;
-        const unsigned long long my_count = B > t ? (B - t + kLanes - 1) / kLanes : 0;
-        const LaneHeader h = hdrs[(size_t)ti * kLanes + t];
-        const unsigned long long p_abs = d.payload_off + h.buf_offset;  // offset from the 256-byte aligned base
-        const unsigned long long blk0 = p_abs >> 4;
-        uint32_t rel = (uint32_t)(p_abs & 15);  // read position relative to blk0*16
-        const uint32_t rel_end = rel + h.byte_count;
-        uint32_t loaded = 0;  // 16-byte blocks fetched so far
-        uint32_t x = h.final_state;
-        uint32_t* rw = reinterpret_cast<uint32_t*>(ring);
-        // A valid stream never needs bytes past its own end; a damaged one could
-        // run ahead, so fetching stops one block after the lane's last byte (the
-        // lane then decodes garbage and fails its end check).
-        const uint32_t max_blocks = ((rel_end + 15) >> 4) + 1;
-        auto fetch = [&]() {
-            if (loaded < max_blocks) {
-                const uint4 v = ld_global_v4(payload + (blk0 + loaded) * 16);
-                const uint32_t r = (loaded & 1) * 4;
-                rw[(r + 0) * kLanes + t] = v.x;
-                rw[(r + 1) * kLanes + t] = v.y;
-                rw[(r + 2) * kLanes + t] = v.z;
-                rw[(r + 3) * kLanes + t] = v.w;
-            }
-            ++loaded;
-        };
-        if (active && my_count) {
-            fetch();
-            fetch();
-        }
-        __syncthreads();  // table complete
-
-        const uint32_t n_tiles = (uint32_t)((c_max + kDecRows - 1) / kDecRows);
-        for (uint32_t j = 0; j < n_tiles; ++j) {
-            const unsigned long long row0 = (unsigned long long)j * kDecRows;
-            const uint32_t rows = (uint32_t)((c_max - row0) < kDecRows ? (c_max - row0) : kDecRows);
-            if (active) {
-                for (uint32_t g = 0; g < ((rows + 7) >> 3); ++g) {
-#pragma unroll
-                    for (uint32_t u = 0; u < 8; ++u) {
-                        const uint32_t r = g * 8 + u;
-                        if (row0 + r < my_count) {
-                            const uint32_t slot = x & (kM - 1);
-                            const uint32_t e = dtab[slot];
-                            tile[r * kLanes + t] = (uint8_t)e;
-                            x = (((e >> 8) & 0xFFFu) + 1u) * (x >> kScaleBits) + (e >> 20);
-                            const uint32_t b0 = ring[((rel >> 2) & 7) * (kLanes * 4) + t * 4 + (rel & 3)];
-                            const uint32_t r1 = rel + 1;
-                            const uint32_t b1 = ring[((r1 >> 2) & 7) * (kLanes * 4) + t * 4 + (r1 & 3)];
-                            if (x < (1u << 15)) {
-                                x = (x << 16) | (b0 << 8) | b1;
-                                rel += 2;
-                            } else if (x < kL) {
-                                x = (x << 8) | b0;
-                                rel += 1;
-                            }
-                        }
-                    }
-                    // keep at least 16 unread bytes in the ring for the next 8 symbols
-                    if (my_count && rel >= (loaded - 1) * 16) fetch();
-                }
-            }
-            __syncthreads();  // tile complete
-
-            // ---- merge with the sidecar and store
-            const unsigned long long off = row0 * kLanes;
-            const uint32_t nb = (uint32_t)((B - off) < kDecTileBytes ? (B - off) : kDecTileBytes);
-            uint32_t body = 0;
-            if (vec && d.spe * 2 == d.es && (d.es == 4 || d.es == 2)) {
-                const uint32_t nvec = nb >> 4;
-                body = nvec << 4;
-                for (uint32_t v = t; v < nvec; v += 256) {
-                    const uint4 m = *reinterpret_cast<const uint4*>(tile + v * 16);
-                    const uint2 s = *reinterpret_cast<const uint2*>(sidecar + d.sidecar_off + ((off + v * 16) >> 1));
-                    uint4 o;
-                    if (d.es == 4) {
-                        o.x = (m.x & 0xFFFF0000u) | (s.x & 0xFFFFu);
-                        o.y = (m.y & 0xFFFF0000u) | (s.x >> 16);
-                        o.z = (m.z & 0xFFFF0000u) | (s.y & 0xFFFFu);
-                        o.w = (m.w & 0xFFFF0000u) | (s.y >> 16);
-                    } else {
-                        o.x = (m.x & 0xFF00FF00u) | __byte_perm(s.x, 0, 0x4140);
-                        o.y = (m.y & 0xFF00FF00u) | __byte_perm(s.x, 0, 0x4342);
-                        o.z = (m.z & 0xFF00FF00u) | __byte_perm(s.y, 0, 0x4140);
-                        o.w = (m.w & 0xFF00FF00u) | __byte_perm(s.y, 0, 0x4342);
-                    }
-                    *reinterpret_cast<uint4*>(d.dst + off + (size_t)v * 16) = o;
-                }
-            }
-            for (uint32_t i = body + t; i < nb; i += 256) {
-                const unsigned long long gi = off + i;
-                const uint32_t jb = (uint32_t)(gi % d.es);
-                d.dst[gi] = jb < d.spe ? sidecar[d.sidecar_off + (gi / d.es) * d.spe + jb] : tile[i];
-            }
-            __syncthreads();  // tile may be overwritten
-        }
-
-        if (active) {
-            uint32_t err = 0;
-            if (x != kL) err |= kErrEndState;
-            if (rel != rel_end) err |= kErrEndPointer;
-            if (err) atomicOr(&status[ti], err);
-        }
-        __syncthreads();  // table, ring and cum are reused by the next tensor
-    }
-}
+namespace chk {
 
 // ------------------------------------------------------------------ statistics
 __device__ __forceinline__ float half_bits_to_float(uint32_t h) {

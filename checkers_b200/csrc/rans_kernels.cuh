@@ -1,0 +1,650 @@
+// rans_kernels.cuh -- 256-lane rANS encode / decode and the payload layout
+// kernels.  Included by kernels.cuh (which provides the shared types).
+//
+// Thread mapping.  A tensor is 256 interleaved lanes: lane t owns bytes t,
+// t+256, ...  (src/ANSCompressor.cpp:154-211 in the Checkers tree).  A team of
+// 64 threads works on one tensor; thread j owns the four lanes 4j..4j+3, i.e.
+// one aligned 32-bit word of every 256-byte row, so a warp reads or writes 128
+// contiguous bytes per row with no staging.  Of those four lanes only the ones
+// that carry codec input are real chains:
+//     fp32      bytes 2,3 of each word     2 chains per thread
+//     bf16/fp16 bytes 1,3 of each word     2 chains per thread
+//     int8/32   all four bytes             4 chains per thread
+// The remaining lanes only ever see the zeroed low bytes.  Every such lane of a
+// tensor encodes the same symbol-0 sequence, so that sequence is produced once
+// per tensor (zero_lane_kernel) and shared: a lane with one symbol fewer owns a
+// suffix of the same byte string.  The independent chains of a thread give the
+// scheduler instruction-level parallelism across the serial state updates.
+#pragma once
+
+namespace chk {
+
+// Result of the shared symbol-0 chain of one tensor: state and byte count after
+// c_max symbols ([0]) and after c_max-1 symbols ([1]); its bytes end at the top
+// of the tensor's zero region.
+struct ZeroRec {
+    uint32_t state[2];
+    uint32_t nbytes[2];
+};
+
+constexpr uint32_t kTeam = 64;  // threads per tensor
+
+// shared memory of one encode team: table (256 x 16 B) + 32-byte output ring per chain
+template <int NV>
+struct EncSmem {
+    uint4 tab[256];
+    uint32_t ring[NV * 8 * kTeam];
+};
+constexpr uint32_t kEncSmemBytes = sizeof(EncSmem<4>);
+
+// One encode step of one chain: renormalise (at most two bytes, low byte first,
+// written downward) and advance the state.  `ring` is the chain's word column.
+__device__ __forceinline__ void enc_step(uint32_t sym, const uint4* tab, uint32_t& x, uint32_t& wpos, uint8_t* ring_bytes) {
+    const uint4 e = tab[sym];
+    const uint32_t f = e.y & 0xFFFFu;
+    if (f == 0) {  // symbol not in the table: raw escape byte, state untouched
+        --wpos;
+        ring_bytes[((wpos >> 2) & 7) * (kTeam * 4) + (wpos & 3)] = (uint8_t)sym;
+        return;
+    }
+    const uint32_t xmax = e.y << 19;  // freq * 2^19 (the shift field falls off the top)
+    const bool e1 = x >= xmax;
+    const bool e2 = (x >> 8) >= xmax;
+    if (e1) {
+        --wpos;
+        ring_bytes[((wpos >> 2) & 7) * (kTeam * 4) + (wpos & 3)] = (uint8_t)x;
+    }
+    if (e2) {
+        --wpos;
+        ring_bytes[((wpos >> 2) & 7) * (kTeam * 4) + (wpos & 3)] = (uint8_t)(x >> 8);
+    }
+    x >>= ((uint32_t)e1 + (uint32_t)e2) * 8;
+    const uint32_t q = __umulhi(x, e.x) >> (e.y >> 16);
+    x = x + q * e.w + e.z;
+}
+
+// After at most 8 steps (16 bytes): move the one 16-byte block that may have
+// completed from the ring to the lane's scratch region.
+__device__ __forceinline__ void enc_flush(uint32_t wpos, uint32_t& flushed, const uint32_t* ring_words, uint8_t* region) {
+    const uint32_t done_to = (wpos + 15) >> 4;
+    if (done_to < flushed) {
+        const uint32_t b = flushed - 1;
+        uint4 v;
+        v.x = ring_words[((b * 4 + 0) & 7) * kTeam];
+        v.y = ring_words[((b * 4 + 1) & 7) * kTeam];
+        v.z = ring_words[((b * 4 + 2) & 7) * kTeam];
+        v.w = ring_words[((b * 4 + 3) & 7) * kTeam];
+        *reinterpret_cast<uint4*>(region + (size_t)b * 16) = v;
+        flushed = b;
+    }
+}
+
+__device__ __forceinline__ uint32_t load_row_word(const uint8_t* p, bool aligned4) {
+    if (aligned4) return *reinterpret_cast<const uint32_t*>(p);
+    return (uint32_t)p[0] | ((uint32_t)p[1] << 8) | ((uint32_t)p[2] << 16) | ((uint32_t)p[3] << 24);
+}
+
+template <int NV>
+__device__ __forceinline__ void encode_tensor(const TensorDesc& d, uint32_t ti, const EncEntry* __restrict__ tables,
+                                              uint8_t* __restrict__ scratch, LaneHeader* __restrict__ hdrs,
+                                              unsigned long long* __restrict__ lane_src,
+                                              const ZeroRec* __restrict__ zrec, unsigned char* smem_raw) {
+    EncSmem<NV>* sm = reinterpret_cast<EncSmem<NV>*>(smem_raw);
+    const uint32_t j = threadIdx.x;
+    const unsigned long long B = d.n_bytes;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const EncEntry e = tables[(size_t)d.table_idx * 256 + j * 4 + i];
+        sm->tab[j * 4 + i] = make_uint4(e.rcp, e.freq_shift, e.bias, e.cmpl);
+    }
+    __syncthreads();
+
+    // byte position inside the thread's word for each of its chains
+    uint32_t bpos[NV];
+    if (NV == 4) {
+#pragma unroll
+        for (int k = 0; k < NV; ++k) bpos[k] = k;
+    } else {
+        bpos[0] = d.es == 4 ? 2u : 1u;
+        bpos[NV - 1] = 3u;
+    }
+
+    uint32_t x[NV], wpos[NV], flushed[NV];
+    uint8_t* region[NV];
+    uint8_t* ringb[NV];
+    const uint32_t* ringw[NV];
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        x[k] = kL;
+        wpos[k] = d.chunk_stride;
+        flushed[k] = d.chunk_stride >> 4;
+        region[k] = scratch + d.scratch_off + (size_t)(j * NV + k) * d.chunk_stride;
+        ringw[k] = sm->ring + (size_t)k * 8 * kTeam + j;
+        ringb[k] = reinterpret_cast<uint8_t*>(sm->ring + (size_t)k * 8 * kTeam + j);
+    }
+
+    const unsigned long long full_rows = B >> 8;
+    const uint32_t tail = (uint32_t)(B & 255);
+    const bool aligned4 = (reinterpret_cast<uintptr_t>(d.src) & 3) == 0;
+    const uint8_t* col = d.src + 4 * j;
+
+    // the last, partial row (symbols of the highest index come first)
+    if (tail) {
+#pragma unroll
+        for (int k = 0; k < NV; ++k) {
+            const uint32_t t = 4 * j + bpos[k];
+            if (t < tail) enc_step(d.src[(full_rows << 8) + t], sm->tab, x[k], wpos[k], ringb[k]);
+        }
+    }
+    // rows above the last multiple of 8, one at a time: with the partial row at most 8 steps
+    unsigned long long r = full_rows;
+    const uint32_t odd = (uint32_t)(full_rows & 7);
+    for (uint32_t u = 0; u < odd; ++u) {
+        --r;
+        const uint32_t w = load_row_word(col + (r << 8), aligned4);
+#pragma unroll
+        for (int k = 0; k < NV; ++k) enc_step((w >> (8 * bpos[k])) & 0xFF, sm->tab, x[k], wpos[k], ringb[k]);
+    }
+#pragma unroll
+    for (int k = 0; k < NV; ++k) enc_flush(wpos[k], flushed[k], ringw[k], region[k]);
+
+    // full groups of 8 rows, highest first; the 8 loads are issued before the dependent chains run
+    while (r >= 8) {
+        r -= 8;
+        uint32_t w[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) w[u] = load_row_word(col + ((r + u) << 8), aligned4);
+#pragma unroll
+        for (int u = 7; u >= 0; --u) {
+#pragma unroll
+            for (int k = 0; k < NV; ++k) enc_step((w[u] >> (8 * bpos[k])) & 0xFF, sm->tab, x[k], wpos[k], ringb[k]);
+        }
+#pragma unroll
+        for (int k = 0; k < NV; ++k) enc_flush(wpos[k], flushed[k], ringw[k], region[k]);
+    }
+
+    // bytes of the last, partial block; lane headers; where the lane's bytes start
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        for (uint32_t p = wpos[k]; p < (flushed[k] << 4); ++p)
+            region[k][p] = ringb[k][((p >> 2) & 7) * (kTeam * 4) + (p & 3)];
+        const uint32_t t = 4 * j + bpos[k];
+        LaneHeader h;
+        h.final_state = x[k];
+        h.byte_count = d.chunk_stride - wpos[k];
+        h.buf_offset = 0;
+        h.pad = 0;
+        hdrs[(size_t)ti * kLanes + t] = h;
+        lane_src[(size_t)ti * kLanes + t] = d.scratch_off + (unsigned long long)(j * NV + k) * d.chunk_stride + wpos[k];
+    }
+    if (NV == 2) {  // the thread's other two lanes share the tensor's symbol-0 chain
+        const ZeroRec z = zrec[ti];
+        const unsigned long long c_max = (B + kLanes - 1) / kLanes;
+        const unsigned long long zbase = d.scratch_off + (unsigned long long)kTeam * NV * d.chunk_stride;
+#pragma unroll
+        for (uint32_t b = 0; b < 4; ++b) {
+            if (b == bpos[0] || b == 3u) continue;
+            const uint32_t t = 4 * j + b;
+            const unsigned long long cnt = B > t ? (B - t + kLanes - 1) / kLanes : 0;
+            LaneHeader h;
+            h.buf_offset = 0;
+            h.pad = 0;
+            if (cnt == 0) {
+                h.final_state = kL;
+                h.byte_count = 0;
+            } else {
+                const int w = cnt == c_max ? 0 : 1;
+                h.final_state = z.state[w];
+                h.byte_count = z.nbytes[w];
+            }
+            hdrs[(size_t)ti * kLanes + t] = h;
+            lane_src[(size_t)ti * kLanes + t] = zbase + d.chunk_stride - h.byte_count;
+        }
+    }
+    __syncthreads();  // table and ring are reused by the next tensor
+}
+
+// One team (CTA of 64 threads) per tensor.
+__global__ void __launch_bounds__(kTeam) rans_encode_kernel(const TensorDesc* __restrict__ descs,
+                                                            const EncEntry* __restrict__ tables,
+                                                            uint8_t* __restrict__ scratch,
+                                                            LaneHeader* __restrict__ hdrs,
+                                                            unsigned long long* __restrict__ lane_src,
+                                                            const ZeroRec* __restrict__ zrec, uint32_t n_tensors) {
+    CHK_DYN_SMEM(smem);
+    for (uint32_t ti = blockIdx.x; ti < n_tensors; ti += gridDim.x) {
+        const TensorDesc d = descs[ti];
+        if (d.spe * 2 == d.es)
+            encode_tensor<2>(d, ti, tables, scratch, hdrs, lane_src, zrec, smem);
+        else
+            encode_tensor<4>(d, ti, tables, scratch, hdrs, lane_src, zrec, smem);
+    }
+}
+
+// The symbol-0 chain of every tensor that has zeroed low bytes: one thread per
+// tensor, c_max steps, bytes written downward from the top of the tensor's zero
+// region (the region after its value-lane regions).
+__global__ void __launch_bounds__(128) zero_lane_kernel(const TensorDesc* __restrict__ descs,
+                                                        const EncEntry* __restrict__ tables,
+                                                        uint8_t* __restrict__ scratch, ZeroRec* __restrict__ zrec,
+                                                        uint32_t n_tensors) {
+    const uint32_t ti = blockIdx.x * blockDim.x + threadIdx.x;
+    if (ti >= n_tensors) return;
+    const TensorDesc d = descs[ti];
+    ZeroRec z;
+    z.state[0] = z.state[1] = kL;
+    z.nbytes[0] = z.nbytes[1] = 0;
+    if (d.spe * 2 != d.es) {
+        zrec[ti] = z;
+        return;
+    }
+    const EncEntry e = tables[(size_t)d.table_idx * 256];
+    const uint32_t f = e.freq_shift & 0xFFFFu, sh = e.freq_shift >> 16, xmax = e.freq_shift << 19;
+    uint8_t* const region = scratch + d.scratch_off + (size_t)kTeam * 2 * d.chunk_stride;
+    uint32_t wpos = d.chunk_stride, x = kL;
+    const unsigned long long c_max = (d.n_bytes + kLanes - 1) / kLanes;
+    for (unsigned long long i = 1; i <= c_max; ++i) {
+        if (f == 0) {
+            region[--wpos] = 0;
+        } else {
+            if (x >= xmax) {
+                region[--wpos] = (uint8_t)x;
+                x >>= 8;
+                if (x >= xmax) {
+                    region[--wpos] = (uint8_t)x;
+                    x >>= 8;
+                }
+            }
+            const uint32_t q = __umulhi(x, e.rcp) >> sh;
+            x = x + q * e.cmpl + e.bias;
+        }
+        if (i + 1 == c_max) {
+            z.state[1] = x;
+            z.nbytes[1] = d.chunk_stride - wpos;
+        }
+    }
+    z.state[0] = x;
+    z.nbytes[0] = d.chunk_stride - wpos;
+    zrec[ti] = z;
+}
+
+// ------------------------------------------------------------------ offsets and compaction
+// Per tensor: exclusive prefix sum of the 256 lane byte counts
+// (src/ANSCompressor.cpp:647-651), the passthrough decision total >= n_bytes
+// (:695-713) and the final on-disk lane headers (:686-691).
+__global__ void __launch_bounds__(256) lane_scan_kernel(TensorDesc* __restrict__ descs,
+                                                        LaneHeader* __restrict__ hdrs,
+                                                        unsigned long long* __restrict__ payload_size,
+                                                        uint32_t* __restrict__ lane_off, uint32_t n_tensors) {
+    CHK_SHARED uint32_t warp_tot[8];
+    const uint32_t t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    for (uint32_t ti = blockIdx.x; ti < n_tensors; ti += gridDim.x) {
+        LaneHeader h = hdrs[(size_t)ti * kLanes + t];
+        uint32_t v = h.byte_count;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t n = __shfl_up_sync(0xffffffffu, v, o);
+            if (lane >= (uint32_t)o) v += n;
+        }
+        if (lane == 31) warp_tot[warp] = v;
+        __syncthreads();
+        uint32_t before = 0, total = 0;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) {
+            if ((uint32_t)w < warp) before += warp_tot[w];
+            total += warp_tot[w];
+        }
+        const uint32_t excl = before + v - h.byte_count;
+        const unsigned long long B = descs[ti].n_bytes;
+        const bool raw = (unsigned long long)total >= B;
+        lane_off[(size_t)ti * kLanes + t] = excl;
+        if (raw) {
+            h.final_state = 0;
+            h.byte_count = t == 0 ? (uint32_t)B : 0u;
+            h.buf_offset = 0;
+        } else {
+            h.buf_offset = excl;
+        }
+        h.pad = 0;
+        hdrs[(size_t)ti * kLanes + t] = h;
+        if (t == 0) {
+            payload_size[ti] = raw ? B : (unsigned long long)total;
+            if (raw) descs[ti].flags |= kFlagRaw; else descs[ti].flags &= ~kFlagRaw;
+        }
+        __syncthreads();
+    }
+}
+
+// Exclusive prefix sum of the per-tensor payload sizes (one CTA); total in out[n].
+__global__ void __launch_bounds__(1024) tensor_scan_kernel(TensorDesc* __restrict__ descs,
+                                                           const unsigned long long* __restrict__ payload_size,
+                                                           unsigned long long* __restrict__ payload_off,
+                                                           uint32_t n_tensors) {
+    CHK_SHARED unsigned long long part[1024];
+    const uint32_t t = threadIdx.x;
+    const uint32_t per = (n_tensors + 1023) / 1024;
+    const uint32_t lo = t * per < n_tensors ? t * per : n_tensors;
+    const uint32_t hi = lo + per < n_tensors ? lo + per : n_tensors;
+    unsigned long long s = 0;
+    for (uint32_t i = lo; i < hi; ++i) s += payload_size[i];
+    part[t] = s;
+    __syncthreads();
+    if (t == 0) {
+        unsigned long long run = 0;
+        for (uint32_t i = 0; i < 1024; ++i) {
+            const unsigned long long v = part[i];
+            part[i] = run;
+            run += v;
+        }
+        payload_off[n_tensors] = run;
+    }
+    __syncthreads();
+    unsigned long long run = part[t];
+    for (uint32_t i = lo; i < hi; ++i) {
+        payload_off[i] = run;
+        descs[i].payload_off = run;
+        run += payload_size[i];
+    }
+}
+
+// Gather (src/ANSCompressor.cpp:225-238): one warp per (tensor, lane) moves that
+// lane's bytes from scratch to their place in the data section, 16 bytes per
+// thread per step once the destination is aligned.  A passthrough tensor instead
+// has its masked bytes written, each warp taking 1/256 of the tensor.
+__global__ void __launch_bounds__(256) compact_kernel(const TensorDesc* __restrict__ descs,
+                                                      const LaneHeader* __restrict__ hdrs,
+                                                      const unsigned long long* __restrict__ lane_src,
+                                                      const uint32_t* __restrict__ lane_off,
+                                                      const uint8_t* __restrict__ scratch,
+                                                      uint8_t* __restrict__ payload, uint32_t n_tensors) {
+    const uint32_t lane = threadIdx.x & 31;
+    const unsigned long long warps = ((unsigned long long)gridDim.x * blockDim.x) >> 5;
+    const unsigned long long total = (unsigned long long)n_tensors * kLanes;
+    for (unsigned long long w = (((unsigned long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5); w < total;
+         w += warps) {
+        const uint32_t ti = (uint32_t)(w >> 8), t = (uint32_t)(w & 255);
+        const TensorDesc d = descs[ti];
+        uint8_t* out = payload + d.payload_off;
+        if (d.flags & kFlagRaw) {
+            const unsigned long long per = (d.n_bytes + kLanes - 1) / kLanes;
+            const unsigned long long a = per * t;
+            const unsigned long long b = a + per < d.n_bytes ? a + per : d.n_bytes;
+            for (unsigned long long i = a + lane; i < b; i += 32)
+                out[i] = (i % d.es) < d.spe ? (uint8_t)0 : d.src[i];
+            continue;
+        }
+        const uint32_t cnt = hdrs[(size_t)ti * kLanes + t].byte_count;
+        const uint8_t* s = scratch + lane_src[(size_t)ti * kLanes + t];
+        uint8_t* o = out + lane_off[(size_t)ti * kLanes + t];
+        uint32_t head = (uint32_t)((16 - (reinterpret_cast<uintptr_t>(o) & 15)) & 15);
+        if (head > cnt) head = cnt;
+        if (lane < head) o[lane] = s[lane];
+        const uint32_t nvec = (cnt - head) >> 4;
+        const uint8_t* sv = s + head;
+        uint8_t* ov = o + head;
+        const uint32_t mis = (uint32_t)(reinterpret_cast<uintptr_t>(sv) & 3);
+        const uint32_t* sw = reinterpret_cast<const uint32_t*>(sv - mis);
+        for (uint32_t v = lane; v < nvec; v += 32) {
+            const uint32_t a0 = sw[v * 4 + 0], a1 = sw[v * 4 + 1], a2 = sw[v * 4 + 2], a3 = sw[v * 4 + 3];
+            uint4 r;
+            if (mis) {
+                const uint32_t a4 = sw[v * 4 + 4];
+                r.x = __funnelshift_r(a0, a1, mis * 8);
+                r.y = __funnelshift_r(a1, a2, mis * 8);
+                r.z = __funnelshift_r(a2, a3, mis * 8);
+                r.w = __funnelshift_r(a3, a4, mis * 8);
+            } else {
+                r = make_uint4(a0, a1, a2, a3);
+            }
+            *reinterpret_cast<uint4*>(ov + (size_t)v * 16) = r;
+        }
+        for (uint32_t i = head + (nvec << 4) + lane; i < cnt; i += 32) o[i] = s[i];
+    }
+}
+
+// ------------------------------------------------------------------ rANS decode
+// Decode table entry: symbol[0:8) | (freq-1)[8:20) | (slot - cum[symbol])[20:32)
+template <int NV>
+struct DecSmem {
+    uint32_t dtab[kM];
+    uint32_t ring[NV * 8 * kTeam];
+    uint32_t cum[260];
+};
+constexpr uint32_t kDecSmemBytes = sizeof(DecSmem<4>);
+
+struct DecChain {
+    uint32_t x;
+    uint32_t rel;      // read position relative to blk0 * 16
+    uint32_t rel_end;  // where a valid stream ends
+    uint32_t loaded;   // 16-byte blocks fetched so far
+    uint32_t max_blocks;
+    unsigned long long blk0;
+};
+
+// Fetch the next aligned 16 bytes of a lane's stream into its 32-byte ring.  A
+// valid stream never needs bytes past its own end; a damaged one could run
+// ahead, so fetching stops one block after the lane's last byte (the lane then
+// decodes garbage and fails its end check).
+__device__ __forceinline__ void dec_fetch(DecChain& c, const uint8_t* __restrict__ payload, uint32_t* ring_words) {
+    if (c.loaded < c.max_blocks) {
+        const uint4 v = ld_global_v4(payload + (c.blk0 + c.loaded) * 16);
+        const uint32_t r = (c.loaded & 1) * 4;
+        ring_words[(r + 0) * kTeam] = v.x;
+        ring_words[(r + 1) * kTeam] = v.y;
+        ring_words[(r + 2) * kTeam] = v.z;
+        ring_words[(r + 3) * kTeam] = v.w;
+    }
+    ++c.loaded;
+}
+
+__device__ __forceinline__ uint32_t dec_step(DecChain& c, const uint32_t* dtab, const uint8_t* ring_bytes) {
+    const uint32_t slot = c.x & (kM - 1);
+    const uint32_t e = dtab[slot];
+    uint32_t x = (((e >> 8) & 0xFFFu) + 1u) * (c.x >> kScaleBits) + (e >> 20);
+    const uint32_t r0 = c.rel, r1 = c.rel + 1;
+    const uint32_t b0 = ring_bytes[((r0 >> 2) & 7) * (kTeam * 4) + (r0 & 3)];
+    const uint32_t b1 = ring_bytes[((r1 >> 2) & 7) * (kTeam * 4) + (r1 & 3)];
+    if (x < (1u << 15)) {
+        x = (x << 16) | (b0 << 8) | b1;
+        c.rel += 2;
+    } else if (x < kL) {
+        x = (x << 8) | b0;
+        c.rel += 1;
+    }
+    c.x = x;
+    return e & 0xFFu;
+}
+
+template <int NV>
+__device__ __forceinline__ void decode_tensor(const TensorDesc& d, uint32_t ti,
+                                              const uint32_t* __restrict__ freq_tables,
+                                              const uint32_t* __restrict__ cum_tables,
+                                              const LaneHeader* __restrict__ hdrs,
+                                              const uint8_t* __restrict__ payload,
+                                              const uint8_t* __restrict__ sidecar, uint32_t check_zero_lanes,
+                                              uint32_t* __restrict__ status, unsigned char* smem_raw) {
+    DecSmem<NV>* sm = reinterpret_cast<DecSmem<NV>*>(smem_raw);
+    const uint32_t j = threadIdx.x;
+    const unsigned long long B = d.n_bytes;
+
+    // ---- slot table
+    const uint32_t* fq = freq_tables + (size_t)d.table_idx * 256;
+    const uint32_t* cq = cum_tables + (size_t)d.table_idx * 257;
+    for (uint32_t i = j; i < 257; i += kTeam) sm->cum[i] = cq[i];
+    __syncthreads();
+    for (uint32_t slot = j; slot < kM; slot += kTeam) {
+        uint32_t lo = 0, hi = 256;  // last s with cum[s] <= slot
+        while (hi - lo > 1) {
+            const uint32_t mid = (lo + hi) >> 1;
+            if (sm->cum[mid] <= slot) lo = mid; else hi = mid;
+        }
+        sm->dtab[slot] = lo | ((fq[lo] - 1) << 8) | ((slot - sm->cum[lo]) << 20);
+    }
+
+    uint32_t bpos[NV];
+    if (NV == 4) {
+#pragma unroll
+        for (int k = 0; k < NV; ++k) bpos[k] = k;
+    } else {
+        bpos[0] = d.es == 4 ? 2u : 1u;
+        bpos[NV - 1] = 3u;
+    }
+    // mask of the word's bytes that come from the codec (the rest come from the sidecar)
+    const uint32_t keep = NV == 4 ? 0xFFFFFFFFu : (d.es == 4 ? 0xFFFF0000u : 0xFF00FF00u);
+
+    DecChain ch[NV];
+    uint32_t* ringw[NV];
+    const uint8_t* ringb[NV];
+    unsigned long long cnt[NV];
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const uint32_t t = 4 * j + bpos[k];
+        cnt[k] = B > t ? (B - t + kLanes - 1) / kLanes : 0;
+        const LaneHeader h = hdrs[(size_t)ti * kLanes + t];
+        const unsigned long long p_abs = d.payload_off + h.buf_offset;
+        ch[k].x = h.final_state;
+        ch[k].blk0 = p_abs >> 4;
+        ch[k].rel = (uint32_t)(p_abs & 15);
+        ch[k].rel_end = ch[k].rel + h.byte_count;
+        ch[k].max_blocks = ((ch[k].rel_end + 15) >> 4) + 1;
+        ch[k].loaded = 0;
+        ringw[k] = sm->ring + (size_t)k * 8 * kTeam + j;
+        ringb[k] = reinterpret_cast<const uint8_t*>(ringw[k]);
+        if (cnt[k]) {
+            dec_fetch(ch[k], payload, ringw[k]);
+            dec_fetch(ch[k], payload, ringw[k]);
+        }
+    }
+    __syncthreads();  // table complete
+
+    const unsigned long long full_rows = B >> 8;
+    const uint32_t tail = (uint32_t)(B & 255);
+    const bool dst4 = (reinterpret_cast<uintptr_t>(d.dst) & 3) == 0;
+    const bool side2 = NV == 2 && ((reinterpret_cast<uintptr_t>(sidecar) + d.sidecar_off) & 1) == 0;
+    uint8_t* col = d.dst + 4 * j;
+
+    // low bytes of the word of row r: fp32 -> element 64r+j (2 bytes); bf16 -> elements 128r+2j, +1
+    auto side_word = [&](unsigned long long r) -> uint32_t {
+        if (NV == 4) return 0u;
+        const uint8_t* sp = sidecar + d.sidecar_off + (r << 7) + 2 * j;
+        const uint32_t s = side2 ? (uint32_t)*reinterpret_cast<const uint16_t*>(sp)
+                                 : ((uint32_t)sp[0] | ((uint32_t)sp[1] << 8));
+        return d.es == 4 ? s : ((s & 0xFFu) | ((s & 0xFF00u) << 8));
+    };
+    auto store_word = [&](unsigned long long r, uint32_t w) {
+        uint8_t* p = col + (r << 8);
+        if (dst4) {
+            *reinterpret_cast<uint32_t*>(p) = w;
+        } else {
+            p[0] = (uint8_t)w;
+            p[1] = (uint8_t)(w >> 8);
+            p[2] = (uint8_t)(w >> 16);
+            p[3] = (uint8_t)(w >> 24);
+        }
+    };
+
+    unsigned long long r = 0;
+    while (r + 8 <= full_rows) {
+        uint32_t side[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) side[u] = side_word(r + u);
+        uint32_t w[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            uint32_t acc = 0;
+#pragma unroll
+            for (int k = 0; k < NV; ++k) acc |= dec_step(ch[k], sm->dtab, ringb[k]) << (8 * bpos[k]);
+            w[u] = (acc & keep) | side[u];
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) store_word(r + u, w[u]);
+#pragma unroll
+        for (int k = 0; k < NV; ++k)
+            if (ch[k].rel >= (ch[k].loaded - 1) * 16) dec_fetch(ch[k], payload, ringw[k]);
+        r += 8;
+    }
+    // remaining full rows and the partial row: at most 8 steps per chain
+    for (; r < full_rows; ++r) {
+        uint32_t acc = 0;
+#pragma unroll
+        for (int k = 0; k < NV; ++k) acc |= dec_step(ch[k], sm->dtab, ringb[k]) << (8 * bpos[k]);
+        store_word(r, (acc & keep) | side_word(r));
+    }
+    if (tail) {
+        uint32_t acc = 0;
+#pragma unroll
+        for (int k = 0; k < NV; ++k)
+            if (4 * j + bpos[k] < tail) acc |= dec_step(ch[k], sm->dtab, ringb[k]) << (8 * bpos[k]);
+#pragma unroll
+        for (uint32_t b = 0; b < 4; ++b) {
+            const uint32_t t = 4 * j + b;
+            if (t >= tail) continue;
+            const unsigned long long gi = (full_rows << 8) + t;
+            const uint32_t jb = (uint32_t)(gi % d.es);
+            d.dst[gi] = jb < d.spe ? sidecar[d.sidecar_off + (gi / d.es) * d.spe + jb] : (uint8_t)(acc >> (8 * b));
+        }
+    }
+
+    uint32_t err = 0;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        if (ch[k].x != kL) err |= kErrEndState;
+        if (ch[k].rel != ch[k].rel_end) err |= kErrEndPointer;
+    }
+    if (NV == 2 && check_zero_lanes) {
+        // optional: replay the lanes that only carry zeroed bytes and check their end state
+#pragma unroll
+        for (uint32_t b = 0; b < 4; ++b) {
+            if (b == bpos[0] || b == 3u) continue;
+            const uint32_t t = 4 * j + b;
+            const unsigned long long n = B > t ? (B - t + kLanes - 1) / kLanes : 0;
+            const LaneHeader h = hdrs[(size_t)ti * kLanes + t];
+            const uint8_t* p = payload + d.payload_off + h.buf_offset;
+            const uint8_t* const end = p + h.byte_count;
+            uint32_t x = h.final_state;
+            bool bad = false;
+            for (unsigned long long i = 0; i < n && !bad; ++i) {
+                const uint32_t e = sm->dtab[x & (kM - 1)];
+                if (e & 0xFFu) bad = true;  // must decode to symbol 0
+                x = (((e >> 8) & 0xFFFu) + 1u) * (x >> kScaleBits) + (e >> 20);
+                while (x < kL && !bad) {
+                    if (p >= end) bad = true; else x = (x << 8) | *p++;
+                }
+            }
+            if (bad || p != end) err |= kErrEndPointer;
+            if (x != kL) err |= kErrEndState;
+        }
+    }
+    if (err) atomicOr(&status[ti], err);
+    __syncthreads();  // table and rings are reused by the next tensor
+}
+
+// One team (CTA of 64 threads) per tensor.  Each thread rebuilds one 32-bit word
+// of every row from its decoded bytes and the sidecar and stores it directly.
+__global__ void __launch_bounds__(kTeam) rans_decode_kernel(const TensorDesc* __restrict__ descs,
+                                                            const uint32_t* __restrict__ freq_tables,  // [T][256]
+                                                            const uint32_t* __restrict__ cum_tables,   // [T][257]
+                                                            const LaneHeader* __restrict__ hdrs,
+                                                            const uint8_t* __restrict__ payload,
+                                                            const uint8_t* __restrict__ sidecar, uint32_t n_tensors,
+                                                            uint32_t check_zero_lanes,
+                                                            uint32_t* __restrict__ status /* per tensor */) {
+    CHK_DYN_SMEM(smem);
+    for (uint32_t ti = blockIdx.x; ti < n_tensors; ti += gridDim.x) {
+        const TensorDesc d = descs[ti];
+        if (d.flags & kFlagRaw) {  // payload is the masked tensor
+            const uint8_t* in = payload + d.payload_off;
+            for (unsigned long long i = threadIdx.x; i < d.n_bytes; i += kTeam) {
+                const uint32_t jb = (uint32_t)(i % d.es);
+                d.dst[i] = jb < d.spe ? sidecar[d.sidecar_off + (i / d.es) * d.spe + jb] : in[i];
+            }
+            continue;
+        }
+        if (d.spe * 2 == d.es)
+            decode_tensor<2>(d, ti, freq_tables, cum_tables, hdrs, payload, sidecar, check_zero_lanes, status, smem);
+        else
+            decode_tensor<4>(d, ti, freq_tables, cum_tables, hdrs, payload, sidecar, check_zero_lanes, status, smem);
+    }
+}
+
+}  // namespace chk

@@ -41,7 +41,7 @@ Batch make_batch(size_t n, const uint8_t* const* srcs, uint8_t* const* dsts, con
         const uintptr_t p = (uintptr_t)(srcs ? (const void*)srcs[i] : (const void*)dsts[i]);
         if ((p & 15) == 0 && (d.sidecar_off & 15) == 0) d.flags |= kFlagAligned;
         b.sidecar_total += (d.n_bytes / d.es) * d.spe;
-        b.scratch_total += 256ull * d.chunk_stride;
+        b.scratch_total += (d.spe * 2 == d.es ? 129ull : 256ull) * d.chunk_stride;
         b.bytes_total += d.n_bytes;
         b.tile_start[i + 1] = b.tile_start[i] + (uint32_t)((d.n_bytes + kSplitTileBytes - 1) / kSplitTileBytes);
     }
@@ -92,16 +92,20 @@ uint32_t emu_encode(size_t n, const uint8_t* const* srcs, const uint64_t* n_byte
     // keep lane regions 16-byte aligned like the device allocation
     uint8_t* scr = (uint8_t*)(((uintptr_t)scratch.data() + 15) & ~(uintptr_t)15);
     std::vector<LaneHeader> hdrs(n * 256);
-    std::vector<uint32_t> wpos(n * 256), loff(n * 256);
+    std::vector<unsigned long long> lsrc(n * 256);
+    std::vector<uint32_t> loff(n * 256);
+    std::vector<ZeroRec> zrec(n);
     std::vector<unsigned long long> psize(n), poff(n + 1);
     uint32_t status = 0;
-    emu::launch(grid, 256, kEncSmemBytes, [&] {
-        rans_encode_kernel(b.descs.data(), enc.data(), scr, hdrs.data(), wpos.data(), (uint32_t)n, &status);
+    emu::launch((unsigned)((n + 127) / 128), 128, 0,
+                [&] { zero_lane_kernel(b.descs.data(), enc.data(), scr, zrec.data(), (uint32_t)n); });
+    emu::launch(grid, kTeam, kEncSmemBytes, [&] {
+        rans_encode_kernel(b.descs.data(), enc.data(), scr, hdrs.data(), lsrc.data(), zrec.data(), (uint32_t)n);
     });
     emu::launch(grid, 256, 0, [&] { lane_scan_kernel(b.descs.data(), hdrs.data(), psize.data(), loff.data(), (uint32_t)n); });
     emu::launch(1, 1024, 0, [&] { tensor_scan_kernel(b.descs.data(), psize.data(), poff.data(), (uint32_t)n); });
     emu::launch(grid, 256, 0, [&] {
-        compact_kernel(b.descs.data(), hdrs.data(), wpos.data(), loff.data(), scr, payload_out, (uint32_t)n);
+        compact_kernel(b.descs.data(), hdrs.data(), lsrc.data(), loff.data(), scr, payload_out, (uint32_t)n);
     });
     for (size_t i = 0; i <= n; ++i) payload_off_out[i] = poff[i];
     std::memcpy(hdrs_out, hdrs.data(), n * 4096);
@@ -120,7 +124,7 @@ void emu_decode(size_t n, uint8_t* const* dsts, const uint64_t* n_bytes, const u
         if (raw[i]) b.descs[i].flags |= kFlagRaw;
     }
     std::memset(status_out, 0, n * 4);
-    emu::launch(grid, 256, kDecSmemBytes, [&] {
+    emu::launch(grid, kTeam, kDecSmemBytes, [&] {
         rans_decode_kernel(b.descs.data(), nf, cf, (const LaneHeader*)hdrs, payload, sidecar, (uint32_t)n,
                            check_zero_lanes, status_out);
     });

@@ -1,0 +1,108 @@
+"""The library's CUDA kernels, compiled by g++ behind the block emulator
+(tests/emu), against the oracle: checks index arithmetic, ring buffers, tails,
+misalignment and the shared symbol-0 chain without a GPU.  Bit-exact."""
+import numpy as np
+import pytest
+
+from emu_lib import aligned
+from oracle_lib import ELEM_SIZE, SIDECAR_PER_ELEM, synth
+
+CASES = [("bf16_weight", 40000), ("f32_master", 20000), ("f32_exp_avg_sq", 10001), ("i8", 1000), ("bf16_norm_gain", 4097),
+         ("f32_uniform_bits", 9000), ("i32", 777), ("f16_weight", 70001), ("bf16_weight", 3), ("f32_master", 1),
+         ("i8", 255), ("i8", 256), ("i8", 257), ("bf16_weight", 2048 + 64), ("f32_master", 64 * 9 + 3)]
+
+
+def make(cases, seed, misalign=None):
+    tensors, es, spe, dts = [], [], [], []
+    for i, (kind, n) in enumerate(cases):
+        raw, dt = synth(kind, n, seed + i)
+        m = 0 if misalign is None else misalign[i % len(misalign)] * ELEM_SIZE[dt]
+        a = aligned(raw.size + 64)[m:m + raw.size]
+        a[:] = raw
+        tensors.append(a); es.append(ELEM_SIZE[dt]); spe.append(SIDECAR_PER_ELEM[dt]); dts.append(dt)
+    return tensors, es, spe, dts
+
+
+@pytest.mark.parametrize("misalign", [None, [1, 0, 3, 2]])
+def test_split_hist_encode_decode(emu, oracle, misalign):
+    tensors, es, spe, dts = make(CASES, 1, misalign)
+    side, hist = emu.split_hist(tensors, es, spe)
+    off, tabs, masked_all = 0, [], []
+    for i, a in enumerate(tensors):
+        m, s = (oracle.split(a, dts[i]) if spe[i] else (a.copy(), np.zeros(0, np.uint8)))
+        assert np.array_equal(side[off:off + s.size], s), i
+        off += s.size
+        h = oracle.byte_histogram(m)
+        hh = hist[i].copy()
+        hh[0] += a.size // es[i] * spe[i]
+        assert np.array_equal(hh, h), i
+        tabs.append(oracle.normalize(h, False))
+        masked_all.append(m)
+    nf, cf = np.stack([t[0] for t in tabs]), np.stack([t[1] for t in tabs])
+    payload, poff, hdrs, raw, st = emu.encode(tensors, es, spe, list(range(len(tensors))), nf, cf)
+    assert st == 0
+    for i in range(len(tensors)):
+        p, hd, r = oracle.compress_tensor(masked_all[i], *tabs[i][:3])
+        got = payload[int(poff[i]):int(poff[i + 1])]
+        assert bool(raw[i]) == r, i
+        assert np.array_equal(got, p), i
+        assert np.array_equal(hdrs[i], hd), i
+    for dst_mis in (0, 4):
+        outs, status = emu.decode([a.size for a in tensors], es, spe, list(range(len(tensors))), nf, cf, hdrs, payload,
+                                  poff, raw, side, check_zero=1, dst_misalign=dst_mis)
+        assert not status.any()
+        for o, a in zip(outs, tensors):
+            assert np.array_equal(o, a)
+
+
+def test_shared_and_degenerate_tables(emu, oracle):
+    """Members encoded with an anchor's full-alphabet table (incl. tables that do not sum
+    to 4096, and symbols the table lacks), and a passthrough tensor."""
+    tensors, es, spe, dts = make([("bf16_weight", 30000), ("bf16_weight", 20000), ("f32_master", 5000),
+                                  ("i8", 3000), ("f32_uniform_bits", 3000)], 9)
+    masked = [oracle.split(a, d)[0] if s else a.copy() for a, d, s in zip(tensors, dts, spe)]
+    t_anchor = oracle.normalize(oracle.byte_histogram(masked[0]), True)      # sums past 4096
+    t_f32 = oracle.normalize(oracle.byte_histogram(masked[2]), True, repaired=True)
+    hist_few = np.zeros(256, np.uint32); hist_few[:4] = [100, 50, 20, 3]     # lacks most symbols -> escapes
+    t_few = oracle.normalize(hist_few, False)
+    hist_skew = np.ones(256, np.uint32); hist_skew[0] = 10 ** 6                # every other symbol costs 12 bits
+    t_noise = oracle.normalize(hist_skew, False)
+    tabs = [t_anchor, t_f32, t_few, t_noise]
+    table_idx = [0, 0, 1, 3, 2]
+    nf, cf = np.stack([t[0] for t in tabs]), np.stack([t[1] for t in tabs])
+    payload, poff, hdrs, raw, st = emu.encode(tensors, es, spe, table_idx, nf, cf)
+    for i in range(len(tensors)):
+        p, hd, r = oracle.compress_tensor(masked[i], *tabs[table_idx[i]][:3])
+        assert bool(raw[i]) == r, i
+        assert np.array_equal(payload[int(poff[i]):int(poff[i + 1])], p), i
+        assert np.array_equal(hdrs[i], hd), i
+    assert raw[3] == 1  # random bytes under a skewed table expand: the passthrough rule stores them raw
+    side = emu.split_hist(tensors, es, spe)[0]
+    outs, status = emu.decode([a.size for a in tensors[2:4]], es[2:4], spe[2:4], [1, 3], nf, cf, hdrs[2:4],
+                              payload, poff[2:4], raw[2:4], side[50000:])
+    assert not status.any()
+    assert np.array_equal(outs[0], tensors[2])       # repaired shared table decodes
+    assert np.array_equal(outs[1], tensors[3])       # raw passthrough restores
+
+
+def test_stage_kernels(emu, oracle):
+    for kind, n, mis in [("bf16_weight", 10007, 0), ("f32_master", 4099, 0), ("f16_weight", 4000, 2), ("f32_master", 512, 4)]:
+        raw, dt = synth(kind, n, 3)
+        m, s = emu.split(raw, ELEM_SIZE[dt], SIDECAR_PER_ELEM[dt], misalign=mis)
+        m_ref, s_ref = oracle.split(raw, dt)
+        assert np.array_equal(m, m_ref) and np.array_equal(s, s_ref)
+        assert np.array_equal(emu.byte_histogram(m_ref, misalign=mis + 1), oracle.byte_histogram(m_ref))
+
+
+def test_stats_kernel(emu, oracle):
+    cases = [("bf16_weight", 5000), ("f32_master", 4099), ("f16_weight", 2048), ("i8", 300), ("i32", 1000),
+             ("bf16_norm_gain", 513), ("f32_exp_avg_sq", 256), ("f32_master", 1)]
+    tensors, es, spe, dts = make(cases, 4)
+    for bins in (256, 64):
+        res = emu.stats(tensors, [a.size // e for a, e in zip(tensors, es)], dts, bins=bins)
+        for i, a in enumerate(tensors):
+            h, mom, mm = oracle.tensor_stats(a, dts[i], bins)
+            assert np.array_equal(res[i][0], h), i
+            assert np.array_equal(res[i][1].view(np.uint32), mom.view(np.uint32)), i
+            assert np.array_equal(res[i][2].view(np.uint32), mm.view(np.uint32)), i
+            assert res[i][3][4] == np.float32(mm[1] - mm[0])

@@ -28,6 +28,7 @@ def dev_bytes(arr, misalign=0):
     buf = torch.zeros(a.size + misalign + 64, dtype=torch.uint8, device="cuda")
     view = buf[misalign:misalign + a.size]
     view.copy_(torch.from_numpy(a.copy()))
+    torch.cuda.synchronize()  # the library works on its own stream
     return view
 
 
