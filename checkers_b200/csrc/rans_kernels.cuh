@@ -29,6 +29,13 @@ struct ZeroRec {
 
 constexpr uint32_t kTeam = 64;  // threads per tensor
 
+// Byte of the thread's 32-bit row word that chain k encodes.  NV = chains per
+// thread; B0 = byte of the first chain when NV == 2 (2 for fp32, 1 for bf16/fp16).
+template <int NV, int B0>
+__device__ __forceinline__ constexpr uint32_t chain_byte(int k) {
+    return NV == 4 ? (uint32_t)k : (k == 0 ? (uint32_t)B0 : 3u);
+}
+
 // shared memory of one encode team: table (256 x 16 B) + 32-byte output ring per chain
 template <int NV>
 struct EncSmem {
@@ -84,7 +91,7 @@ __device__ __forceinline__ uint32_t load_row_word(const uint8_t* p, bool aligned
     return (uint32_t)p[0] | ((uint32_t)p[1] << 8) | ((uint32_t)p[2] << 16) | ((uint32_t)p[3] << 24);
 }
 
-template <int NV>
+template <int NV, int B0>
 __device__ __forceinline__ void encode_tensor(const TensorDesc& d, uint32_t ti, const EncEntry* __restrict__ tables,
                                               uint8_t* __restrict__ scratch, LaneHeader* __restrict__ hdrs,
                                               unsigned long long* __restrict__ lane_src,
@@ -98,16 +105,6 @@ __device__ __forceinline__ void encode_tensor(const TensorDesc& d, uint32_t ti, 
         sm->tab[j * 4 + i] = make_uint4(e.rcp, e.freq_shift, e.bias, e.cmpl);
     }
     __syncthreads();
-
-    // byte position inside the thread's word for each of its chains
-    uint32_t bpos[NV];
-    if (NV == 4) {
-#pragma unroll
-        for (int k = 0; k < NV; ++k) bpos[k] = k;
-    } else {
-        bpos[0] = d.es == 4 ? 2u : 1u;
-        bpos[NV - 1] = 3u;
-    }
 
     uint32_t x[NV], wpos[NV], flushed[NV];
     uint8_t* region[NV];
@@ -132,7 +129,7 @@ __device__ __forceinline__ void encode_tensor(const TensorDesc& d, uint32_t ti, 
     if (tail) {
 #pragma unroll
         for (int k = 0; k < NV; ++k) {
-            const uint32_t t = 4 * j + bpos[k];
+            const uint32_t t = 4 * j + chain_byte<NV, B0>(k);
             if (t < tail) enc_step(d.src[(full_rows << 8) + t], sm->tab, x[k], wpos[k], ringb[k]);
         }
     }
@@ -143,7 +140,7 @@ __device__ __forceinline__ void encode_tensor(const TensorDesc& d, uint32_t ti, 
         --r;
         const uint32_t w = load_row_word(col + (r << 8), aligned4);
 #pragma unroll
-        for (int k = 0; k < NV; ++k) enc_step((w >> (8 * bpos[k])) & 0xFF, sm->tab, x[k], wpos[k], ringb[k]);
+        for (int k = 0; k < NV; ++k) enc_step((w >> (8 * chain_byte<NV, B0>(k))) & 0xFF, sm->tab, x[k], wpos[k], ringb[k]);
     }
 #pragma unroll
     for (int k = 0; k < NV; ++k) enc_flush(wpos[k], flushed[k], ringw[k], region[k]);
@@ -157,7 +154,7 @@ __device__ __forceinline__ void encode_tensor(const TensorDesc& d, uint32_t ti, 
 #pragma unroll
         for (int u = 7; u >= 0; --u) {
 #pragma unroll
-            for (int k = 0; k < NV; ++k) enc_step((w[u] >> (8 * bpos[k])) & 0xFF, sm->tab, x[k], wpos[k], ringb[k]);
+            for (int k = 0; k < NV; ++k) enc_step((w[u] >> (8 * chain_byte<NV, B0>(k))) & 0xFF, sm->tab, x[k], wpos[k], ringb[k]);
         }
 #pragma unroll
         for (int k = 0; k < NV; ++k) enc_flush(wpos[k], flushed[k], ringw[k], region[k]);
@@ -168,7 +165,7 @@ __device__ __forceinline__ void encode_tensor(const TensorDesc& d, uint32_t ti, 
     for (int k = 0; k < NV; ++k) {
         for (uint32_t p = wpos[k]; p < (flushed[k] << 4); ++p)
             region[k][p] = ringb[k][((p >> 2) & 7) * (kTeam * 4) + (p & 3)];
-        const uint32_t t = 4 * j + bpos[k];
+        const uint32_t t = 4 * j + chain_byte<NV, B0>(k);
         LaneHeader h;
         h.final_state = x[k];
         h.byte_count = d.chunk_stride - wpos[k];
@@ -183,7 +180,7 @@ __device__ __forceinline__ void encode_tensor(const TensorDesc& d, uint32_t ti, 
         const unsigned long long zbase = d.scratch_off + (unsigned long long)kTeam * NV * d.chunk_stride;
 #pragma unroll
         for (uint32_t b = 0; b < 4; ++b) {
-            if (b == bpos[0] || b == 3u) continue;
+            if (b == (uint32_t)B0 || b == 3u) continue;
             const uint32_t t = 4 * j + b;
             const unsigned long long cnt = B > t ? (B - t + kLanes - 1) / kLanes : 0;
             LaneHeader h;
@@ -214,10 +211,12 @@ __global__ void __launch_bounds__(kTeam) rans_encode_kernel(const TensorDesc* __
     CHK_DYN_SMEM(smem);
     for (uint32_t ti = blockIdx.x; ti < n_tensors; ti += gridDim.x) {
         const TensorDesc d = descs[ti];
-        if (d.spe * 2 == d.es)
-            encode_tensor<2>(d, ti, tables, scratch, hdrs, lane_src, zrec, smem);
+        if (d.es == 4 && d.spe == 2)
+            encode_tensor<2, 2>(d, ti, tables, scratch, hdrs, lane_src, zrec, smem);
+        else if (d.es == 2 && d.spe == 1)
+            encode_tensor<2, 1>(d, ti, tables, scratch, hdrs, lane_src, zrec, smem);
         else
-            encode_tensor<4>(d, ti, tables, scratch, hdrs, lane_src, zrec, smem);
+            encode_tensor<4, 0>(d, ti, tables, scratch, hdrs, lane_src, zrec, smem);
     }
 }
 
@@ -455,7 +454,7 @@ __device__ __forceinline__ uint32_t dec_step(DecChain& c, const uint32_t* dtab, 
     return e & 0xFFu;
 }
 
-template <int NV>
+template <int NV, int B0>
 __device__ __forceinline__ void decode_tensor(const TensorDesc& d, uint32_t ti,
                                               const uint32_t* __restrict__ freq_tables,
                                               const uint32_t* __restrict__ cum_tables,
@@ -481,16 +480,8 @@ __device__ __forceinline__ void decode_tensor(const TensorDesc& d, uint32_t ti,
         sm->dtab[slot] = lo | ((fq[lo] - 1) << 8) | ((slot - sm->cum[lo]) << 20);
     }
 
-    uint32_t bpos[NV];
-    if (NV == 4) {
-#pragma unroll
-        for (int k = 0; k < NV; ++k) bpos[k] = k;
-    } else {
-        bpos[0] = d.es == 4 ? 2u : 1u;
-        bpos[NV - 1] = 3u;
-    }
     // mask of the word's bytes that come from the codec (the rest come from the sidecar)
-    const uint32_t keep = NV == 4 ? 0xFFFFFFFFu : (d.es == 4 ? 0xFFFF0000u : 0xFF00FF00u);
+    constexpr uint32_t keep = NV == 4 ? 0xFFFFFFFFu : (B0 == 2 ? 0xFFFF0000u : 0xFF00FF00u);
 
     DecChain ch[NV];
     uint32_t* ringw[NV];
@@ -498,7 +489,7 @@ __device__ __forceinline__ void decode_tensor(const TensorDesc& d, uint32_t ti,
     unsigned long long cnt[NV];
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
-        const uint32_t t = 4 * j + bpos[k];
+        const uint32_t t = 4 * j + chain_byte<NV, B0>(k);
         cnt[k] = B > t ? (B - t + kLanes - 1) / kLanes : 0;
         const LaneHeader h = hdrs[(size_t)ti * kLanes + t];
         const unsigned long long p_abs = d.payload_off + h.buf_offset;
@@ -529,7 +520,7 @@ __device__ __forceinline__ void decode_tensor(const TensorDesc& d, uint32_t ti,
         const uint8_t* sp = sidecar + d.sidecar_off + (r << 7) + 2 * j;
         const uint32_t s = side2 ? (uint32_t)*reinterpret_cast<const uint16_t*>(sp)
                                  : ((uint32_t)sp[0] | ((uint32_t)sp[1] << 8));
-        return d.es == 4 ? s : ((s & 0xFFu) | ((s & 0xFF00u) << 8));
+        return B0 == 2 ? s : ((s & 0xFFu) | ((s & 0xFF00u) << 8));
     };
     auto store_word = [&](unsigned long long r, uint32_t w) {
         uint8_t* p = col + (r << 8);
@@ -553,7 +544,7 @@ __device__ __forceinline__ void decode_tensor(const TensorDesc& d, uint32_t ti,
         for (int u = 0; u < 8; ++u) {
             uint32_t acc = 0;
 #pragma unroll
-            for (int k = 0; k < NV; ++k) acc |= dec_step(ch[k], sm->dtab, ringb[k]) << (8 * bpos[k]);
+            for (int k = 0; k < NV; ++k) acc |= dec_step(ch[k], sm->dtab, ringb[k]) << (8 * chain_byte<NV, B0>(k));
             w[u] = (acc & keep) | side[u];
         }
 #pragma unroll
@@ -567,14 +558,14 @@ __device__ __forceinline__ void decode_tensor(const TensorDesc& d, uint32_t ti,
     for (; r < full_rows; ++r) {
         uint32_t acc = 0;
 #pragma unroll
-        for (int k = 0; k < NV; ++k) acc |= dec_step(ch[k], sm->dtab, ringb[k]) << (8 * bpos[k]);
+        for (int k = 0; k < NV; ++k) acc |= dec_step(ch[k], sm->dtab, ringb[k]) << (8 * chain_byte<NV, B0>(k));
         store_word(r, (acc & keep) | side_word(r));
     }
     if (tail) {
         uint32_t acc = 0;
 #pragma unroll
         for (int k = 0; k < NV; ++k)
-            if (4 * j + bpos[k] < tail) acc |= dec_step(ch[k], sm->dtab, ringb[k]) << (8 * bpos[k]);
+            if (4 * j + chain_byte<NV, B0>(k) < tail) acc |= dec_step(ch[k], sm->dtab, ringb[k]) << (8 * chain_byte<NV, B0>(k));
 #pragma unroll
         for (uint32_t b = 0; b < 4; ++b) {
             const uint32_t t = 4 * j + b;
@@ -595,7 +586,7 @@ __device__ __forceinline__ void decode_tensor(const TensorDesc& d, uint32_t ti,
         // optional: replay the lanes that only carry zeroed bytes and check their end state
 #pragma unroll
         for (uint32_t b = 0; b < 4; ++b) {
-            if (b == bpos[0] || b == 3u) continue;
+            if (b == (uint32_t)B0 || b == 3u) continue;
             const uint32_t t = 4 * j + b;
             const unsigned long long n = B > t ? (B - t + kLanes - 1) / kLanes : 0;
             const LaneHeader h = hdrs[(size_t)ti * kLanes + t];
@@ -640,10 +631,12 @@ __global__ void __launch_bounds__(kTeam) rans_decode_kernel(const TensorDesc* __
             }
             continue;
         }
-        if (d.spe * 2 == d.es)
-            decode_tensor<2>(d, ti, freq_tables, cum_tables, hdrs, payload, sidecar, check_zero_lanes, status, smem);
+        if (d.es == 4 && d.spe == 2)
+            decode_tensor<2, 2>(d, ti, freq_tables, cum_tables, hdrs, payload, sidecar, check_zero_lanes, status, smem);
+        else if (d.es == 2 && d.spe == 1)
+            decode_tensor<2, 1>(d, ti, freq_tables, cum_tables, hdrs, payload, sidecar, check_zero_lanes, status, smem);
         else
-            decode_tensor<4>(d, ti, freq_tables, cum_tables, hdrs, payload, sidecar, check_zero_lanes, status, smem);
+            decode_tensor<4, 0>(d, ti, freq_tables, cum_tables, hdrs, payload, sidecar, check_zero_lanes, status, smem);
     }
 }
 
