@@ -402,18 +402,16 @@ static void compress(Context* c, bool host_images) {
 
     // ---- stage 2: encode
     {
-        if (!c->enc_attr_set) {
-            CHK_CUDA(cudaFuncSetAttribute(rans_encode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          (int)kEncSmemBytes));
-            c->enc_attr_set = true;
-        }
         // the shared symbol-0 chain of every tensor first (one thread each), then the value lanes
         zero_lane_kernel<<<(uint32_t)((W + 127) / 128), 128, 0, s>>>(
             static_cast<const TensorDesc*>(c->d_descs.p), static_cast<const EncEntry*>(c->d_enc.p),
             static_cast<uint8_t*>(c->d_scratch.p), static_cast<ZeroRec*>(c->d_zrec.p), (uint32_t)W);
         CHK_CUDA(cudaGetLastError());
+        bool any_int = false;
+        for (size_t i = 0; i < W && !any_int; ++i) any_int = c->work[i].spe * 2 != c->work[i].es;
         const uint32_t grid = (uint32_t)(W < 148u * 256u ? W : 148u * 256u);
-        rans_encode_kernel<<<grid, kTeam, kEncSmemBytes, s>>>(
+        auto kernel = any_int ? rans_encode_kernel<true> : rans_encode_kernel<false>;
+        kernel<<<grid, kTeam, any_int ? sizeof(EncSmem<4>) : sizeof(EncSmem<2>), s>>>(
             static_cast<const TensorDesc*>(c->d_descs.p), static_cast<const EncEntry*>(c->d_enc.p),
             static_cast<uint8_t*>(c->d_scratch.p), static_cast<LaneHeader*>(c->d_hdrs.p),
             static_cast<unsigned long long*>(c->d_lsrc.p), static_cast<const ZeroRec*>(c->d_zrec.p), (uint32_t)W);
@@ -588,14 +586,15 @@ static void run_decode(Context* c, size_t W, const uint8_t* d_payload, const uin
     dev_ensure(c, c->d_status, W * 4 + 256);
     pin_ensure(c->h_status, W * 4 + 256);
     CHK_CUDA(cudaMemsetAsync(c->d_status.p, 0, W * 4, s));
-    if (!c->dec_attr_set) {
-        CHK_CUDA(cudaFuncSetAttribute(rans_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      (int)kDecSmemBytes));
-        c->dec_attr_set = true;
-    }
+    // integer tensors run four chains per thread and need the larger ring area
+    bool any_int = false;
+    const TensorDesc* hd = static_cast<const TensorDesc*>(c->h_descs.p);
+    for (size_t i = 0; i < W && !any_int; ++i) any_int = hd[i].spe * 2 != hd[i].es;
+    const uint32_t smem = any_int ? kDecSmemBytes4 : kDecSmemBytes2;
     CHK_CUDA(cudaEventRecord(c->ev[1], s));
     const uint32_t grid = (uint32_t)(W < 148u * 256u ? W : 148u * 256u);
-    rans_decode_kernel<<<grid, kTeam, kDecSmemBytes, s>>>(static_cast<const TensorDesc*>(c->d_descs.p), d_freq, d_cum,
+    auto kernel = any_int ? rans_decode_kernel<true> : rans_decode_kernel<false>;
+    kernel<<<grid, kTeam, smem, s>>>(static_cast<const TensorDesc*>(c->d_descs.p), d_freq, d_cum,
                                                         d_hdrs, d_payload, d_sidecar, (uint32_t)W,
                                                         c->verify_zero_lanes ? 1u : 0u,
                                                         static_cast<uint32_t*>(c->d_status.p));

@@ -145,12 +145,23 @@ __device__ __forceinline__ void encode_tensor(const TensorDesc& d, uint32_t ti, 
 #pragma unroll
     for (int k = 0; k < NV; ++k) enc_flush(wpos[k], flushed[k], ringw[k], region[k]);
 
-    // full groups of 8 rows, highest first; the 8 loads are issued before the dependent chains run
+    // full groups of 8 rows, highest first.  The words of the NEXT group are
+    // requested before the current group's dependent chains run, so the memory
+    // latency hides behind 8 * NV chain steps.
+    uint32_t nxt[8];
+    if (r >= 8) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u) nxt[u] = load_row_word(col + ((r - 8 + u) << 8), aligned4);
+    }
     while (r >= 8) {
         r -= 8;
         uint32_t w[8];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) w[u] = load_row_word(col + ((r + u) << 8), aligned4);
+        for (int u = 0; u < 8; ++u) w[u] = nxt[u];
+        if (r >= 8) {
+#pragma unroll
+            for (int u = 0; u < 8; ++u) nxt[u] = load_row_word(col + ((r - 8 + u) << 8), aligned4);
+        }
 #pragma unroll
         for (int u = 7; u >= 0; --u) {
 #pragma unroll
@@ -201,7 +212,10 @@ __device__ __forceinline__ void encode_tensor(const TensorDesc& d, uint32_t ti, 
     __syncthreads();  // table and ring are reused by the next tensor
 }
 
-// One team (CTA of 64 threads) per tensor.
+// One team (CTA of 64 threads) per tensor.  kInts = false is the build for
+// batches of float tensors only (two chains per thread, fewer registers, more
+// resident teams); the host picks the variant per batch.
+template <bool kInts>
 __global__ void __launch_bounds__(kTeam) rans_encode_kernel(const TensorDesc* __restrict__ descs,
                                                             const EncEntry* __restrict__ tables,
                                                             uint8_t* __restrict__ scratch,
@@ -215,7 +229,7 @@ __global__ void __launch_bounds__(kTeam) rans_encode_kernel(const TensorDesc* __
             encode_tensor<2, 2>(d, ti, tables, scratch, hdrs, lane_src, zrec, smem);
         else if (d.es == 2 && d.spe == 1)
             encode_tensor<2, 1>(d, ti, tables, scratch, hdrs, lane_src, zrec, smem);
-        else
+        else if (kInts)
             encode_tensor<4, 0>(d, ti, tables, scratch, hdrs, lane_src, zrec, smem);
     }
 }
@@ -406,34 +420,46 @@ __global__ void __launch_bounds__(256) compact_kernel(const TensorDesc* __restri
 template <int NV>
 struct DecSmem {
     uint32_t dtab[kM];
-    uint32_t ring[NV * 8 * kTeam];
+    uint32_t ring[NV * 16 * kTeam];  // 64-byte input ring per chain, word-interleaved across the team
     uint32_t cum[260];
 };
-constexpr uint32_t kDecSmemBytes = sizeof(DecSmem<4>);
+constexpr uint32_t kDecSmemBytes2 = sizeof(DecSmem<2>);  // float tensors only
+constexpr uint32_t kDecSmemBytes4 = sizeof(DecSmem<4>);  // batches that contain integer tensors
 
 struct DecChain {
     uint32_t x;
     uint32_t rel;      // read position relative to blk0 * 16
     uint32_t rel_end;  // where a valid stream ends
-    uint32_t loaded;   // 16-byte blocks fetched so far
+    uint32_t loaded;   // 16-byte blocks requested so far
     uint32_t max_blocks;
     unsigned long long blk0;
+    uint4 pend;        // block requested at the previous check, not yet in the ring
+    bool has_pend;
 };
 
-// Fetch the next aligned 16 bytes of a lane's stream into its 32-byte ring.  A
-// valid stream never needs bytes past its own end; a damaged one could run
-// ahead, so fetching stops one block after the lane's last byte (the lane then
+// A lane reads its stream forward in aligned 16-byte blocks.  A block is
+// REQUESTED at one check point and only moved into the ring at the next one
+// (8 symbols later), so the load latency hides behind decode work; at least 16
+// unread bytes are in the ring whenever a group of 8 symbols starts.
+// A valid stream never needs bytes past its own end; a damaged one could run
+// ahead, so requests stop one block after the lane's last byte (the lane then
 // decodes garbage and fails its end check).
-__device__ __forceinline__ void dec_fetch(DecChain& c, const uint8_t* __restrict__ payload, uint32_t* ring_words) {
+__device__ __forceinline__ void dec_request(DecChain& c, const uint8_t* __restrict__ payload) {
     if (c.loaded < c.max_blocks) {
-        const uint4 v = ld_global_v4(payload + (c.blk0 + c.loaded) * 16);
-        const uint32_t r = (c.loaded & 1) * 4;
-        ring_words[(r + 0) * kTeam] = v.x;
-        ring_words[(r + 1) * kTeam] = v.y;
-        ring_words[(r + 2) * kTeam] = v.z;
-        ring_words[(r + 3) * kTeam] = v.w;
+        c.pend = ld_global_v4(payload + (c.blk0 + c.loaded) * 16);
+        c.has_pend = true;
     }
     ++c.loaded;
+}
+__device__ __forceinline__ void dec_commit(DecChain& c, uint32_t* ring_words) {
+    if (c.has_pend) {
+        const uint32_t r = ((c.loaded - 1) & 3) * 4;
+        ring_words[(r + 0) * kTeam] = c.pend.x;
+        ring_words[(r + 1) * kTeam] = c.pend.y;
+        ring_words[(r + 2) * kTeam] = c.pend.z;
+        ring_words[(r + 3) * kTeam] = c.pend.w;
+        c.has_pend = false;
+    }
 }
 
 __device__ __forceinline__ uint32_t dec_step(DecChain& c, const uint32_t* dtab, const uint8_t* ring_bytes) {
@@ -441,8 +467,8 @@ __device__ __forceinline__ uint32_t dec_step(DecChain& c, const uint32_t* dtab, 
     const uint32_t e = dtab[slot];
     uint32_t x = (((e >> 8) & 0xFFFu) + 1u) * (c.x >> kScaleBits) + (e >> 20);
     const uint32_t r0 = c.rel, r1 = c.rel + 1;
-    const uint32_t b0 = ring_bytes[((r0 >> 2) & 7) * (kTeam * 4) + (r0 & 3)];
-    const uint32_t b1 = ring_bytes[((r1 >> 2) & 7) * (kTeam * 4) + (r1 & 3)];
+    const uint32_t b0 = ring_bytes[((r0 >> 2) & 15) * (kTeam * 4) + (r0 & 3)];
+    const uint32_t b1 = ring_bytes[((r1 >> 2) & 15) * (kTeam * 4) + (r1 & 3)];
     if (x < (1u << 15)) {
         x = (x << 16) | (b0 << 8) | b1;
         c.rel += 2;
@@ -486,11 +512,9 @@ __device__ __forceinline__ void decode_tensor(const TensorDesc& d, uint32_t ti,
     DecChain ch[NV];
     uint32_t* ringw[NV];
     const uint8_t* ringb[NV];
-    unsigned long long cnt[NV];
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
         const uint32_t t = 4 * j + chain_byte<NV, B0>(k);
-        cnt[k] = B > t ? (B - t + kLanes - 1) / kLanes : 0;
         const LaneHeader h = hdrs[(size_t)ti * kLanes + t];
         const unsigned long long p_abs = d.payload_off + h.buf_offset;
         ch[k].x = h.final_state;
@@ -499,11 +523,15 @@ __device__ __forceinline__ void decode_tensor(const TensorDesc& d, uint32_t ti,
         ch[k].rel_end = ch[k].rel + h.byte_count;
         ch[k].max_blocks = ((ch[k].rel_end + 15) >> 4) + 1;
         ch[k].loaded = 0;
-        ringw[k] = sm->ring + (size_t)k * 8 * kTeam + j;
+        ch[k].has_pend = false;
+        ringw[k] = sm->ring + (size_t)k * 16 * kTeam + j;
         ringb[k] = reinterpret_cast<const uint8_t*>(ringw[k]);
-        if (cnt[k]) {
-            dec_fetch(ch[k], payload, ringw[k]);
-            dec_fetch(ch[k], payload, ringw[k]);
+        if (B > t) {  // the lane has symbols: start with three blocks in the ring
+#pragma unroll
+            for (int i = 0; i < 3; ++i) {
+                dec_request(ch[k], payload);
+                dec_commit(ch[k], ringw[k]);
+            }
         }
     }
     __syncthreads();  // table complete
@@ -535,10 +563,19 @@ __device__ __forceinline__ void decode_tensor(const TensorDesc& d, uint32_t ti,
     };
 
     unsigned long long r = 0;
+    uint32_t side_next[8];
+    if (8 <= full_rows) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u) side_next[u] = side_word(u);
+    }
     while (r + 8 <= full_rows) {
         uint32_t side[8];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) side[u] = side_word(r + u);
+        for (int u = 0; u < 8; ++u) side[u] = side_next[u];
+        if (r + 16 <= full_rows) {  // low bytes of the next group, requested ahead of use
+#pragma unroll
+            for (int u = 0; u < 8; ++u) side_next[u] = side_word(r + 8 + u);
+        }
         uint32_t w[8];
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
@@ -550,10 +587,15 @@ __device__ __forceinline__ void decode_tensor(const TensorDesc& d, uint32_t ti,
 #pragma unroll
         for (int u = 0; u < 8; ++u) store_word(r + u, w[u]);
 #pragma unroll
-        for (int k = 0; k < NV; ++k)
-            if (ch[k].rel >= (ch[k].loaded - 1) * 16) dec_fetch(ch[k], payload, ringw[k]);
+        for (int k = 0; k < NV; ++k) {
+            dec_commit(ch[k], ringw[k]);
+            // fewer than 33 unread bytes in the ring: request the next block now
+            if (ch[k].rel + 32 >= ch[k].loaded * 16) dec_request(ch[k], payload);
+        }
         r += 8;
     }
+#pragma unroll
+    for (int k = 0; k < NV; ++k) dec_commit(ch[k], ringw[k]);
     // remaining full rows and the partial row: at most 8 steps per chain
     for (; r < full_rows; ++r) {
         uint32_t acc = 0;
@@ -612,6 +654,8 @@ __device__ __forceinline__ void decode_tensor(const TensorDesc& d, uint32_t ti,
 
 // One team (CTA of 64 threads) per tensor.  Each thread rebuilds one 32-bit word
 // of every row from its decoded bytes and the sidecar and stores it directly.
+// kInts as for the encoder.
+template <bool kInts>
 __global__ void __launch_bounds__(kTeam) rans_decode_kernel(const TensorDesc* __restrict__ descs,
                                                             const uint32_t* __restrict__ freq_tables,  // [T][256]
                                                             const uint32_t* __restrict__ cum_tables,   // [T][257]
@@ -635,7 +679,7 @@ __global__ void __launch_bounds__(kTeam) rans_decode_kernel(const TensorDesc* __
             decode_tensor<2, 2>(d, ti, freq_tables, cum_tables, hdrs, payload, sidecar, check_zero_lanes, status, smem);
         else if (d.es == 2 && d.spe == 1)
             decode_tensor<2, 1>(d, ti, freq_tables, cum_tables, hdrs, payload, sidecar, check_zero_lanes, status, smem);
-        else
+        else if (kInts)
             decode_tensor<4, 0>(d, ti, freq_tables, cum_tables, hdrs, payload, sidecar, check_zero_lanes, status, smem);
     }
 }

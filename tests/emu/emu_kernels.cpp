@@ -100,7 +100,7 @@ uint32_t emu_encode(size_t n, const uint8_t* const* srcs, const uint64_t* n_byte
     emu::launch((unsigned)((n + 127) / 128), 128, 0,
                 [&] { zero_lane_kernel(b.descs.data(), enc.data(), scr, zrec.data(), (uint32_t)n); });
     emu::launch(grid, kTeam, kEncSmemBytes, [&] {
-        rans_encode_kernel(b.descs.data(), enc.data(), scr, hdrs.data(), lsrc.data(), zrec.data(), (uint32_t)n);
+        rans_encode_kernel<true>(b.descs.data(), enc.data(), scr, hdrs.data(), lsrc.data(), zrec.data(), (uint32_t)n);
     });
     emu::launch(grid, 256, 0, [&] { lane_scan_kernel(b.descs.data(), hdrs.data(), psize.data(), loff.data(), (uint32_t)n); });
     emu::launch(1, 1024, 0, [&] { tensor_scan_kernel(b.descs.data(), psize.data(), poff.data(), (uint32_t)n); });
@@ -124,8 +124,8 @@ void emu_decode(size_t n, uint8_t* const* dsts, const uint64_t* n_bytes, const u
         if (raw[i]) b.descs[i].flags |= kFlagRaw;
     }
     std::memset(status_out, 0, n * 4);
-    emu::launch(grid, kTeam, kDecSmemBytes, [&] {
-        rans_decode_kernel(b.descs.data(), nf, cf, (const LaneHeader*)hdrs, payload, sidecar, (uint32_t)n,
+    emu::launch(grid, kTeam, kDecSmemBytes4, [&] {
+        rans_decode_kernel<true>(b.descs.data(), nf, cf, (const LaneHeader*)hdrs, payload, sidecar, (uint32_t)n,
                            check_zero_lanes, status_out);
     });
 }
