@@ -410,7 +410,17 @@ static void compress(Context* c, bool host_images) {
         bool any_int = false;
         for (size_t i = 0; i < W && !any_int; ++i) any_int = c->work[i].spe * 2 != c->work[i].es;
         const uint32_t grid = (uint32_t)(W < 148u * 256u ? W : 148u * 256u);
-        auto kernel = any_int ? rans_encode_kernel<true> : rans_encode_kernel<false>;
+        // A tensor can only meet a symbol its table lacks when it borrows another tensor's
+        // table; the reference builds shared tables over the full alphabet, so this is
+        // normally false and the kernel without the escape test runs.
+        bool need_escape = false;
+        for (size_t i = 0; i < W && !need_escape; ++i) {
+            if (c->work[i].owns) continue;
+            const FreqTable& ft = c->tables[c->work[i].table];
+            for (int sy = 0; sy < 256 && !need_escape; ++sy) need_escape = ft.norm_freq[sy] == 0;
+        }
+        auto kernel = any_int ? (need_escape ? rans_encode_kernel<true, true> : rans_encode_kernel<true, false>)
+                              : (need_escape ? rans_encode_kernel<false, true> : rans_encode_kernel<false, false>);
         kernel<<<grid, kTeam, any_int ? sizeof(EncSmem<4>) : sizeof(EncSmem<2>), s>>>(
             static_cast<const TensorDesc*>(c->d_descs.p), static_cast<const EncEntry*>(c->d_enc.p),
             static_cast<uint8_t*>(c->d_scratch.p), static_cast<LaneHeader*>(c->d_hdrs.p),

@@ -36,22 +36,25 @@ __device__ __forceinline__ constexpr uint32_t chain_byte(int k) {
     return NV == 4 ? (uint32_t)k : (k == 0 ? (uint32_t)B0 : 3u);
 }
 
-// shared memory of one encode team: table (256 x 16 B) + 32-byte output ring per chain
+// Shared memory of one encode team: table (256 x 16 B) + a 32-byte output ring
+// per chain.  A ring is 8 contiguous words; rings are 9 words apart so that the
+// 32 lanes of a warp writing the same ring position hit 32 different banks.
+constexpr uint32_t kEncRingWords = 9;
 template <int NV>
 struct EncSmem {
     uint4 tab[256];
-    uint32_t ring[NV * 8 * kTeam];
+    uint32_t ring[NV * kTeam * kEncRingWords];
 };
-constexpr uint32_t kEncSmemBytes = sizeof(EncSmem<4>);
 
 // One encode step of one chain: renormalise (at most two bytes, low byte first,
-// written downward) and advance the state.  `ring` is the chain's word column.
+// written downward) and advance the state.  kEscape = false drops the test for
+// symbols that are missing from the table (the host proves there are none).
+template <bool kEscape>
 __device__ __forceinline__ void enc_step(uint32_t sym, const uint4* tab, uint32_t& x, uint32_t& wpos, uint8_t* ring_bytes) {
     const uint4 e = tab[sym];
-    const uint32_t f = e.y & 0xFFFFu;
-    if (f == 0) {  // symbol not in the table: raw escape byte, state untouched
+    if (kEscape && e.y == 0) {  // symbol not in the table: raw escape byte, state untouched
         --wpos;
-        ring_bytes[((wpos >> 2) & 7) * (kTeam * 4) + (wpos & 3)] = (uint8_t)sym;
+        ring_bytes[wpos & 31] = (uint8_t)sym;
         return;
     }
     const uint32_t xmax = e.y << 19;  // freq * 2^19 (the shift field falls off the top)
@@ -59,13 +62,14 @@ __device__ __forceinline__ void enc_step(uint32_t sym, const uint4* tab, uint32_
     const bool e2 = (x >> 8) >= xmax;
     if (e1) {
         --wpos;
-        ring_bytes[((wpos >> 2) & 7) * (kTeam * 4) + (wpos & 3)] = (uint8_t)x;
+        ring_bytes[wpos & 31] = (uint8_t)x;
+        x >>= 8;
     }
     if (e2) {
         --wpos;
-        ring_bytes[((wpos >> 2) & 7) * (kTeam * 4) + (wpos & 3)] = (uint8_t)(x >> 8);
+        ring_bytes[wpos & 31] = (uint8_t)x;
+        x >>= 8;
     }
-    x >>= ((uint32_t)e1 + (uint32_t)e2) * 8;
     const uint32_t q = __umulhi(x, e.x) >> (e.y >> 16);
     x = x + q * e.w + e.z;
 }
@@ -76,12 +80,8 @@ __device__ __forceinline__ void enc_flush(uint32_t wpos, uint32_t& flushed, cons
     const uint32_t done_to = (wpos + 15) >> 4;
     if (done_to < flushed) {
         const uint32_t b = flushed - 1;
-        uint4 v;
-        v.x = ring_words[((b * 4 + 0) & 7) * kTeam];
-        v.y = ring_words[((b * 4 + 1) & 7) * kTeam];
-        v.z = ring_words[((b * 4 + 2) & 7) * kTeam];
-        v.w = ring_words[((b * 4 + 3) & 7) * kTeam];
-        *reinterpret_cast<uint4*>(region + (size_t)b * 16) = v;
+        const uint32_t* w = ring_words + (b & 1) * 4;
+        *reinterpret_cast<uint4*>(region + (size_t)b * 16) = make_uint4(w[0], w[1], w[2], w[3]);
         flushed = b;
     }
 }
@@ -91,7 +91,7 @@ __device__ __forceinline__ uint32_t load_row_word(const uint8_t* p, bool aligned
     return (uint32_t)p[0] | ((uint32_t)p[1] << 8) | ((uint32_t)p[2] << 16) | ((uint32_t)p[3] << 24);
 }
 
-template <int NV, int B0>
+template <int NV, int B0, bool kEscape>
 __device__ __forceinline__ void encode_tensor(const TensorDesc& d, uint32_t ti, const EncEntry* __restrict__ tables,
                                               uint8_t* __restrict__ scratch, LaneHeader* __restrict__ hdrs,
                                               unsigned long long* __restrict__ lane_src,
@@ -116,8 +116,8 @@ __device__ __forceinline__ void encode_tensor(const TensorDesc& d, uint32_t ti, 
         wpos[k] = d.chunk_stride;
         flushed[k] = d.chunk_stride >> 4;
         region[k] = scratch + d.scratch_off + (size_t)(j * NV + k) * d.chunk_stride;
-        ringw[k] = sm->ring + (size_t)k * 8 * kTeam + j;
-        ringb[k] = reinterpret_cast<uint8_t*>(sm->ring + (size_t)k * 8 * kTeam + j);
+        ringw[k] = sm->ring + (size_t)(k * kTeam + j) * kEncRingWords;
+        ringb[k] = reinterpret_cast<uint8_t*>(sm->ring + (size_t)(k * kTeam + j) * kEncRingWords);
     }
 
     const unsigned long long full_rows = B >> 8;
@@ -130,7 +130,7 @@ __device__ __forceinline__ void encode_tensor(const TensorDesc& d, uint32_t ti, 
 #pragma unroll
         for (int k = 0; k < NV; ++k) {
             const uint32_t t = 4 * j + chain_byte<NV, B0>(k);
-            if (t < tail) enc_step(d.src[(full_rows << 8) + t], sm->tab, x[k], wpos[k], ringb[k]);
+            if (t < tail) enc_step<kEscape>(d.src[(full_rows << 8) + t], sm->tab, x[k], wpos[k], ringb[k]);
         }
     }
     // rows above the last multiple of 8, one at a time: with the partial row at most 8 steps
@@ -140,7 +140,7 @@ __device__ __forceinline__ void encode_tensor(const TensorDesc& d, uint32_t ti, 
         --r;
         const uint32_t w = load_row_word(col + (r << 8), aligned4);
 #pragma unroll
-        for (int k = 0; k < NV; ++k) enc_step((w >> (8 * chain_byte<NV, B0>(k))) & 0xFF, sm->tab, x[k], wpos[k], ringb[k]);
+        for (int k = 0; k < NV; ++k) enc_step<kEscape>((w >> (8 * chain_byte<NV, B0>(k))) & 0xFF, sm->tab, x[k], wpos[k], ringb[k]);
     }
 #pragma unroll
     for (int k = 0; k < NV; ++k) enc_flush(wpos[k], flushed[k], ringw[k], region[k]);
@@ -165,7 +165,7 @@ __device__ __forceinline__ void encode_tensor(const TensorDesc& d, uint32_t ti, 
 #pragma unroll
         for (int u = 7; u >= 0; --u) {
 #pragma unroll
-            for (int k = 0; k < NV; ++k) enc_step((w[u] >> (8 * chain_byte<NV, B0>(k))) & 0xFF, sm->tab, x[k], wpos[k], ringb[k]);
+            for (int k = 0; k < NV; ++k) enc_step<kEscape>((w[u] >> (8 * chain_byte<NV, B0>(k))) & 0xFF, sm->tab, x[k], wpos[k], ringb[k]);
         }
 #pragma unroll
         for (int k = 0; k < NV; ++k) enc_flush(wpos[k], flushed[k], ringw[k], region[k]);
@@ -175,7 +175,7 @@ __device__ __forceinline__ void encode_tensor(const TensorDesc& d, uint32_t ti, 
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
         for (uint32_t p = wpos[k]; p < (flushed[k] << 4); ++p)
-            region[k][p] = ringb[k][((p >> 2) & 7) * (kTeam * 4) + (p & 3)];
+            region[k][p] = ringb[k][p & 31];
         const uint32_t t = 4 * j + chain_byte<NV, B0>(k);
         LaneHeader h;
         h.final_state = x[k];
@@ -215,7 +215,7 @@ __device__ __forceinline__ void encode_tensor(const TensorDesc& d, uint32_t ti, 
 // One team (CTA of 64 threads) per tensor.  kInts = false is the build for
 // batches of float tensors only (two chains per thread, fewer registers, more
 // resident teams); the host picks the variant per batch.
-template <bool kInts>
+template <bool kInts, bool kEscape>
 __global__ void __launch_bounds__(kTeam) rans_encode_kernel(const TensorDesc* __restrict__ descs,
                                                             const EncEntry* __restrict__ tables,
                                                             uint8_t* __restrict__ scratch,
@@ -226,11 +226,11 @@ __global__ void __launch_bounds__(kTeam) rans_encode_kernel(const TensorDesc* __
     for (uint32_t ti = blockIdx.x; ti < n_tensors; ti += gridDim.x) {
         const TensorDesc d = descs[ti];
         if (d.es == 4 && d.spe == 2)
-            encode_tensor<2, 2>(d, ti, tables, scratch, hdrs, lane_src, zrec, smem);
+            encode_tensor<2, 2, kEscape>(d, ti, tables, scratch, hdrs, lane_src, zrec, smem);
         else if (d.es == 2 && d.spe == 1)
-            encode_tensor<2, 1>(d, ti, tables, scratch, hdrs, lane_src, zrec, smem);
+            encode_tensor<2, 1, kEscape>(d, ti, tables, scratch, hdrs, lane_src, zrec, smem);
         else if (kInts)
-            encode_tensor<4, 0>(d, ti, tables, scratch, hdrs, lane_src, zrec, smem);
+            encode_tensor<4, 0, kEscape>(d, ti, tables, scratch, hdrs, lane_src, zrec, smem);
     }
 }
 
@@ -420,7 +420,9 @@ __global__ void __launch_bounds__(256) compact_kernel(const TensorDesc* __restri
 template <int NV>
 struct DecSmem {
     uint32_t dtab[kM];
-    uint32_t ring[NV * 16 * kTeam];  // 64-byte input ring per chain, word-interleaved across the team
+    // 64-byte input ring per chain plus one word whose first byte mirrors ring byte 0
+    // (so byte p+1 is always at address p+1); 17 words apart keeps a warp conflict-free
+    uint32_t ring[NV * kTeam * 17];
     uint32_t cum[260];
 };
 constexpr uint32_t kDecSmemBytes2 = sizeof(DecSmem<2>);  // float tensors only
@@ -454,10 +456,11 @@ __device__ __forceinline__ void dec_request(DecChain& c, const uint8_t* __restri
 __device__ __forceinline__ void dec_commit(DecChain& c, uint32_t* ring_words) {
     if (c.has_pend) {
         const uint32_t r = ((c.loaded - 1) & 3) * 4;
-        ring_words[(r + 0) * kTeam] = c.pend.x;
-        ring_words[(r + 1) * kTeam] = c.pend.y;
-        ring_words[(r + 2) * kTeam] = c.pend.z;
-        ring_words[(r + 3) * kTeam] = c.pend.w;
+        ring_words[r + 0] = c.pend.x;
+        ring_words[r + 1] = c.pend.y;
+        ring_words[r + 2] = c.pend.z;
+        ring_words[r + 3] = c.pend.w;
+        if (r == 0) ring_words[16] = c.pend.x;  // mirror of byte 0 behind byte 63
         c.has_pend = false;
     }
 }
@@ -466,9 +469,9 @@ __device__ __forceinline__ uint32_t dec_step(DecChain& c, const uint32_t* dtab, 
     const uint32_t slot = c.x & (kM - 1);
     const uint32_t e = dtab[slot];
     uint32_t x = (((e >> 8) & 0xFFFu) + 1u) * (c.x >> kScaleBits) + (e >> 20);
-    const uint32_t r0 = c.rel, r1 = c.rel + 1;
-    const uint32_t b0 = ring_bytes[((r0 >> 2) & 15) * (kTeam * 4) + (r0 & 3)];
-    const uint32_t b1 = ring_bytes[((r1 >> 2) & 15) * (kTeam * 4) + (r1 & 3)];
+    const uint8_t* rp = ring_bytes + (c.rel & 63);
+    const uint32_t b0 = rp[0];
+    const uint32_t b1 = rp[1];
     if (x < (1u << 15)) {
         x = (x << 16) | (b0 << 8) | b1;
         c.rel += 2;
@@ -524,7 +527,7 @@ __device__ __forceinline__ void decode_tensor(const TensorDesc& d, uint32_t ti,
         ch[k].max_blocks = ((ch[k].rel_end + 15) >> 4) + 1;
         ch[k].loaded = 0;
         ch[k].has_pend = false;
-        ringw[k] = sm->ring + (size_t)k * 16 * kTeam + j;
+        ringw[k] = sm->ring + (size_t)(k * kTeam + j) * 17;
         ringb[k] = reinterpret_cast<const uint8_t*>(ringw[k]);
         if (B > t) {  // the lane has symbols: start with three blocks in the ring
 #pragma unroll

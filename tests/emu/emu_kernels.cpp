@@ -79,7 +79,7 @@ void emu_split_hist(size_t n, const uint8_t* const* srcs, const uint64_t* n_byte
 uint32_t emu_encode(size_t n, const uint8_t* const* srcs, const uint64_t* n_bytes, const uint32_t* es,
                     const uint32_t* spe, const uint32_t* table_idx, size_t n_tables, const uint32_t* nf,
                     const uint32_t* cf, uint8_t* payload_out, uint64_t* payload_off_out, uint32_t* hdrs_out,
-                    uint8_t* raw_out, uint32_t grid) {
+                    uint8_t* raw_out, uint32_t grid, uint32_t float_only) {
     Batch b = make_batch(n, srcs, nullptr, n_bytes, es, spe, table_idx, nullptr);
     std::vector<EncEntry> enc(n_tables * 256);
     for (size_t t = 0; t < n_tables; ++t) {
@@ -99,9 +99,16 @@ uint32_t emu_encode(size_t n, const uint8_t* const* srcs, const uint64_t* n_byte
     uint32_t status = 0;
     emu::launch((unsigned)((n + 127) / 128), 128, 0,
                 [&] { zero_lane_kernel(b.descs.data(), enc.data(), scr, zrec.data(), (uint32_t)n); });
-    emu::launch(grid, kTeam, kEncSmemBytes, [&] {
-        rans_encode_kernel<true>(b.descs.data(), enc.data(), scr, hdrs.data(), lsrc.data(), zrec.data(), (uint32_t)n);
-    });
+    if (float_only)  // the variant the pipeline uses for float-only batches without missing symbols
+        emu::launch(grid, kTeam, sizeof(EncSmem<2>), [&] {
+            rans_encode_kernel<false, false>(b.descs.data(), enc.data(), scr, hdrs.data(), lsrc.data(), zrec.data(),
+                                             (uint32_t)n);
+        });
+    else
+        emu::launch(grid, kTeam, sizeof(EncSmem<4>), [&] {
+            rans_encode_kernel<true, true>(b.descs.data(), enc.data(), scr, hdrs.data(), lsrc.data(), zrec.data(),
+                                           (uint32_t)n);
+        });
     emu::launch(grid, 256, 0, [&] { lane_scan_kernel(b.descs.data(), hdrs.data(), psize.data(), loff.data(), (uint32_t)n); });
     emu::launch(1, 1024, 0, [&] { tensor_scan_kernel(b.descs.data(), psize.data(), poff.data(), (uint32_t)n); });
     emu::launch(grid, 256, 0, [&] {
@@ -117,17 +124,23 @@ uint32_t emu_encode(size_t n, const uint8_t* const* srcs, const uint64_t* n_byte
 void emu_decode(size_t n, uint8_t* const* dsts, const uint64_t* n_bytes, const uint32_t* es, const uint32_t* spe,
                 const uint32_t* table_idx, const uint32_t* nf, const uint32_t* cf, const uint32_t* hdrs,
                 const uint8_t* payload, const uint64_t* payload_off, const uint8_t* raw, const uint8_t* sidecar,
-                uint32_t check_zero_lanes, uint32_t* status_out, uint32_t grid) {
+                uint32_t check_zero_lanes, uint32_t* status_out, uint32_t grid, uint32_t float_only) {
     Batch b = make_batch(n, nullptr, dsts, n_bytes, es, spe, table_idx, nullptr);
     for (size_t i = 0; i < n; ++i) {
         b.descs[i].payload_off = payload_off[i];
         if (raw[i]) b.descs[i].flags |= kFlagRaw;
     }
     std::memset(status_out, 0, n * 4);
-    emu::launch(grid, kTeam, kDecSmemBytes4, [&] {
-        rans_decode_kernel<true>(b.descs.data(), nf, cf, (const LaneHeader*)hdrs, payload, sidecar, (uint32_t)n,
-                           check_zero_lanes, status_out);
-    });
+    if (float_only)
+        emu::launch(grid, kTeam, kDecSmemBytes2, [&] {
+            rans_decode_kernel<false>(b.descs.data(), nf, cf, (const LaneHeader*)hdrs, payload, sidecar, (uint32_t)n,
+                                      check_zero_lanes, status_out);
+        });
+    else
+        emu::launch(grid, kTeam, kDecSmemBytes4, [&] {
+            rans_decode_kernel<true>(b.descs.data(), nf, cf, (const LaneHeader*)hdrs, payload, sidecar, (uint32_t)n,
+                                     check_zero_lanes, status_out);
+        });
 }
 
 // outs: n * sizeof(StatsOut)/4 words

@@ -55,6 +55,30 @@ def test_split_hist_encode_decode(emu, oracle, misalign):
             assert np.array_equal(o, a)
 
 
+def test_float_only_kernel_variants(emu, oracle):
+    """The kernel builds used for float-only batches (two chains per thread, no escape test)."""
+    cases = [("bf16_weight", 50000), ("f32_master", 30000), ("f16_weight", 8191), ("f32_exp_avg_sq_lognormal", 2049),
+             ("bf16_norm_gain", 130), ("f32_master", 63)]
+    tensors, es, spe, dts = make(cases, 21)
+    side, hist = emu.split_hist(tensors, es, spe)
+    tabs, masked = [], []
+    for a, d in zip(tensors, dts):
+        m, _ = oracle.split(a, d)
+        masked.append(m)
+        tabs.append(oracle.normalize(oracle.byte_histogram(m), False))
+    nf, cf = np.stack([t[0] for t in tabs]), np.stack([t[1] for t in tabs])
+    payload, poff, hdrs, raw, _ = emu.encode(tensors, es, spe, list(range(len(tensors))), nf, cf, float_only=True)
+    for i in range(len(tensors)):
+        p, hd, r = oracle.compress_tensor(masked[i], *tabs[i][:3])
+        assert bool(raw[i]) == r and np.array_equal(payload[int(poff[i]):int(poff[i + 1])], p), i
+        assert np.array_equal(hdrs[i], hd), i
+    outs, status = emu.decode([a.size for a in tensors], es, spe, list(range(len(tensors))), nf, cf, hdrs, payload,
+                              poff, raw, side, check_zero=1, float_only=True)
+    assert not status.any()
+    for o, a in zip(outs, tensors):
+        assert np.array_equal(o, a)
+
+
 def test_shared_and_degenerate_tables(emu, oracle):
     """Members encoded with an anchor's full-alphabet table (incl. tables that do not sum
     to 4096, and symbols the table lacks), and a passthrough tensor."""
