@@ -157,15 +157,18 @@ constexpr uint32_t kSplitTileBytes = 32768;
 // Count one byte value in this warp's private bins.
 __device__ __forceinline__ void bin_add(uint32_t* wh, uint32_t b) { atomicAdd(&wh[b], 1u); }
 
-// Count a byte value that many lanes of the warp are likely to share (sign and
-// exponent bytes): lanes holding the same value elect one leader that adds the
-// whole group at once.  Every lane of the warp must call this; lanes with
-// nothing to count pass ok = false.
-__device__ __forceinline__ void bin_add_grouped(uint32_t* wh, uint32_t b, bool ok, uint32_t lane) {
-    const uint32_t key = ok ? b : (0x100u + lane);
-    const uint32_t peers = __match_any_sync(0xffffffffu, key);
-    if (ok && lane == (uint32_t)(__ffs(peers) - 1)) atomicAdd(&wh[b], (uint32_t)__popc(peers));
-}
+// Sign-and-exponent bytes take only a handful of values, so a warp's 32 lanes
+// would pile onto the same few counters.  They are counted in a second set of
+// bins kept in kHotCopies copies (a lane uses copy lane % kHotCopies), laid out
+// so that the values that occur together -- neighbouring exponents, either
+// sign -- and the copies all fall into different shared-memory banks:
+//   slot(b) = 2 * (b & 127) + (b >> 7)      neighbours 2 apart, the sign 1 apart
+//   copy c starts kHotStride = 264 (= 8 mod 32) counters after copy c - 1
+constexpr uint32_t kHotCopies = 4;
+constexpr uint32_t kHotStride = 264;
+constexpr uint32_t kHotWords = kHotCopies * kHotStride;
+__device__ __forceinline__ uint32_t hot_slot(uint32_t b) { return ((b & 127u) << 1) | (b >> 7); }
+__device__ __forceinline__ void bin_add_hot(uint32_t* hot_copy, uint32_t b) { atomicAdd(&hot_copy[hot_slot(b)], 1u); }
 
 // One byte at tensor offset `off`: low bytes go to the sidecar, the rest are counted.
 __device__ __forceinline__ void split_one_byte(const TensorDesc& d, unsigned long long off, uint8_t* sidecar,
@@ -190,8 +193,10 @@ __global__ void __launch_bounds__(256) split_hist_kernel(const TensorDesc* __res
                                                          uint8_t* __restrict__ sidecar,
                                                          uint32_t* __restrict__ hist) {
     CHK_SHARED uint32_t wh[8][256];
+    CHK_SHARED uint32_t hot[8][kHotWords];
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     for (uint32_t i = tid; i < 8 * 256; i += 256) (&wh[0][0])[i] = 0;
+    for (uint32_t i = tid; i < 8 * kHotWords; i += 256) (&hot[0][0])[i] = 0;
     __syncthreads();
 
     const uint32_t t0 = (uint32_t)((unsigned long long)total_tiles * blockIdx.x / gridDim.x);
@@ -209,10 +214,16 @@ __global__ void __launch_bounds__(256) split_hist_kernel(const TensorDesc* __res
     auto flush = [&](uint32_t tensor) {
         __syncthreads();
         uint32_t s = 0;
+        const uint32_t hs = hot_slot(tid);
 #pragma unroll
         for (int w = 0; w < 8; ++w) {
             s += wh[w][tid];
             wh[w][tid] = 0;
+#pragma unroll
+            for (uint32_t c = 0; c < kHotCopies; ++c) {
+                s += hot[w][c * kHotStride + hs];
+                hot[w][c * kHotStride + hs] = 0;
+            }
         }
         if (s && (descs[tensor].flags & kFlagNeedHist)) atomicAdd(&hist[(size_t)tensor * 256 + tid], s);
         __syncthreads();
@@ -228,6 +239,7 @@ __global__ void __launch_bounds__(256) split_hist_kernel(const TensorDesc* __res
         const uint32_t nb = (uint32_t)((d.n_bytes - base) < kSplitTileBytes ? (d.n_bytes - base) : kSplitTileBytes);
         const bool count = (d.flags & kFlagNeedHist) != 0;
         uint32_t* mine = wh[warp];
+        uint32_t* mine_hot = hot[warp] + (lane % kHotCopies) * kHotStride;
 
         if ((d.flags & kFlagAligned) && (d.es == 4 || d.es == 2) && d.spe * 2 == d.es) {
             const uint32_t nvec = nb >> 4;
@@ -248,8 +260,10 @@ __global__ void __launch_bounds__(256) split_hist_kernel(const TensorDesc* __res
                     if (count) {
 #pragma unroll
                         for (int k = 0; k < 4; ++k) {
-                            if (ok) bin_add(mine, (w[k] >> 16) & 0xFF);
-                            bin_add_grouped(mine, w[k] >> 24, ok, lane);
+                            if (ok) {
+                                bin_add(mine, (w[k] >> 16) & 0xFF);
+                                bin_add_hot(mine_hot, w[k] >> 24);
+                            }
                         }
                     }
                 } else {
@@ -262,8 +276,10 @@ __global__ void __launch_bounds__(256) split_hist_kernel(const TensorDesc* __res
                     if (count) {
 #pragma unroll
                         for (int k = 0; k < 4; ++k) {
-                            bin_add_grouped(mine, (w[k] >> 8) & 0xFF, ok, lane);
-                            bin_add_grouped(mine, w[k] >> 24, ok, lane);
+                            if (ok) {
+                                bin_add_hot(mine_hot, (w[k] >> 8) & 0xFF);
+                                bin_add_hot(mine_hot, w[k] >> 24);
+                            }
                         }
                     }
                 }
