@@ -37,52 +37,81 @@ __device__ __forceinline__ constexpr uint32_t chain_byte(int k) {
 }
 
 // Shared memory of one encode team: table (256 x 16 B) + a 32-byte output ring
-// per chain.  A ring is 8 contiguous words; rings are 9 words apart so that the
-// 32 lanes of a warp writing the same ring position hit 32 different banks.
-constexpr uint32_t kEncRingWords = 9;
+// per chain.  Ring words are interleaved across the team (word w of thread j's
+// chain k sits at ring[(k*8 + w) * 64 + j]), so a warp never has a bank conflict
+// on it whatever the lanes' positions are.
 template <int NV>
 struct EncSmem {
     uint4 tab[256];
-    uint32_t ring[NV * kTeam * kEncRingWords];
+    uint32_t ring[NV * 8 * kTeam];
 };
 
-// One encode step of one chain: renormalise (at most two bytes, low byte first,
-// written downward) and advance the state.  kEscape = false drops the test for
-// symbols that are missing from the table (the host proves there are none).
+// Output side of one chain.  Emitted bytes are first collected in a 64-bit
+// register pair (newest byte lowest); every two steps a completed 4-byte word
+// moves to the shared-memory ring, and every eight steps a completed 16-byte
+// block moves from the ring to the lane's scratch region.  Streams grow
+// downward in memory, so the oldest byte of a word is its most significant one.
+struct EncOut {
+    uint32_t lo, hi;    // pending bytes, newest in lo[7:0]
+    uint32_t cnt;       // pending bytes (< 4 after a word check)
+    uint32_t wpos;      // lowest byte position already in the ring (multiple of 4)
+    uint32_t flushed;   // lowest 16-byte block already in global memory
+};
+
+__device__ __forceinline__ void enc_emit(EncOut& o, uint32_t v) {  // append byte v[7:0]
+    o.hi = __byte_perm(o.hi, o.lo, 0x2107);
+    o.lo = __byte_perm(o.lo, v, 0x2104);
+    ++o.cnt;
+}
+
+// One encode step of one chain: renormalise (at most two bytes, low byte first)
+// and advance the state.  kEscape = false drops the test for symbols that are
+// missing from the table (the host proves there are none).
 template <bool kEscape>
-__device__ __forceinline__ void enc_step(uint32_t sym, const uint4* tab, uint32_t& x, uint32_t& wpos, uint8_t* ring_bytes) {
+__device__ __forceinline__ void enc_step(uint32_t sym, const uint4* tab, uint32_t& x, EncOut& o) {
     const uint4 e = tab[sym];
     if (kEscape && e.y == 0) {  // symbol not in the table: raw escape byte, state untouched
-        --wpos;
-        ring_bytes[wpos & 31] = (uint8_t)sym;
+        enc_emit(o, sym);
         return;
     }
     const uint32_t xmax = e.y << 19;  // freq * 2^19 (the shift field falls off the top)
     const bool e1 = x >= xmax;
     const bool e2 = (x >> 8) >= xmax;
     if (e1) {
-        --wpos;
-        ring_bytes[wpos & 31] = (uint8_t)x;
+        enc_emit(o, x);
         x >>= 8;
     }
     if (e2) {
-        --wpos;
-        ring_bytes[wpos & 31] = (uint8_t)x;
+        enc_emit(o, x);
         x >>= 8;
     }
     const uint32_t q = __umulhi(x, e.x) >> (e.y >> 16);
     x = x + q * e.w + e.z;
 }
 
-// After at most 8 steps (16 bytes): move the one 16-byte block that may have
-// completed from the ring to the lane's scratch region.
-__device__ __forceinline__ void enc_flush(uint32_t wpos, uint32_t& flushed, const uint32_t* ring_words, uint8_t* region) {
-    const uint32_t done_to = (wpos + 15) >> 4;
-    if (done_to < flushed) {
-        const uint32_t b = flushed - 1;
-        const uint32_t* w = ring_words + (b & 1) * 4;
-        *reinterpret_cast<uint4*>(region + (size_t)b * 16) = make_uint4(w[0], w[1], w[2], w[3]);
-        flushed = b;
+// After at most two steps (4 new bytes, fewer than 8 pending): move one word to the ring.
+__device__ __forceinline__ void enc_word(EncOut& o, uint32_t* ring_col) {
+    if (o.cnt >= 4) {
+        const uint32_t w = __funnelshift_r(o.lo, o.hi, (o.cnt - 4) * 8);
+        o.wpos -= 4;
+        ring_col[((o.wpos >> 2) & 7) * kTeam] = w;
+        o.cnt -= 4;
+    }
+}
+
+// After at most eight steps (16 new bytes in the ring): move the one 16-byte block
+// that may have completed to the lane's scratch region.
+__device__ __forceinline__ void enc_block(EncOut& o, const uint32_t* ring_col, uint8_t* region) {
+    const uint32_t done_to = (o.wpos + 15) >> 4;
+    if (done_to < o.flushed) {
+        const uint32_t b = o.flushed - 1;
+        uint4 v;
+        v.x = ring_col[((b * 4 + 0) & 7) * kTeam];
+        v.y = ring_col[((b * 4 + 1) & 7) * kTeam];
+        v.z = ring_col[((b * 4 + 2) & 7) * kTeam];
+        v.w = ring_col[((b * 4 + 3) & 7) * kTeam];
+        *reinterpret_cast<uint4*>(region + (size_t)b * 16) = v;
+        o.flushed = b;
     }
 }
 
@@ -106,18 +135,19 @@ __device__ __forceinline__ void encode_tensor(const TensorDesc& d, uint32_t ti, 
     }
     __syncthreads();
 
-    uint32_t x[NV], wpos[NV], flushed[NV];
+    uint32_t x[NV];
+    EncOut out[NV];
     uint8_t* region[NV];
-    uint8_t* ringb[NV];
-    const uint32_t* ringw[NV];
+    uint32_t* ring[NV];
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
         x[k] = kL;
-        wpos[k] = d.chunk_stride;
-        flushed[k] = d.chunk_stride >> 4;
+        out[k].lo = out[k].hi = 0;
+        out[k].cnt = 0;
+        out[k].wpos = d.chunk_stride;
+        out[k].flushed = d.chunk_stride >> 4;
         region[k] = scratch + d.scratch_off + (size_t)(j * NV + k) * d.chunk_stride;
-        ringw[k] = sm->ring + (size_t)(k * kTeam + j) * kEncRingWords;
-        ringb[k] = reinterpret_cast<uint8_t*>(sm->ring + (size_t)(k * kTeam + j) * kEncRingWords);
+        ring[k] = sm->ring + (size_t)k * 8 * kTeam + j;
     }
 
     const unsigned long long full_rows = B >> 8;
@@ -125,12 +155,22 @@ __device__ __forceinline__ void encode_tensor(const TensorDesc& d, uint32_t ti, 
     const bool aligned4 = (reinterpret_cast<uintptr_t>(d.src) & 3) == 0;
     const uint8_t* col = d.src + 4 * j;
 
+    // One row for all chains of the thread, then (every second row) the word check.
+    auto row = [&](uint32_t w, bool word_check) {
+#pragma unroll
+        for (int k = 0; k < NV; ++k) {
+            enc_step<kEscape>((w >> (8 * chain_byte<NV, B0>(k))) & 0xFF, sm->tab, x[k], out[k]);
+            if (word_check) enc_word(out[k], ring[k]);
+        }
+    };
+
     // the last, partial row (symbols of the highest index come first)
     if (tail) {
 #pragma unroll
         for (int k = 0; k < NV; ++k) {
             const uint32_t t = 4 * j + chain_byte<NV, B0>(k);
-            if (t < tail) enc_step<kEscape>(d.src[(full_rows << 8) + t], sm->tab, x[k], wpos[k], ringb[k]);
+            if (t < tail) enc_step<kEscape>(d.src[(full_rows << 8) + t], sm->tab, x[k], out[k]);
+            enc_word(out[k], ring[k]);
         }
     }
     // rows above the last multiple of 8, one at a time: with the partial row at most 8 steps
@@ -138,12 +178,10 @@ __device__ __forceinline__ void encode_tensor(const TensorDesc& d, uint32_t ti, 
     const uint32_t odd = (uint32_t)(full_rows & 7);
     for (uint32_t u = 0; u < odd; ++u) {
         --r;
-        const uint32_t w = load_row_word(col + (r << 8), aligned4);
-#pragma unroll
-        for (int k = 0; k < NV; ++k) enc_step<kEscape>((w >> (8 * chain_byte<NV, B0>(k))) & 0xFF, sm->tab, x[k], wpos[k], ringb[k]);
+        row(load_row_word(col + (r << 8), aligned4), true);
     }
 #pragma unroll
-    for (int k = 0; k < NV; ++k) enc_flush(wpos[k], flushed[k], ringw[k], region[k]);
+    for (int k = 0; k < NV; ++k) enc_block(out[k], ring[k], region[k]);
 
     // full groups of 8 rows, highest first.  The words of the NEXT group are
     // requested before the current group's dependent chains run, so the memory
@@ -163,27 +201,30 @@ __device__ __forceinline__ void encode_tensor(const TensorDesc& d, uint32_t ti, 
             for (int u = 0; u < 8; ++u) nxt[u] = load_row_word(col + ((r - 8 + u) << 8), aligned4);
         }
 #pragma unroll
-        for (int u = 7; u >= 0; --u) {
+        for (int u = 7; u >= 0; --u) row(w[u], (u & 1) == 0);
 #pragma unroll
-            for (int k = 0; k < NV; ++k) enc_step<kEscape>((w[u] >> (8 * chain_byte<NV, B0>(k))) & 0xFF, sm->tab, x[k], wpos[k], ringb[k]);
-        }
-#pragma unroll
-        for (int k = 0; k < NV; ++k) enc_flush(wpos[k], flushed[k], ringw[k], region[k]);
+        for (int k = 0; k < NV; ++k) enc_block(out[k], ring[k], region[k]);
     }
 
-    // bytes of the last, partial block; lane headers; where the lane's bytes start
+    // what is still pending: up to 3 bytes in registers, up to 15 in the ring
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
-        for (uint32_t p = wpos[k]; p < (flushed[k] << 4); ++p)
-            region[k][p] = ringb[k][p & 31];
+        EncOut& o = out[k];
+        const uint32_t low = o.wpos - o.cnt;  // final lowest byte position of the stream
+        for (uint32_t i = 0; i < o.cnt; ++i)  // oldest pending byte sits highest in memory
+            region[k][o.wpos - 1 - i] = (uint8_t)(o.lo >> ((o.cnt - 1 - i) * 8));
+        for (uint32_t p = o.wpos; p < (o.flushed << 4); p += 4) {
+            const uint32_t w = ring[k][((p >> 2) & 7) * kTeam];
+            *reinterpret_cast<uint32_t*>(region[k] + p) = w;
+        }
         const uint32_t t = 4 * j + chain_byte<NV, B0>(k);
         LaneHeader h;
         h.final_state = x[k];
-        h.byte_count = d.chunk_stride - wpos[k];
+        h.byte_count = d.chunk_stride - low;
         h.buf_offset = 0;
         h.pad = 0;
         hdrs[(size_t)ti * kLanes + t] = h;
-        lane_src[(size_t)ti * kLanes + t] = d.scratch_off + (unsigned long long)(j * NV + k) * d.chunk_stride + wpos[k];
+        lane_src[(size_t)ti * kLanes + t] = d.scratch_off + (unsigned long long)(j * NV + k) * d.chunk_stride + low;
     }
     if (NV == 2) {  // the thread's other two lanes share the tensor's symbol-0 chain
         const ZeroRec z = zrec[ti];
@@ -465,22 +506,27 @@ __device__ __forceinline__ void dec_commit(DecChain& c, uint32_t* ring_words) {
     }
 }
 
+// acc with its byte P replaced by the low byte of v
+template <uint32_t P>
+__device__ __forceinline__ uint32_t put_byte(uint32_t acc, uint32_t v) {
+    constexpr uint32_t sel = P == 0 ? 0x3214u : P == 1 ? 0x3240u : P == 2 ? 0x3410u : 0x4210u;
+    return __byte_perm(acc, v, sel);
+}
+
+// One decode step: look the slot up, step the state back, and pull in 0, 1 or 2
+// stream bytes without branching: the two candidate bytes are placed at the top
+// of a word and funnel-shifted into the state by 0, 8 or 16 bits.  Returns the
+// table entry (symbol in its low byte).
 __device__ __forceinline__ uint32_t dec_step(DecChain& c, const uint32_t* dtab, const uint8_t* ring_bytes) {
-    const uint32_t slot = c.x & (kM - 1);
-    const uint32_t e = dtab[slot];
-    uint32_t x = (((e >> 8) & 0xFFFu) + 1u) * (c.x >> kScaleBits) + (e >> 20);
+    const uint32_t e = dtab[c.x & (kM - 1)];
+    const uint32_t xs = c.x >> kScaleBits;
+    const uint32_t x = ((e >> 8) & 0xFFFu) * xs + xs + (e >> 20);
     const uint8_t* rp = ring_bytes + (c.rel & 63);
-    const uint32_t b0 = rp[0];
-    const uint32_t b1 = rp[1];
-    if (x < (1u << 15)) {
-        x = (x << 16) | (b0 << 8) | b1;
-        c.rel += 2;
-    } else if (x < kL) {
-        x = (x << 8) | b0;
-        c.rel += 1;
-    }
-    c.x = x;
-    return e & 0xFFu;
+    const uint32_t top = ((uint32_t)rp[0] << 24) | ((uint32_t)rp[1] << 16);
+    const uint32_t n = (x < kL ? 1u : 0u) + (x < (1u << 15) ? 1u : 0u);
+    c.x = __funnelshift_l(top, x, n * 8);
+    c.rel += n;
+    return e;
 }
 
 template <int NV, int B0>
@@ -508,9 +554,6 @@ __device__ __forceinline__ void decode_tensor(const TensorDesc& d, uint32_t ti,
         }
         sm->dtab[slot] = lo | ((fq[lo] - 1) << 8) | ((slot - sm->cum[lo]) << 20);
     }
-
-    // mask of the word's bytes that come from the codec (the rest come from the sidecar)
-    constexpr uint32_t keep = NV == 4 ? 0xFFFFFFFFu : (B0 == 2 ? 0xFFFF0000u : 0xFF00FF00u);
 
     DecChain ch[NV];
     uint32_t* ringw[NV];
@@ -579,16 +622,13 @@ __device__ __forceinline__ void decode_tensor(const TensorDesc& d, uint32_t ti,
 #pragma unroll
             for (int u = 0; u < 8; ++u) side_next[u] = side_word(r + 8 + u);
         }
-        uint32_t w[8];
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
-            uint32_t acc = 0;
+            uint32_t acc = side[u];
 #pragma unroll
-            for (int k = 0; k < NV; ++k) acc |= dec_step(ch[k], sm->dtab, ringb[k]) << (8 * chain_byte<NV, B0>(k));
-            w[u] = (acc & keep) | side[u];
+            for (int k = 0; k < NV; ++k) acc = put_byte<chain_byte<NV, B0>(k)>(acc, dec_step(ch[k], sm->dtab, ringb[k]));
+            store_word(r + u, acc);
         }
-#pragma unroll
-        for (int u = 0; u < 8; ++u) store_word(r + u, w[u]);
 #pragma unroll
         for (int k = 0; k < NV; ++k) {
             dec_commit(ch[k], ringw[k]);
@@ -601,16 +641,16 @@ __device__ __forceinline__ void decode_tensor(const TensorDesc& d, uint32_t ti,
     for (int k = 0; k < NV; ++k) dec_commit(ch[k], ringw[k]);
     // remaining full rows and the partial row: at most 8 steps per chain
     for (; r < full_rows; ++r) {
-        uint32_t acc = 0;
+        uint32_t acc = side_word(r);
 #pragma unroll
-        for (int k = 0; k < NV; ++k) acc |= dec_step(ch[k], sm->dtab, ringb[k]) << (8 * chain_byte<NV, B0>(k));
-        store_word(r, (acc & keep) | side_word(r));
+        for (int k = 0; k < NV; ++k) acc = put_byte<chain_byte<NV, B0>(k)>(acc, dec_step(ch[k], sm->dtab, ringb[k]));
+        store_word(r, acc);
     }
     if (tail) {
         uint32_t acc = 0;
 #pragma unroll
         for (int k = 0; k < NV; ++k)
-            if (4 * j + chain_byte<NV, B0>(k) < tail) acc |= dec_step(ch[k], sm->dtab, ringb[k]) << (8 * chain_byte<NV, B0>(k));
+            if (4 * j + chain_byte<NV, B0>(k) < tail) acc = put_byte<chain_byte<NV, B0>(k)>(acc, dec_step(ch[k], sm->dtab, ringb[k]));
 #pragma unroll
         for (uint32_t b = 0; b < 4; ++b) {
             const uint32_t t = 4 * j + b;
