@@ -8,7 +8,8 @@ CSRC = os.path.join(PKG, "csrc")
 LIB_DIR = os.path.join(PKG, "lib")
 LIB = os.path.join(LIB_DIR, "libcheckers_b200.so")
 SOURCES = ["engine.cu"]
-HEADERS = ["kernels.cuh", "tables.hpp", "clusters.hpp", os.path.join("..", "..", "include", "checkers_b200.h")]
+HEADERS = ["kernels.cuh", "rans_kernels.cuh", "tables.hpp", "clusters.hpp",
+           os.path.join("..", "..", "include", "checkers_b200.h")]
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-shared"]
@@ -18,7 +19,8 @@ def needs_build():
     if not os.path.exists(LIB):
         return True
     t = os.path.getmtime(LIB)
-    return any(os.path.getmtime(os.path.join(CSRC, f)) > t for f in SOURCES + HEADERS)
+    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [os.path.join(CSRC, h) for h in HEADERS]
+    return any(os.path.getmtime(f) > t for f in deps)
 
 
 def build(force=False, verbose=False):

@@ -507,9 +507,8 @@ __device__ __forceinline__ void dec_commit(DecChain& c, uint32_t* ring_words) {
 }
 
 // acc with its byte P replaced by the low byte of v
-template <uint32_t P>
-__device__ __forceinline__ uint32_t put_byte(uint32_t acc, uint32_t v) {
-    constexpr uint32_t sel = P == 0 ? 0x3214u : P == 1 ? 0x3240u : P == 2 ? 0x3410u : 0x4210u;
+__device__ __forceinline__ uint32_t put_byte(uint32_t acc, uint32_t v, uint32_t P) {
+    const uint32_t sel = P == 0 ? 0x3214u : P == 1 ? 0x3240u : P == 2 ? 0x3410u : 0x4210u;  // folds once unrolled
     return __byte_perm(acc, v, sel);
 }
 
@@ -626,7 +625,7 @@ __device__ __forceinline__ void decode_tensor(const TensorDesc& d, uint32_t ti,
         for (int u = 0; u < 8; ++u) {
             uint32_t acc = side[u];
 #pragma unroll
-            for (int k = 0; k < NV; ++k) acc = put_byte<chain_byte<NV, B0>(k)>(acc, dec_step(ch[k], sm->dtab, ringb[k]));
+            for (int k = 0; k < NV; ++k) acc = put_byte(acc, dec_step(ch[k], sm->dtab, ringb[k]), chain_byte<NV, B0>(k));
             store_word(r + u, acc);
         }
 #pragma unroll
@@ -643,14 +642,14 @@ __device__ __forceinline__ void decode_tensor(const TensorDesc& d, uint32_t ti,
     for (; r < full_rows; ++r) {
         uint32_t acc = side_word(r);
 #pragma unroll
-        for (int k = 0; k < NV; ++k) acc = put_byte<chain_byte<NV, B0>(k)>(acc, dec_step(ch[k], sm->dtab, ringb[k]));
+        for (int k = 0; k < NV; ++k) acc = put_byte(acc, dec_step(ch[k], sm->dtab, ringb[k]), chain_byte<NV, B0>(k));
         store_word(r, acc);
     }
     if (tail) {
         uint32_t acc = 0;
 #pragma unroll
         for (int k = 0; k < NV; ++k)
-            if (4 * j + chain_byte<NV, B0>(k) < tail) acc = put_byte<chain_byte<NV, B0>(k)>(acc, dec_step(ch[k], sm->dtab, ringb[k]));
+            if (4 * j + chain_byte<NV, B0>(k) < tail) acc = put_byte(acc, dec_step(ch[k], sm->dtab, ringb[k]), chain_byte<NV, B0>(k));
 #pragma unroll
         for (uint32_t b = 0; b < 4; ++b) {
             const uint32_t t = 4 * j + b;

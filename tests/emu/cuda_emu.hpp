@@ -233,6 +233,10 @@ static inline unsigned __funnelshift_r(unsigned lo, unsigned hi, unsigned sh) {
     unsigned long long v = ((unsigned long long)hi << 32) | lo;
     return (unsigned)(v >> (sh & 31));
 }
+static inline unsigned __funnelshift_l(unsigned lo, unsigned hi, unsigned sh) {
+    unsigned long long v = ((unsigned long long)hi << 32) | lo;
+    return (unsigned)((v << (sh & 31)) >> 32);
+}
 static inline unsigned __byte_perm(unsigned a, unsigned b, unsigned s) {
     unsigned long long v = ((unsigned long long)b << 32) | a;
     unsigned r = 0;

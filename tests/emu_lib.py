@@ -19,7 +19,9 @@ u64p = C.POINTER(C.c_uint64)
 
 def build_emu():
     srcs = [os.path.join(EMU_DIR, "emu_kernels.cpp"), os.path.join(EMU_DIR, "cuda_emu.hpp"),
-            os.path.join(CSRC, "kernels.cuh"), os.path.join(CSRC, "tables.hpp")]
+            os.path.join(CSRC, "kernels.cuh"), os.path.join(CSRC, "rans_kernels.cuh"),
+            os.path.join(CSRC, "tables.hpp")]
+    srcs += [os.path.join(CSRC, f) for f in os.listdir(CSRC)]
     if not os.path.exists(EMU_SO) or any(os.path.getmtime(EMU_SO) < os.path.getmtime(s) for s in srcs):
         subprocess.check_call(["g++", "-std=c++17", "-O1", "-I", CSRC, "-I", EMU_DIR, "-shared", "-fPIC", "-w",
                                srcs[0], "-o", EMU_SO])
