@@ -117,10 +117,12 @@ struct Context {
     int host_threads = 0;
 
     // device buffers (grow-only, from the context's pool)
-    DevBuf d_descs, d_tiles, d_hist, d_sidecar, d_scratch, d_hdrs, d_lsrc, d_zrec, d_loff, d_psize, d_poff, d_payload, d_enc,
-        d_freq, d_cum, d_status, d_stats_desc, d_stats_out;
+    DevBuf d_descs, d_tiles, d_hist, d_sidecar, d_scratch, d_hdrs, d_lsrc, d_order, d_ticket, d_loff, d_psize, d_poff,
+        d_payload, d_enc, d_freq, d_cum, d_status, d_stats_desc, d_stats_out;
+    cudaStream_t side_stream = nullptr;
+    int sm_count = 0;
     // pinned host staging
-    PinBuf h_hist, h_hdrs, h_poff, h_descs, h_status, h_enc, h_stats;
+    PinBuf h_hist, h_hdrs, h_poff, h_descs, h_status, h_enc, h_stats, h_order;
     PinBuf img[3];  // states, mantissa, tables
 
     // result of the last compression
@@ -266,6 +268,31 @@ static std::string get_name(const uint8_t* p) {
     return std::string(reinterpret_cast<const char*>(p), n);
 }
 
+// Largest-first processing order of a batch plus a zeroed ticket counter for
+// the persistent encode / decode kernels.
+template <typename SizeFn>
+static void upload_order(Context* c, size_t W, SizeFn&& size_of) {
+    std::vector<uint32_t> order(W);
+    for (size_t i = 0; i < W; ++i) order[i] = (uint32_t)i;
+    std::stable_sort(order.begin(), order.end(),
+                     [&](uint32_t a, uint32_t b) { return size_of(a) > size_of(b); });
+    pin_ensure(c->h_order, W * 4);
+    std::memcpy(c->h_order.p, order.data(), W * 4);
+    dev_ensure(c, c->d_order, W * 4);
+    dev_ensure(c, c->d_ticket, 256);
+    CHK_CUDA(cudaMemcpyAsync(c->d_order.p, c->h_order.p, W * 4, cudaMemcpyHostToDevice, c->stream));
+    CHK_CUDA(cudaMemsetAsync(c->d_ticket.p, 0, 256, c->stream));
+}
+
+// Grid of a persistent team kernel: as many teams as fit on the device at once.
+static uint32_t persistent_grid(Context* c, const void* kernel, size_t smem, size_t W) {
+    int per_sm = 0;
+    CHK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, (int)kTeam, smem));
+    if (per_sm < 1) per_sm = 1;
+    const size_t cap = (size_t)per_sm * (size_t)(c->sm_count > 0 ? c->sm_count : 1);
+    return (uint32_t)(W < cap ? W : cap);
+}
+
 // ------------------------------------------------------------------ compress
 static void compress(Context* c, bool host_images) {
     const auto t_total = std::chrono::steady_clock::now();
@@ -331,7 +358,7 @@ static void compress(Context* c, bool host_images) {
     dev_ensure(c, c->d_scratch, scratch_total + 64);
     dev_ensure(c, c->d_hdrs, W * 4096);
     dev_ensure(c, c->d_lsrc, W * 2048);
-    dev_ensure(c, c->d_zrec, W * sizeof(ZeroRec));
+    upload_order(c, W, [&](size_t i) { return c->descs[i].n_bytes; });
     dev_ensure(c, c->d_loff, W * 1024);
     dev_ensure(c, c->d_psize, W * 8);
     dev_ensure(c, c->d_poff, (W + 1) * 8);
@@ -402,14 +429,17 @@ static void compress(Context* c, bool host_images) {
 
     // ---- stage 2: encode
     {
-        // the shared symbol-0 chain of every tensor first (one thread each), then the value lanes
-        zero_lane_kernel<<<(uint32_t)((W + 127) / 128), 128, 0, s>>>(
+        // The shared symbol-0 chain of every tensor (one thread each) runs on the side
+        // stream next to the value lanes; both are joined before the offsets are computed.
+        CHK_CUDA(cudaStreamWaitEvent(c->side_stream, c->ev[2], 0));
+        zero_lane_kernel<<<(uint32_t)((W + 127) / 128), 128, 0, c->side_stream>>>(
             static_cast<const TensorDesc*>(c->d_descs.p), static_cast<const EncEntry*>(c->d_enc.p),
-            static_cast<uint8_t*>(c->d_scratch.p), static_cast<ZeroRec*>(c->d_zrec.p), (uint32_t)W);
+            static_cast<uint8_t*>(c->d_scratch.p), static_cast<LaneHeader*>(c->d_hdrs.p),
+            static_cast<unsigned long long*>(c->d_lsrc.p), (uint32_t)W);
         CHK_CUDA(cudaGetLastError());
+        CHK_CUDA(cudaEventRecord(c->ev[7], c->side_stream));
         bool any_int = false;
         for (size_t i = 0; i < W && !any_int; ++i) any_int = c->work[i].spe * 2 != c->work[i].es;
-        const uint32_t grid = (uint32_t)(W < 148u * 256u ? W : 148u * 256u);
         // A tensor can only meet a symbol its table lacks when it borrows another tensor's
         // table; the reference builds shared tables over the full alphabet, so this is
         // normally false and the kernel without the escape test runs.
@@ -421,14 +451,18 @@ static void compress(Context* c, bool host_images) {
         }
         auto kernel = any_int ? (need_escape ? rans_encode_kernel<true, true> : rans_encode_kernel<true, false>)
                               : (need_escape ? rans_encode_kernel<false, true> : rans_encode_kernel<false, false>);
-        kernel<<<grid, kTeam, any_int ? sizeof(EncSmem<4>) : sizeof(EncSmem<2>), s>>>(
+        const size_t smem = any_int ? sizeof(EncSmem<4>) : sizeof(EncSmem<2>);
+        const uint32_t grid = persistent_grid(c, reinterpret_cast<const void*>(kernel), smem, W);
+        kernel<<<grid, kTeam, smem, s>>>(
             static_cast<const TensorDesc*>(c->d_descs.p), static_cast<const EncEntry*>(c->d_enc.p),
             static_cast<uint8_t*>(c->d_scratch.p), static_cast<LaneHeader*>(c->d_hdrs.p),
-            static_cast<unsigned long long*>(c->d_lsrc.p), static_cast<const ZeroRec*>(c->d_zrec.p), (uint32_t)W);
+            static_cast<unsigned long long*>(c->d_lsrc.p), static_cast<const uint32_t*>(c->d_order.p),
+            static_cast<uint32_t*>(c->d_ticket.p), (uint32_t)W);
         CHK_CUDA(cudaGetLastError());
         c->launches += 2;
     }
     CHK_CUDA(cudaEventRecord(c->ev[3], s));
+    CHK_CUDA(cudaStreamWaitEvent(s, c->ev[7], 0));
 
     // ---- stage 3: offsets + compaction into the data-section layout
     {
@@ -601,13 +635,18 @@ static void run_decode(Context* c, size_t W, const uint8_t* d_payload, const uin
     const TensorDesc* hd = static_cast<const TensorDesc*>(c->h_descs.p);
     for (size_t i = 0; i < W && !any_int; ++i) any_int = hd[i].spe * 2 != hd[i].es;
     const uint32_t smem = any_int ? kDecSmemBytes4 : kDecSmemBytes2;
-    CHK_CUDA(cudaEventRecord(c->ev[1], s));
-    const uint32_t grid = (uint32_t)(W < 148u * 256u ? W : 148u * 256u);
+    upload_order(c, W, [&](size_t i) { return hd[i].n_bytes; });
     auto kernel = any_int ? rans_decode_kernel<true> : rans_decode_kernel<false>;
-    kernel<<<grid, kTeam, smem, s>>>(static_cast<const TensorDesc*>(c->d_descs.p), d_freq, d_cum,
-                                                        d_hdrs, d_payload, d_sidecar, (uint32_t)W,
-                                                        c->verify_zero_lanes ? 1u : 0u,
-                                                        static_cast<uint32_t*>(c->d_status.p));
+    if (smem > 48 * 1024 && !c->dec_attr_set) {
+        CHK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        c->dec_attr_set = true;
+    }
+    const uint32_t grid = persistent_grid(c, reinterpret_cast<const void*>(kernel), smem, W);
+    CHK_CUDA(cudaEventRecord(c->ev[1], s));
+    kernel<<<grid, kTeam, smem, s>>>(static_cast<const TensorDesc*>(c->d_descs.p), d_freq, d_cum, d_hdrs, d_payload,
+                                     d_sidecar, static_cast<const uint32_t*>(c->d_order.p),
+                                     static_cast<uint32_t*>(c->d_ticket.p), (uint32_t)W,
+                                     c->verify_zero_lanes ? 1u : 0u, static_cast<uint32_t*>(c->d_status.p));
     CHK_CUDA(cudaGetLastError());
     c->launches++;
     CHK_CUDA(cudaEventRecord(c->ev[2], s));
@@ -896,6 +935,8 @@ int chk_context_create(int device, int rank, int local_rank, chk_context** out) 
     c->local_rank = local_rank;
     try {
         CHK_CUDA(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
+        CHK_CUDA(cudaStreamCreateWithFlags(&c->side_stream, cudaStreamNonBlocking));
+        CHK_CUDA(cudaDeviceGetAttribute(&c->sm_count, cudaDevAttrMultiProcessorCount, device));
         cudaMemPoolProps props{};
         props.allocType = cudaMemAllocationTypePinned;
         props.handleTypes = cudaMemHandleTypeNone;
@@ -919,18 +960,19 @@ int chk_context_destroy(chk_context* c) {
     cudaSetDevice(c->device);
     if (c->stream) cudaStreamSynchronize(c->stream);
     DevBuf* bufs[] = {&c->d_descs, &c->d_tiles, &c->d_hist, &c->d_sidecar, &c->d_scratch, &c->d_hdrs,
-                      &c->d_lsrc, &c->d_zrec, &c->d_loff, &c->d_psize, &c->d_poff, &c->d_payload, &c->d_enc,
+                      &c->d_lsrc, &c->d_order, &c->d_ticket, &c->d_loff, &c->d_psize, &c->d_poff, &c->d_payload, &c->d_enc,
                       &c->d_freq, &c->d_cum, &c->d_status, &c->d_stats_desc, &c->d_stats_out};
     for (DevBuf* b : bufs)
         if (b->p) cudaFreeAsync(b->p, c->stream);
     if (c->stream) cudaStreamSynchronize(c->stream);
-    PinBuf* pins[] = {&c->h_hist, &c->h_hdrs, &c->h_poff, &c->h_descs, &c->h_status, &c->h_enc, &c->h_stats,
+    PinBuf* pins[] = {&c->h_hist, &c->h_hdrs, &c->h_poff, &c->h_descs, &c->h_status, &c->h_enc, &c->h_stats, &c->h_order,
                       &c->img[0], &c->img[1], &c->img[2]};
     for (PinBuf* b : pins)
         if (b->p) cudaFreeHost(b->p);
     for (auto& e : c->ev)
         if (e) cudaEventDestroy(e);
     if (c->pool) cudaMemPoolDestroy(c->pool);
+    if (c->side_stream) cudaStreamDestroy(c->side_stream);
     if (c->stream) cudaStreamDestroy(c->stream);
     delete c;
     CHK_API_END

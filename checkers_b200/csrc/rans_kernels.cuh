@@ -19,14 +19,6 @@
 
 namespace chk {
 
-// Result of the shared symbol-0 chain of one tensor: state and byte count after
-// c_max symbols ([0]) and after c_max-1 symbols ([1]); its bytes end at the top
-// of the tensor's zero region.
-struct ZeroRec {
-    uint32_t state[2];
-    uint32_t nbytes[2];
-};
-
 constexpr uint32_t kTeam = 64;  // threads per tensor
 
 // Byte of the thread's 32-bit row word that chain k encodes.  NV = chains per
@@ -123,8 +115,7 @@ __device__ __forceinline__ uint32_t load_row_word(const uint8_t* p, bool aligned
 template <int NV, int B0, bool kEscape>
 __device__ __forceinline__ void encode_tensor(const TensorDesc& d, uint32_t ti, const EncEntry* __restrict__ tables,
                                               uint8_t* __restrict__ scratch, LaneHeader* __restrict__ hdrs,
-                                              unsigned long long* __restrict__ lane_src,
-                                              const ZeroRec* __restrict__ zrec, unsigned char* smem_raw) {
+                                              unsigned long long* __restrict__ lane_src, unsigned char* smem_raw) {
     EncSmem<NV>* sm = reinterpret_cast<EncSmem<NV>*>(smem_raw);
     const uint32_t j = threadIdx.x;
     const unsigned long long B = d.n_bytes;
@@ -226,76 +217,69 @@ __device__ __forceinline__ void encode_tensor(const TensorDesc& d, uint32_t ti, 
         hdrs[(size_t)ti * kLanes + t] = h;
         lane_src[(size_t)ti * kLanes + t] = d.scratch_off + (unsigned long long)(j * NV + k) * d.chunk_stride + low;
     }
-    if (NV == 2) {  // the thread's other two lanes share the tensor's symbol-0 chain
-        const ZeroRec z = zrec[ti];
-        const unsigned long long c_max = (B + kLanes - 1) / kLanes;
-        const unsigned long long zbase = d.scratch_off + (unsigned long long)kTeam * NV * d.chunk_stride;
-#pragma unroll
-        for (uint32_t b = 0; b < 4; ++b) {
-            if (b == (uint32_t)B0 || b == 3u) continue;
-            const uint32_t t = 4 * j + b;
-            const unsigned long long cnt = B > t ? (B - t + kLanes - 1) / kLanes : 0;
-            LaneHeader h;
-            h.buf_offset = 0;
-            h.pad = 0;
-            if (cnt == 0) {
-                h.final_state = kL;
-                h.byte_count = 0;
-            } else {
-                const int w = cnt == c_max ? 0 : 1;
-                h.final_state = z.state[w];
-                h.byte_count = z.nbytes[w];
-            }
-            hdrs[(size_t)ti * kLanes + t] = h;
-            lane_src[(size_t)ti * kLanes + t] = zbase + d.chunk_stride - h.byte_count;
-        }
-    }
     __syncthreads();  // table and ring are reused by the next tensor
 }
 
 // One team (CTA of 64 threads) per tensor.  kInts = false is the build for
 // batches of float tensors only (two chains per thread, fewer registers, more
 // resident teams); the host picks the variant per batch.
+// Work is handed out through a ticket counter in the order given by `order`
+// (largest tensors first), so a persistent grid of resident teams drains the
+// batch without a ragged last wave.
+__device__ __forceinline__ uint32_t next_ticket(uint32_t* ticket, uint32_t* slot) {
+    if (threadIdx.x == 0) *slot = atomicAdd(ticket, 1u);
+    __syncthreads();
+    return *slot;  // every thread reads it before the next barrier, which precedes the next write
+}
+
 template <bool kInts, bool kEscape>
 __global__ void __launch_bounds__(kTeam) rans_encode_kernel(const TensorDesc* __restrict__ descs,
                                                             const EncEntry* __restrict__ tables,
                                                             uint8_t* __restrict__ scratch,
                                                             LaneHeader* __restrict__ hdrs,
                                                             unsigned long long* __restrict__ lane_src,
-                                                            const ZeroRec* __restrict__ zrec, uint32_t n_tensors) {
+                                                            const uint32_t* __restrict__ order,
+                                                            uint32_t* __restrict__ ticket, uint32_t n_tensors) {
     CHK_DYN_SMEM(smem);
-    for (uint32_t ti = blockIdx.x; ti < n_tensors; ti += gridDim.x) {
+    CHK_SHARED uint32_t s_ticket;
+    for (;;) {
+        const uint32_t tk = next_ticket(ticket, &s_ticket);
+        if (tk >= n_tensors) break;
+        const uint32_t ti = order[tk];
         const TensorDesc d = descs[ti];
         if (d.es == 4 && d.spe == 2)
-            encode_tensor<2, 2, kEscape>(d, ti, tables, scratch, hdrs, lane_src, zrec, smem);
+            encode_tensor<2, 2, kEscape>(d, ti, tables, scratch, hdrs, lane_src, smem);
         else if (d.es == 2 && d.spe == 1)
-            encode_tensor<2, 1, kEscape>(d, ti, tables, scratch, hdrs, lane_src, zrec, smem);
+            encode_tensor<2, 1, kEscape>(d, ti, tables, scratch, hdrs, lane_src, smem);
         else if (kInts)
-            encode_tensor<4, 0, kEscape>(d, ti, tables, scratch, hdrs, lane_src, zrec, smem);
+            encode_tensor<4, 0, kEscape>(d, ti, tables, scratch, hdrs, lane_src, smem);
+        else
+            __syncthreads();  // keep the barrier count uniform
     }
 }
 
 // The symbol-0 chain of every tensor that has zeroed low bytes: one thread per
 // tensor, c_max steps, bytes written downward from the top of the tensor's zero
-// region (the region after its value-lane regions).
+// region (the region after its value-lane regions).  The same thread then fills
+// in the header and byte location of each of the tensor's zero lanes: a lane
+// with c_max symbols owns the whole string, one with c_max-1 owns its suffix.
+// Runs next to the value-lane kernel (it touches different lanes and regions).
 __global__ void __launch_bounds__(128) zero_lane_kernel(const TensorDesc* __restrict__ descs,
                                                         const EncEntry* __restrict__ tables,
-                                                        uint8_t* __restrict__ scratch, ZeroRec* __restrict__ zrec,
+                                                        uint8_t* __restrict__ scratch,
+                                                        LaneHeader* __restrict__ hdrs,
+                                                        unsigned long long* __restrict__ lane_src,
                                                         uint32_t n_tensors) {
     const uint32_t ti = blockIdx.x * blockDim.x + threadIdx.x;
     if (ti >= n_tensors) return;
     const TensorDesc d = descs[ti];
-    ZeroRec z;
-    z.state[0] = z.state[1] = kL;
-    z.nbytes[0] = z.nbytes[1] = 0;
-    if (d.spe * 2 != d.es) {
-        zrec[ti] = z;
-        return;
-    }
+    if (d.spe * 2 != d.es) return;  // integer tensors have no zeroed bytes
     const EncEntry e = tables[(size_t)d.table_idx * 256];
     const uint32_t f = e.freq_shift & 0xFFFFu, sh = e.freq_shift >> 16, xmax = e.freq_shift << 19;
-    uint8_t* const region = scratch + d.scratch_off + (size_t)kTeam * 2 * d.chunk_stride;
+    const unsigned long long zbase = d.scratch_off + (unsigned long long)kTeam * 2 * d.chunk_stride;
+    uint8_t* const region = scratch + zbase;
     uint32_t wpos = d.chunk_stride, x = kL;
+    uint32_t state1 = kL, nbytes1 = 0;  // after c_max - 1 symbols
     const unsigned long long c_max = (d.n_bytes + kLanes - 1) / kLanes;
     for (unsigned long long i = 1; i <= c_max; ++i) {
         if (f == 0) {
@@ -313,13 +297,22 @@ __global__ void __launch_bounds__(128) zero_lane_kernel(const TensorDesc* __rest
             x = x + q * e.cmpl + e.bias;
         }
         if (i + 1 == c_max) {
-            z.state[1] = x;
-            z.nbytes[1] = d.chunk_stride - wpos;
+            state1 = x;
+            nbytes1 = d.chunk_stride - wpos;
         }
     }
-    z.state[0] = x;
-    z.nbytes[0] = d.chunk_stride - wpos;
-    zrec[ti] = z;
+    const uint32_t state0 = x, nbytes0 = d.chunk_stride - wpos;
+    for (uint32_t t = 0; t < kLanes; ++t) {
+        if ((t % d.es) >= d.spe) continue;
+        const unsigned long long cnt = d.n_bytes > t ? (d.n_bytes - t + kLanes - 1) / kLanes : 0;
+        LaneHeader h;
+        h.buf_offset = 0;
+        h.pad = 0;
+        h.final_state = cnt == 0 ? kL : (cnt == c_max ? state0 : state1);
+        h.byte_count = cnt == 0 ? 0u : (cnt == c_max ? nbytes0 : nbytes1);
+        hdrs[(size_t)ti * kLanes + t] = h;
+        lane_src[(size_t)ti * kLanes + t] = zbase + d.chunk_stride - h.byte_count;
+    }
 }
 
 // ------------------------------------------------------------------ offsets and compaction
@@ -703,11 +696,17 @@ __global__ void __launch_bounds__(kTeam) rans_decode_kernel(const TensorDesc* __
                                                             const uint32_t* __restrict__ cum_tables,   // [T][257]
                                                             const LaneHeader* __restrict__ hdrs,
                                                             const uint8_t* __restrict__ payload,
-                                                            const uint8_t* __restrict__ sidecar, uint32_t n_tensors,
+                                                            const uint8_t* __restrict__ sidecar,
+                                                            const uint32_t* __restrict__ order,
+                                                            uint32_t* __restrict__ ticket, uint32_t n_tensors,
                                                             uint32_t check_zero_lanes,
                                                             uint32_t* __restrict__ status /* per tensor */) {
     CHK_DYN_SMEM(smem);
-    for (uint32_t ti = blockIdx.x; ti < n_tensors; ti += gridDim.x) {
+    CHK_SHARED uint32_t s_ticket;
+    for (;;) {
+        const uint32_t tk = next_ticket(ticket, &s_ticket);
+        if (tk >= n_tensors) break;
+        const uint32_t ti = order[tk];
         const TensorDesc d = descs[ti];
         if (d.flags & kFlagRaw) {  // payload is the masked tensor
             const uint8_t* in = payload + d.payload_off;
@@ -715,6 +714,7 @@ __global__ void __launch_bounds__(kTeam) rans_decode_kernel(const TensorDesc* __
                 const uint32_t jb = (uint32_t)(i % d.es);
                 d.dst[i] = jb < d.spe ? sidecar[d.sidecar_off + (i / d.es) * d.spe + jb] : in[i];
             }
+            __syncthreads();  // s_ticket may be rewritten only after everyone has read it
             continue;
         }
         if (d.es == 4 && d.spe == 2)
@@ -723,6 +723,8 @@ __global__ void __launch_bounds__(kTeam) rans_decode_kernel(const TensorDesc* __
             decode_tensor<2, 1>(d, ti, freq_tables, cum_tables, hdrs, payload, sidecar, check_zero_lanes, status, smem);
         else if (kInts)
             decode_tensor<4, 0>(d, ti, freq_tables, cum_tables, hdrs, payload, sidecar, check_zero_lanes, status, smem);
+        else
+            __syncthreads();
     }
 }
 

@@ -94,20 +94,22 @@ uint32_t emu_encode(size_t n, const uint8_t* const* srcs, const uint64_t* n_byte
     std::vector<LaneHeader> hdrs(n * 256);
     std::vector<unsigned long long> lsrc(n * 256);
     std::vector<uint32_t> loff(n * 256);
-    std::vector<ZeroRec> zrec(n);
+    std::vector<uint32_t> order(n);
+    for (size_t i = 0; i < n; ++i) order[i] = (uint32_t)(n - 1 - i);  // any permutation must give the same result
+    uint32_t ticket = 0;
     std::vector<unsigned long long> psize(n), poff(n + 1);
     uint32_t status = 0;
     emu::launch((unsigned)((n + 127) / 128), 128, 0,
-                [&] { zero_lane_kernel(b.descs.data(), enc.data(), scr, zrec.data(), (uint32_t)n); });
+                [&] { zero_lane_kernel(b.descs.data(), enc.data(), scr, hdrs.data(), lsrc.data(), (uint32_t)n); });
     if (float_only)  // the variant the pipeline uses for float-only batches without missing symbols
         emu::launch(grid, kTeam, sizeof(EncSmem<2>), [&] {
-            rans_encode_kernel<false, false>(b.descs.data(), enc.data(), scr, hdrs.data(), lsrc.data(), zrec.data(),
-                                             (uint32_t)n);
+            rans_encode_kernel<false, false>(b.descs.data(), enc.data(), scr, hdrs.data(), lsrc.data(), order.data(),
+                                             &ticket, (uint32_t)n);
         });
     else
         emu::launch(grid, kTeam, sizeof(EncSmem<4>), [&] {
-            rans_encode_kernel<true, true>(b.descs.data(), enc.data(), scr, hdrs.data(), lsrc.data(), zrec.data(),
-                                           (uint32_t)n);
+            rans_encode_kernel<true, true>(b.descs.data(), enc.data(), scr, hdrs.data(), lsrc.data(), order.data(),
+                                           &ticket, (uint32_t)n);
         });
     emu::launch(grid, 256, 0, [&] { lane_scan_kernel(b.descs.data(), hdrs.data(), psize.data(), loff.data(), (uint32_t)n); });
     emu::launch(1, 1024, 0, [&] { tensor_scan_kernel(b.descs.data(), psize.data(), poff.data(), (uint32_t)n); });
@@ -131,15 +133,18 @@ void emu_decode(size_t n, uint8_t* const* dsts, const uint64_t* n_bytes, const u
         if (raw[i]) b.descs[i].flags |= kFlagRaw;
     }
     std::memset(status_out, 0, n * 4);
+    std::vector<uint32_t> order(n);
+    for (size_t i = 0; i < n; ++i) order[i] = (uint32_t)(n - 1 - i);
+    uint32_t ticket = 0;
     if (float_only)
         emu::launch(grid, kTeam, kDecSmemBytes2, [&] {
-            rans_decode_kernel<false>(b.descs.data(), nf, cf, (const LaneHeader*)hdrs, payload, sidecar, (uint32_t)n,
-                                      check_zero_lanes, status_out);
+            rans_decode_kernel<false>(b.descs.data(), nf, cf, (const LaneHeader*)hdrs, payload, sidecar, order.data(),
+                                      &ticket, (uint32_t)n, check_zero_lanes, status_out);
         });
     else
         emu::launch(grid, kTeam, kDecSmemBytes4, [&] {
-            rans_decode_kernel<true>(b.descs.data(), nf, cf, (const LaneHeader*)hdrs, payload, sidecar, (uint32_t)n,
-                                     check_zero_lanes, status_out);
+            rans_decode_kernel<true>(b.descs.data(), nf, cf, (const LaneHeader*)hdrs, payload, sidecar, order.data(),
+                                     &ticket, (uint32_t)n, check_zero_lanes, status_out);
         });
 }
 
