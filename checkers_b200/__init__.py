@@ -8,9 +8,9 @@ from ._lib import (BF16, CAT_EXP_AVG, CAT_EXP_AVG_SQ, CAT_MASTER, CAT_MODEL, DTY
                    I32, CheckersError)
 from .api import (analyze_tensors, compress_and_save, current_context, initialize_context, load_and_decompress,
                   register_tensors)
-from .context import Context, normalize_histogram
+from .context import STATIC_MAX_TENSOR_BYTES, Context, encode_tensor_static, normalize_histogram
 from .manifest import build_manifest, gather_summaries, write_manifest
 
 __all__ = ["Context", "CheckersError", "initialize_context", "analyze_tensors", "compress_and_save",
            "load_and_decompress", "register_tensors", "current_context", "normalize_histogram", "build_manifest",
-           "gather_summaries", "write_manifest", "F32", "BF16", "F16", "I8", "I32"]
+           "gather_summaries", "write_manifest", "encode_tensor_static", "STATIC_MAX_TENSOR_BYTES", "F32", "BF16", "F16", "I8", "I32"]

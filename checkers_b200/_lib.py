@@ -59,6 +59,8 @@ def _load():
         "chk_get_timing": (C.c_int, [vp, C.c_char_p, C.POINTER(C.c_double)]),
         "chk_kernel_launches": (C.c_int, [vp, C.POINTER(u64)]),
         "chk_get_stream": (C.c_int, [vp, C.POINTER(vp)]),
+        "chk_encode_tensor_static": (C.c_int, [vp, u64, C.c_uint8, u32p, u32p, vp, vp, C.POINTER(u64),
+                                               C.POINTER(C.c_int), vp]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)

@@ -190,6 +190,25 @@ class Context:
         return n.value
 
 
+STATIC_MAX_TENSOR_BYTES = 4 << 20
+
+
+def encode_tensor_static(src_ptr, num_elements, dtype, norm_freq, cum_freq, payload_ptr, lane_headers_ptr, stream=0):
+    """Encode one tensor using only the fixed scratch region built into the library:
+    nothing is allocated on the device or in pinned memory, so it is safe where the
+    allocator must not be touched (HBM full at checkpoint time, memory owned by another
+    framework).  Limited to STATIC_MAX_TENSOR_BYTES per tensor; calls on one GPU must
+    not overlap.  Returns (payload_size, is_raw)."""
+    nf = np.ascontiguousarray(norm_freq, np.uint32)
+    cf = np.ascontiguousarray(cum_freq, np.uint32)
+    size, raw = C.c_uint64(), C.c_int()
+    u32p = C.POINTER(C.c_uint32)
+    check(lib.chk_encode_tensor_static(C.c_void_p(src_ptr), int(num_elements), int(dtype), nf.ctypes.data_as(u32p),
+                                       cf.ctypes.data_as(u32p), C.c_void_p(payload_ptr), C.c_void_p(lane_headers_ptr),
+                                       C.byref(size), C.byref(raw), C.c_void_p(stream)))
+    return size.value, bool(raw.value)
+
+
 def normalize_histogram(hist, ensure_full_alphabet=False, repair=False):
     """Host table normalisation (no device involved).  Returns (norm_freq, cum_freq, x_max, sum)."""
     hist = np.ascontiguousarray(hist, np.uint32)

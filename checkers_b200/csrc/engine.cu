@@ -21,7 +21,9 @@
 #include <cstring>
 #include <filesystem>
 #include <fstream>
+#include <cstddef>
 #include <map>
+#include <mutex>
 #include <string>
 #include <thread>
 #include <unordered_map>
@@ -1228,3 +1230,143 @@ int chk_kernel_launches(chk_context* c, uint64_t* count) {
 }
 
 }  // extern "C"
+
+// ====================================================================== encode without allocating
+// chk_encode_tensor_static: the rANS encode of ONE tensor whose working memory
+// (lane scratch regions, offset tables, the uploaded frequency table, the
+// ticket counter) lives in a fixed device array that is part of the library
+// image, so the call performs no device or pinned-host allocation at all.
+//
+// Who needs it: code that compresses state at the moment device memory is
+// fullest or is owned by someone else -- a checkpoint hook that fires at the
+// peak of a training step, a process whose whole HBM is held by another
+// framework's caching allocator, a serving loop that may not block on the
+// allocator.  For those callers cudaMalloc can fail, synchronise the device or
+// fragment a pool; a fixed region cannot.
+//
+// The price: every GPU that loads this library carries kStaticScratchBytes
+// (about 8.3 MiB) until the process exits, tensors are limited to
+// CHK_STATIC_MAX_TENSOR_BYTES, all calls on a device share the one region
+// (calls that overlap on the GPU would corrupt each other -- issue them on one
+// stream or order them yourself), and the region keeps the previous call's
+// contents (the call clears the few words that must start at zero).
+namespace chk {
+
+constexpr unsigned long long kStaticMaxTensorBytes = CHK_STATIC_MAX_TENSOR_BYTES;
+constexpr uint32_t kStaticChunkStride = (uint32_t)(2 * ((kStaticMaxTensorBytes + 255) / 256));  // bytes per lane
+
+struct StaticScratch {
+    TensorDesc desc;
+    uint32_t order[4];
+    uint32_t ticket[4];
+    unsigned long long payload_size[2];
+    unsigned long long payload_off[2];
+    EncEntry enc[256];
+    unsigned long long lane_src[256];
+    uint32_t lane_off[256];
+    alignas(256) uint8_t lanes[256ull * kStaticChunkStride + 256];  // lane regions are written 16 bytes at a time
+};
+constexpr size_t kStaticScratchBytes = sizeof(StaticScratch);
+static_assert(offsetof(StaticScratch, lanes) % 16 == 0 && offsetof(StaticScratch, lane_src) % 8 == 0 &&
+                  offsetof(StaticScratch, payload_size) % 8 == 0,
+              "static scratch members must keep their natural alignment");
+
+// In host code this name is only a handle for cudaGetSymbolAddress; the device
+// address it stands for is looked up once per device below.
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+static std::mutex g_static_mutex;
+static unsigned char* g_static_addr[64] = {};  // per device ordinal
+
+// First call on a device: resolve the array's device address with that device current.
+static unsigned char* static_scratch_for_current_device() {
+    int dev = -1;
+    CHK_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) throw Error{CHK_ERR_INVALID, "device ordinal out of range for the static scratch table"};
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    if (!g_static_addr[dev]) {
+        void* p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess || !p)
+            throw Error{CHK_ERR_CUDA, std::string("cudaGetSymbolAddress(static scratch): ") + cudaGetErrorString(e)};
+        g_static_addr[dev] = static_cast<unsigned char*>(p);
+    }
+    return g_static_addr[dev];
+}
+
+}  // namespace chk
+
+extern "C" int chk_encode_tensor_static(const void* d_src, uint64_t num_elements, uint8_t dtype,
+                                        const uint32_t norm_freq[256], const uint32_t cum_freq[257],
+                                        void* d_payload, void* d_lane_headers, uint64_t* payload_size_out,
+                                        int* is_raw_out, void* stream) {
+    CHK_API_BEGIN
+    CHK_REQUIRE(d_src && norm_freq && cum_freq && d_payload && d_lane_headers && payload_size_out, "NULL argument");
+    const uint32_t es = elem_size(dtype), spe = sidecar_per_elem(dtype);
+    CHK_REQUIRE(es != 0, "unknown dtype");
+    CHK_REQUIRE(num_elements != 0, "empty tensor");
+    const unsigned long long bytes = (unsigned long long)num_elements * es;
+    if (bytes > kStaticMaxTensorBytes)
+        throw chk::Error{CHK_ERR_CAPACITY, "tensor of " + std::to_string(bytes) + " bytes exceeds the fixed scratch limit of " +
+                                               std::to_string(kStaticMaxTensorBytes) + " bytes (CHK_STATIC_MAX_TENSOR_BYTES)"};
+    unsigned char* base = static_scratch_for_current_device();
+    StaticScratch* dev = reinterpret_cast<StaticScratch*>(base);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+
+    // host-side image of the small header part (desc .. enc); lives on this stack frame only
+    struct Head {
+        TensorDesc desc;
+        uint32_t order[4];
+        uint32_t ticket[4];
+        unsigned long long payload_size[2];
+        unsigned long long payload_off[2];
+        EncEntry enc[256];
+    } head;
+    static_assert(offsetof(StaticScratch, lane_src) == sizeof(Head), "header layout");
+    std::memset(&head, 0, sizeof(head));  // order[0] = 0, ticket = 0, sizes = 0
+    const unsigned long long c_max = (bytes + 255) / 256;
+    head.desc.src = static_cast<const uint8_t*>(d_src);
+    head.desc.n_bytes = bytes;
+    head.desc.es = es;
+    head.desc.spe = spe;
+    head.desc.table_idx = 0;
+    head.desc.scratch_off = offsetof(StaticScratch, lanes);
+    head.desc.chunk_stride = (uint32_t)((2 * c_max + 15) & ~15ull);
+    FreqTable ft;
+    std::memcpy(ft.norm_freq, norm_freq, 1024);
+    std::memcpy(ft.cum_freq, cum_freq, 1028);
+    ft.sum = cum_freq[256];
+    build_enc_entries(ft, head.enc);
+    bool escape = false;
+    for (int i = 0; i < 256 && !escape; ++i) escape = norm_freq[i] == 0;
+
+    // pageable source: the runtime stages it before returning, so the stack frame may go away
+    CHK_CUDA(cudaMemcpyAsync(base, &head, sizeof(head), cudaMemcpyHostToDevice, s));
+    const bool ints = spe * 2 != es;
+    zero_lane_kernel<<<1, 128, 0, s>>>(&dev->desc, dev->enc, base, static_cast<LaneHeader*>(d_lane_headers), dev->lane_src,
+                                       1u);
+    CHK_CUDA(cudaGetLastError());
+    auto kernel = ints ? (escape ? rans_encode_kernel<true, true> : rans_encode_kernel<true, false>)
+                       : (escape ? rans_encode_kernel<false, true> : rans_encode_kernel<false, false>);
+    kernel<<<1, kTeam, ints ? sizeof(EncSmem<4>) : sizeof(EncSmem<2>), s>>>(
+        &dev->desc, dev->enc, base, static_cast<LaneHeader*>(d_lane_headers), dev->lane_src, dev->order, dev->ticket, 1u);
+    CHK_CUDA(cudaGetLastError());
+    lane_scan_kernel<<<1, 256, 0, s>>>(&dev->desc, static_cast<LaneHeader*>(d_lane_headers), dev->payload_size,
+                                       dev->lane_off, 1u);
+    CHK_CUDA(cudaGetLastError());
+    tensor_scan_kernel<<<1, 1024, 0, s>>>(&dev->desc, dev->payload_size, dev->payload_off, 1u);
+    CHK_CUDA(cudaGetLastError());
+    compact_kernel<<<32, 256, 0, s>>>(&dev->desc, static_cast<const LaneHeader*>(d_lane_headers), dev->lane_src,
+                                      dev->lane_off, base, static_cast<uint8_t*>(d_payload), 1u);
+    CHK_CUDA(cudaGetLastError());
+    struct {
+        unsigned long long size;
+        TensorDesc desc;
+    } back;
+    CHK_CUDA(cudaMemcpyAsync(&back.size, dev->payload_size, 8, cudaMemcpyDeviceToHost, s));
+    CHK_CUDA(cudaMemcpyAsync(&back.desc, &dev->desc, sizeof(TensorDesc), cudaMemcpyDeviceToHost, s));
+    CHK_CUDA(cudaStreamSynchronize(s));
+    *payload_size_out = back.size;
+    if (is_raw_out) *is_raw_out = (back.desc.flags & kFlagRaw) ? 1 : 0;
+    CHK_API_END
+}

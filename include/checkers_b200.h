@@ -136,6 +136,42 @@ int chk_get_stream(chk_context* ctx, void** stream_out);
 /* Kernels launched by this context since creation. */
 int chk_kernel_launches(chk_context* ctx, uint64_t* count);
 
+/* ---- encode one tensor without allocating anything -----------------------
+ * Has no counterpart in the reference (which allocates and frees device
+ * buffers per tensor, src/ANSCompressor.cpp:348-388).
+ *
+ * For callers that must not allocate when they compress: a checkpoint hook
+ * running while the training step holds nearly all of HBM, a process whose
+ * device memory belongs to another framework's allocator, a latency-bound loop
+ * that cannot risk the allocator synchronising the device.  Every other entry
+ * point of this library takes its working memory from a CUDA memory pool; this
+ * one uses a fixed region compiled into the library, calls no allocation
+ * routine of any kind, needs no context, and is limited to tensors of at most
+ * CHK_STATIC_MAX_TENSOR_BYTES bytes (larger ones return CHK_ERR_CAPACITY).
+ *
+ *   d_src            device pointer, num_elements of `dtype`
+ *   norm_freq/cum_freq  HOST arrays: the table to encode with (e.g. from
+ *                    chk_normalize_histogram over the tensor's masked bytes)
+ *   d_payload        device buffer of at least num_elements*elem_size bytes;
+ *                    receives the lane streams laid out as in the .ansc data
+ *                    section, or the masked tensor if the passthrough rule fires
+ *   d_lane_headers   device buffer of 256*16 bytes; receives the on-disk headers
+ *   payload_size_out, is_raw_out   host results
+ *   stream           cudaStream_t to run on (NULL = the default stream)
+ *
+ * The region is per GPU and costs about 8.3 MiB of device memory on every GPU
+ * the library is loaded on, for the life of the process.  All calls on one GPU
+ * share it: calls that could overlap on the device must be serialised by the
+ * caller (same stream, or explicit ordering).  It keeps the last call's bytes;
+ * the call itself resets what has to start at zero.  The first call on each
+ * device looks the region's address up (cudaGetSymbolAddress) with that device
+ * current: make that first call before any stream capture begins.  The call
+ * returns after the stream has drained. */
+#define CHK_STATIC_MAX_TENSOR_BYTES (4u << 20)
+int chk_encode_tensor_static(const void* d_src, uint64_t num_elements, uint8_t dtype, const uint32_t norm_freq[256],
+                             const uint32_t cum_freq[257], void* d_payload, void* d_lane_headers,
+                             uint64_t* payload_size_out, int* is_raw_out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
