@@ -53,9 +53,15 @@ namespace emu {
 constexpr size_t kStack = 128 * 1024;
 struct Fiber {
     ucontext_t ctx;
-    std::vector<char> stack;
+    char* stack = nullptr;  // from a pool that is allocated once and reused by every block
     bool done = false;
 };
+// Fiber stacks are not zeroed and never freed: blocks run one after another and reuse them.
+static char* fiber_stack(unsigned t) {
+    static std::vector<char*> pool;
+    while (pool.size() <= t) pool.push_back(static_cast<char*>(std::malloc(kStack)));
+    return pool[t];
+}
 static ucontext_t g_main;
 static std::vector<Fiber>* g_fibers = nullptr;
 static unsigned g_cur = 0;
@@ -103,9 +109,9 @@ static void run_block(unsigned nthreads, std::function<void()> body) {
     g_bar_arrived = 0;
     for (unsigned t = 0; t < nthreads; ++t) {
         Fiber& f = fibers[t];
-        f.stack.resize(kStack);
+        f.stack = fiber_stack(t);
         getcontext(&f.ctx);
-        f.ctx.uc_stack.ss_sp = f.stack.data();
+        f.ctx.uc_stack.ss_sp = f.stack;
         f.ctx.uc_stack.ss_size = kStack;
         f.ctx.uc_link = &g_main;
         makecontext(&f.ctx, trampoline, 0);

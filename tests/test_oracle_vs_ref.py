@@ -8,9 +8,9 @@ import pytest
 
 from oracle_lib import ELEM_SIZE, SIDECAR_PER_ELEM, synth
 
-CASES = [("bf16_weight", 65536), ("f32_master", 32768), ("f32_exp_avg", 8192), ("f32_exp_avg_sq", 10001),
-         ("f32_exp_avg_sq_lognormal", 5000), ("bf16_norm_gain", 4097), ("f16_weight", 3000), ("i8", 1000), ("i32", 777),
-         ("f32_uniform_bits", 20000), ("bf16_weight", 3), ("f32_master", 1), ("i8", 255), ("i8", 256), ("i8", 257)]
+CASES = [("bf16_weight", 8192), ("f32_master", 4096), ("f32_exp_avg", 2048), ("f32_exp_avg_sq", 2501),
+         ("f32_exp_avg_sq_lognormal", 1500), ("bf16_norm_gain", 4097), ("f16_weight", 3000), ("i8", 1000), ("i32", 777),
+         ("f32_uniform_bits", 3000), ("bf16_weight", 3), ("f32_master", 1), ("i8", 255), ("i8", 256), ("i8", 257)]
 
 
 @pytest.mark.parametrize("kind,n", CASES)
@@ -47,7 +47,7 @@ def test_normalize_random_and_adversarial(oracle, ref):
     h = np.zeros(256, np.uint32); h[0] = 2 ** 31; h[255] = 1; hists.append(h)
     h = np.ones(256, np.uint32); h[0] = 10 ** 6; hists.append(h)           # many ties at the minimum
     h = np.zeros(256, np.uint32); h[:20] = 5; hists.append(h)              # all fractions equal
-    for _ in range(300):
+    for _ in range(120):
         k = int(rng.integers(1, 257))
         h = np.zeros(256, np.uint32)
         h[rng.choice(256, k, replace=False)] = rng.integers(1, 10 ** int(rng.integers(1, 8)), k)
