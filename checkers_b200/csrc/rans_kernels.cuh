@@ -67,15 +67,13 @@ __device__ __forceinline__ void enc_step(uint32_t sym, const uint4* tab, uint32_
         return;
     }
     const uint32_t xmax = e.y << 19;  // freq * 2^19 (the shift field falls off the top)
-    const bool e1 = x >= xmax;
-    const bool e2 = (x >> 8) >= xmax;
-    if (e1) {
+    if (x >= xmax) {
         enc_emit(o, x);
         x >>= 8;
-    }
-    if (e2) {
-        enc_emit(o, x);
-        x >>= 8;
+        if (x >= xmax) {  // a second byte needs freq < 16: rare, so most warps skip this as a whole
+            enc_emit(o, x);
+            x >>= 8;
+        }
     }
     const uint32_t q = __umulhi(x, e.x) >> (e.y >> 16);
     x = x + q * e.w + e.z;
@@ -450,10 +448,20 @@ __global__ void __launch_bounds__(256) compact_kernel(const TensorDesc* __restri
 }
 
 // ------------------------------------------------------------------ rANS decode
-// Decode table entry: symbol[0:8) | (freq-1)[8:20) | (slot - cum[symbol])[20:32)
+// Two table shapes, chosen at compile time by kDecTwoLevel:
+//   one level : slot -> symbol[0:8) | (freq-1)[8:20) | (slot - cum[symbol])[20:32)     16 KiB per tensor
+//   two levels: slot -> symbol (1 byte), symbol -> freq[0:16) | cum[16:32)              5 KiB per tensor
+// The second costs one more dependent shared-memory load per symbol but lets about
+// twice as many teams be resident on an SM.
+#ifndef CHK_DEC_TWO_LEVEL
+#define CHK_DEC_TWO_LEVEL 1
+#endif
+constexpr bool kDecTwoLevel = CHK_DEC_TWO_LEVEL != 0;
+
 template <int NV>
 struct DecSmem {
-    uint32_t dtab[kM];
+    uint32_t dtab[kDecTwoLevel ? 256 : kM];  // two levels: freq | cum<<16 per symbol
+    uint8_t slot_sym[kDecTwoLevel ? kM : 4];
     // 64-byte input ring per chain plus one word whose first byte mirrors ring byte 0
     // (so byte p+1 is always at address p+1); 17 words apart keeps a warp conflict-free
     uint32_t ring[NV * kTeam * 17];
@@ -509,16 +517,26 @@ __device__ __forceinline__ uint32_t put_byte(uint32_t acc, uint32_t v, uint32_t 
 // stream bytes without branching: the two candidate bytes are placed at the top
 // of a word and funnel-shifted into the state by 0, 8 or 16 bits.  Returns the
 // table entry (symbol in its low byte).
-__device__ __forceinline__ uint32_t dec_step(DecChain& c, const uint32_t* dtab, const uint8_t* ring_bytes) {
-    const uint32_t e = dtab[c.x & (kM - 1)];
+__device__ __forceinline__ uint32_t dec_step(DecChain& c, const uint32_t* dtab, const uint8_t* slot_sym,
+                                             const uint8_t* ring_bytes) {
+    const uint32_t slot = c.x & (kM - 1);
     const uint32_t xs = c.x >> kScaleBits;
-    const uint32_t x = ((e >> 8) & 0xFFFu) * xs + xs + (e >> 20);
+    uint32_t x, sym;
+    if (kDecTwoLevel) {
+        sym = slot_sym[slot];
+        const uint32_t t = dtab[sym];
+        x = (t & 0xFFFFu) * xs + slot - (t >> 16);
+    } else {
+        const uint32_t e = dtab[slot];
+        sym = e;
+        x = ((e >> 8) & 0xFFFu) * xs + xs + (e >> 20);
+    }
     const uint8_t* rp = ring_bytes + (c.rel & 63);
-    const uint32_t top = ((uint32_t)rp[0] << 24) | ((uint32_t)rp[1] << 16);
+    const uint32_t top = __byte_perm(rp[0], rp[1], 0x0411);  // rp[0] to bits 31..24, rp[1] to bits 23..16
     const uint32_t n = (x < kL ? 1u : 0u) + (x < (1u << 15) ? 1u : 0u);
     c.x = __funnelshift_l(top, x, n * 8);
     c.rel += n;
-    return e;
+    return sym;
 }
 
 template <int NV, int B0>
@@ -544,8 +562,13 @@ __device__ __forceinline__ void decode_tensor(const TensorDesc& d, uint32_t ti,
             const uint32_t mid = (lo + hi) >> 1;
             if (sm->cum[mid] <= slot) lo = mid; else hi = mid;
         }
-        sm->dtab[slot] = lo | ((fq[lo] - 1) << 8) | ((slot - sm->cum[lo]) << 20);
+        if (kDecTwoLevel)
+            sm->slot_sym[slot] = (uint8_t)lo;
+        else
+            sm->dtab[slot] = lo | ((fq[lo] - 1) << 8) | ((slot - sm->cum[lo]) << 20);
     }
+    if (kDecTwoLevel)
+        for (uint32_t sy = j; sy < 256; sy += kTeam) sm->dtab[sy] = fq[sy] | (sm->cum[sy] << 16);
 
     DecChain ch[NV];
     uint32_t* ringw[NV];
@@ -618,7 +641,7 @@ __device__ __forceinline__ void decode_tensor(const TensorDesc& d, uint32_t ti,
         for (int u = 0; u < 8; ++u) {
             uint32_t acc = side[u];
 #pragma unroll
-            for (int k = 0; k < NV; ++k) acc = put_byte(acc, dec_step(ch[k], sm->dtab, ringb[k]), chain_byte<NV, B0>(k));
+            for (int k = 0; k < NV; ++k) acc = put_byte(acc, dec_step(ch[k], sm->dtab, sm->slot_sym, ringb[k]), chain_byte<NV, B0>(k));
             store_word(r + u, acc);
         }
 #pragma unroll
@@ -635,14 +658,14 @@ __device__ __forceinline__ void decode_tensor(const TensorDesc& d, uint32_t ti,
     for (; r < full_rows; ++r) {
         uint32_t acc = side_word(r);
 #pragma unroll
-        for (int k = 0; k < NV; ++k) acc = put_byte(acc, dec_step(ch[k], sm->dtab, ringb[k]), chain_byte<NV, B0>(k));
+        for (int k = 0; k < NV; ++k) acc = put_byte(acc, dec_step(ch[k], sm->dtab, sm->slot_sym, ringb[k]), chain_byte<NV, B0>(k));
         store_word(r, acc);
     }
     if (tail) {
         uint32_t acc = 0;
 #pragma unroll
         for (int k = 0; k < NV; ++k)
-            if (4 * j + chain_byte<NV, B0>(k) < tail) acc = put_byte(acc, dec_step(ch[k], sm->dtab, ringb[k]), chain_byte<NV, B0>(k));
+            if (4 * j + chain_byte<NV, B0>(k) < tail) acc = put_byte(acc, dec_step(ch[k], sm->dtab, sm->slot_sym, ringb[k]), chain_byte<NV, B0>(k));
 #pragma unroll
         for (uint32_t b = 0; b < 4; ++b) {
             const uint32_t t = 4 * j + b;
@@ -672,9 +695,16 @@ __device__ __forceinline__ void decode_tensor(const TensorDesc& d, uint32_t ti,
             uint32_t x = h.final_state;
             bool bad = false;
             for (unsigned long long i = 0; i < n && !bad; ++i) {
-                const uint32_t e = sm->dtab[x & (kM - 1)];
-                if (e & 0xFFu) bad = true;  // must decode to symbol 0
-                x = (((e >> 8) & 0xFFFu) + 1u) * (x >> kScaleBits) + (e >> 20);
+                const uint32_t slot = x & (kM - 1);
+                if (kDecTwoLevel) {
+                    const uint32_t sy = sm->slot_sym[slot], t = sm->dtab[sy];
+                    if (sy) bad = true;  // must decode to symbol 0
+                    x = (t & 0xFFFFu) * (x >> kScaleBits) + slot - (t >> 16);
+                } else {
+                    const uint32_t e = sm->dtab[slot];
+                    if (e & 0xFFu) bad = true;
+                    x = (((e >> 8) & 0xFFFu) + 1u) * (x >> kScaleBits) + (e >> 20);
+                }
                 while (x < kL && !bad) {
                     if (p >= end) bad = true; else x = (x << 8) | *p++;
                 }
