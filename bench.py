@@ -202,6 +202,7 @@ def main():
     ap.add_argument("--cpu-sample-elems", type=int, default=32 << 20, help="parameters in the timed CPU sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--opt", action="append", default=[], help="library option key=value (chk_set_option)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -232,6 +233,9 @@ def main():
     tags = (chk.BF16, chk.F32, chk.F32, chk.F32)
 
     ctx = chk.Context(device=local_rank, rank=rank, local_rank=local_rank)
+    for kv in args.opt:
+        k, v = kv.split("=")
+        ctx.set_option(k, int(v))
     dst = []
     for name, off, n, _ in pieces:
         for (prefix, _), b, o, tag in zip(STATE_KINDS, bufs, outs, tags):

@@ -115,7 +115,7 @@ struct Context {
     std::vector<StatsOut> stats;
 
     bool repair_tables = false, verify_zero_lanes = false;
-    bool enc_attr_set = false, dec_attr_set = false;
+    bool decode_two_level = false;
     int host_threads = 0;
 
     // device buffers (grow-only, from the context's pool)
@@ -636,13 +636,11 @@ static void run_decode(Context* c, size_t W, const uint8_t* d_payload, const uin
     bool any_int = false;
     const TensorDesc* hd = static_cast<const TensorDesc*>(c->h_descs.p);
     for (size_t i = 0; i < W && !any_int; ++i) any_int = hd[i].spe * 2 != hd[i].es;
-    const uint32_t smem = any_int ? kDecSmemBytes4 : kDecSmemBytes2;
+    const bool tl = c->decode_two_level;
+    const uint32_t smem = kDecSmemBytes[any_int ? 1 : 0][tl ? 1 : 0];
     upload_order(c, W, [&](size_t i) { return hd[i].n_bytes; });
-    auto kernel = any_int ? rans_decode_kernel<true> : rans_decode_kernel<false>;
-    if (smem > 48 * 1024 && !c->dec_attr_set) {
-        CHK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        c->dec_attr_set = true;
-    }
+    auto kernel = any_int ? (tl ? rans_decode_kernel<true, true> : rans_decode_kernel<true, false>)
+                          : (tl ? rans_decode_kernel<false, true> : rans_decode_kernel<false, false>);
     const uint32_t grid = persistent_grid(c, reinterpret_cast<const void*>(kernel), smem, W);
     CHK_CUDA(cudaEventRecord(c->ev[1], s));
     kernel<<<grid, kTeam, smem, s>>>(static_cast<const TensorDesc*>(c->d_descs.p), d_freq, d_cum, d_hdrs, d_payload,
@@ -1028,6 +1026,8 @@ int chk_set_option(chk_context* c, const char* key, int64_t value) {
         c->verify_zero_lanes = value != 0;
     else if (k == "host_threads")
         c->host_threads = (int)value;
+    else if (k == "decode_two_level")
+        c->decode_two_level = value != 0;
     else
         throw chk::Error{CHK_ERR_INVALID, "unknown option: " + k};
     CHK_API_END

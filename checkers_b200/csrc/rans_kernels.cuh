@@ -448,27 +448,23 @@ __global__ void __launch_bounds__(256) compact_kernel(const TensorDesc* __restri
 }
 
 // ------------------------------------------------------------------ rANS decode
-// Two table shapes, chosen at compile time by kDecTwoLevel:
+// Two table shapes, chosen per launch by the TL template flag:
 //   one level : slot -> symbol[0:8) | (freq-1)[8:20) | (slot - cum[symbol])[20:32)     16 KiB per tensor
 //   two levels: slot -> symbol (1 byte), symbol -> freq[0:16) | cum[16:32)              5 KiB per tensor
 // The second costs one more dependent shared-memory load per symbol but lets about
 // twice as many teams be resident on an SM.
-#ifndef CHK_DEC_TWO_LEVEL
-#define CHK_DEC_TWO_LEVEL 1
-#endif
-constexpr bool kDecTwoLevel = CHK_DEC_TWO_LEVEL != 0;
-
-template <int NV>
+template <int NV, bool TL>
 struct DecSmem {
-    uint32_t dtab[kDecTwoLevel ? 256 : kM];  // two levels: freq | cum<<16 per symbol
-    uint8_t slot_sym[kDecTwoLevel ? kM : 4];
+    uint32_t dtab[TL ? 256 : kM];  // two levels: freq | cum<<16 per symbol
+    uint8_t slot_sym[TL ? kM : 4];
     // 64-byte input ring per chain plus one word whose first byte mirrors ring byte 0
     // (so byte p+1 is always at address p+1); 17 words apart keeps a warp conflict-free
     uint32_t ring[NV * kTeam * 17];
     uint32_t cum[260];
 };
-constexpr uint32_t kDecSmemBytes2 = sizeof(DecSmem<2>);  // float tensors only
-constexpr uint32_t kDecSmemBytes4 = sizeof(DecSmem<4>);  // batches that contain integer tensors
+// shared memory per team: [chains per thread: 2 = float tensors only, 4 = integers present][table shape]
+constexpr uint32_t kDecSmemBytes[2][2] = {{(uint32_t)sizeof(DecSmem<2, false>), (uint32_t)sizeof(DecSmem<2, true>)},
+                                          {(uint32_t)sizeof(DecSmem<4, false>), (uint32_t)sizeof(DecSmem<4, true>)}};
 
 struct DecChain {
     uint32_t x;
@@ -517,12 +513,13 @@ __device__ __forceinline__ uint32_t put_byte(uint32_t acc, uint32_t v, uint32_t 
 // stream bytes without branching: the two candidate bytes are placed at the top
 // of a word and funnel-shifted into the state by 0, 8 or 16 bits.  Returns the
 // table entry (symbol in its low byte).
+template <bool TL>
 __device__ __forceinline__ uint32_t dec_step(DecChain& c, const uint32_t* dtab, const uint8_t* slot_sym,
                                              const uint8_t* ring_bytes) {
     const uint32_t slot = c.x & (kM - 1);
     const uint32_t xs = c.x >> kScaleBits;
     uint32_t x, sym;
-    if (kDecTwoLevel) {
+    if (TL) {
         sym = slot_sym[slot];
         const uint32_t t = dtab[sym];
         x = (t & 0xFFFFu) * xs + slot - (t >> 16);
@@ -539,7 +536,7 @@ __device__ __forceinline__ uint32_t dec_step(DecChain& c, const uint32_t* dtab, 
     return sym;
 }
 
-template <int NV, int B0>
+template <int NV, int B0, bool TL>
 __device__ __forceinline__ void decode_tensor(const TensorDesc& d, uint32_t ti,
                                               const uint32_t* __restrict__ freq_tables,
                                               const uint32_t* __restrict__ cum_tables,
@@ -547,7 +544,7 @@ __device__ __forceinline__ void decode_tensor(const TensorDesc& d, uint32_t ti,
                                               const uint8_t* __restrict__ payload,
                                               const uint8_t* __restrict__ sidecar, uint32_t check_zero_lanes,
                                               uint32_t* __restrict__ status, unsigned char* smem_raw) {
-    DecSmem<NV>* sm = reinterpret_cast<DecSmem<NV>*>(smem_raw);
+    DecSmem<NV, TL>* sm = reinterpret_cast<DecSmem<NV, TL>*>(smem_raw);
     const uint32_t j = threadIdx.x;
     const unsigned long long B = d.n_bytes;
 
@@ -562,12 +559,12 @@ __device__ __forceinline__ void decode_tensor(const TensorDesc& d, uint32_t ti,
             const uint32_t mid = (lo + hi) >> 1;
             if (sm->cum[mid] <= slot) lo = mid; else hi = mid;
         }
-        if (kDecTwoLevel)
+        if (TL)
             sm->slot_sym[slot] = (uint8_t)lo;
         else
             sm->dtab[slot] = lo | ((fq[lo] - 1) << 8) | ((slot - sm->cum[lo]) << 20);
     }
-    if (kDecTwoLevel)
+    if (TL)
         for (uint32_t sy = j; sy < 256; sy += kTeam) sm->dtab[sy] = fq[sy] | (sm->cum[sy] << 16);
 
     DecChain ch[NV];
@@ -641,7 +638,7 @@ __device__ __forceinline__ void decode_tensor(const TensorDesc& d, uint32_t ti,
         for (int u = 0; u < 8; ++u) {
             uint32_t acc = side[u];
 #pragma unroll
-            for (int k = 0; k < NV; ++k) acc = put_byte(acc, dec_step(ch[k], sm->dtab, sm->slot_sym, ringb[k]), chain_byte<NV, B0>(k));
+            for (int k = 0; k < NV; ++k) acc = put_byte(acc, dec_step<TL>(ch[k], sm->dtab, sm->slot_sym, ringb[k]), chain_byte<NV, B0>(k));
             store_word(r + u, acc);
         }
 #pragma unroll
@@ -658,14 +655,14 @@ __device__ __forceinline__ void decode_tensor(const TensorDesc& d, uint32_t ti,
     for (; r < full_rows; ++r) {
         uint32_t acc = side_word(r);
 #pragma unroll
-        for (int k = 0; k < NV; ++k) acc = put_byte(acc, dec_step(ch[k], sm->dtab, sm->slot_sym, ringb[k]), chain_byte<NV, B0>(k));
+        for (int k = 0; k < NV; ++k) acc = put_byte(acc, dec_step<TL>(ch[k], sm->dtab, sm->slot_sym, ringb[k]), chain_byte<NV, B0>(k));
         store_word(r, acc);
     }
     if (tail) {
         uint32_t acc = 0;
 #pragma unroll
         for (int k = 0; k < NV; ++k)
-            if (4 * j + chain_byte<NV, B0>(k) < tail) acc = put_byte(acc, dec_step(ch[k], sm->dtab, sm->slot_sym, ringb[k]), chain_byte<NV, B0>(k));
+            if (4 * j + chain_byte<NV, B0>(k) < tail) acc = put_byte(acc, dec_step<TL>(ch[k], sm->dtab, sm->slot_sym, ringb[k]), chain_byte<NV, B0>(k));
 #pragma unroll
         for (uint32_t b = 0; b < 4; ++b) {
             const uint32_t t = 4 * j + b;
@@ -696,7 +693,7 @@ __device__ __forceinline__ void decode_tensor(const TensorDesc& d, uint32_t ti,
             bool bad = false;
             for (unsigned long long i = 0; i < n && !bad; ++i) {
                 const uint32_t slot = x & (kM - 1);
-                if (kDecTwoLevel) {
+                if (TL) {
                     const uint32_t sy = sm->slot_sym[slot], t = sm->dtab[sy];
                     if (sy) bad = true;  // must decode to symbol 0
                     x = (t & 0xFFFFu) * (x >> kScaleBits) + slot - (t >> 16);
@@ -719,8 +716,8 @@ __device__ __forceinline__ void decode_tensor(const TensorDesc& d, uint32_t ti,
 
 // One team (CTA of 64 threads) per tensor.  Each thread rebuilds one 32-bit word
 // of every row from its decoded bytes and the sidecar and stores it directly.
-// kInts as for the encoder.
-template <bool kInts>
+// kInts as for the encoder; TL selects the table shape.
+template <bool kInts, bool TL>
 __global__ void __launch_bounds__(kTeam) rans_decode_kernel(const TensorDesc* __restrict__ descs,
                                                             const uint32_t* __restrict__ freq_tables,  // [T][256]
                                                             const uint32_t* __restrict__ cum_tables,   // [T][257]
@@ -748,11 +745,11 @@ __global__ void __launch_bounds__(kTeam) rans_decode_kernel(const TensorDesc* __
             continue;
         }
         if (d.es == 4 && d.spe == 2)
-            decode_tensor<2, 2>(d, ti, freq_tables, cum_tables, hdrs, payload, sidecar, check_zero_lanes, status, smem);
+            decode_tensor<2, 2, TL>(d, ti, freq_tables, cum_tables, hdrs, payload, sidecar, check_zero_lanes, status, smem);
         else if (d.es == 2 && d.spe == 1)
-            decode_tensor<2, 1>(d, ti, freq_tables, cum_tables, hdrs, payload, sidecar, check_zero_lanes, status, smem);
+            decode_tensor<2, 1, TL>(d, ti, freq_tables, cum_tables, hdrs, payload, sidecar, check_zero_lanes, status, smem);
         else if (kInts)
-            decode_tensor<4, 0>(d, ti, freq_tables, cum_tables, hdrs, payload, sidecar, check_zero_lanes, status, smem);
+            decode_tensor<4, 0, TL>(d, ti, freq_tables, cum_tables, hdrs, payload, sidecar, check_zero_lanes, status, smem);
         else
             __syncthreads();
     }

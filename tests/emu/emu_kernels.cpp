@@ -137,13 +137,13 @@ void emu_decode(size_t n, uint8_t* const* dsts, const uint64_t* n_bytes, const u
     for (size_t i = 0; i < n; ++i) order[i] = (uint32_t)(n - 1 - i);
     uint32_t ticket = 0;
     if (float_only)
-        emu::launch(grid, kTeam, kDecSmemBytes2, [&] {
-            rans_decode_kernel<false>(b.descs.data(), nf, cf, (const LaneHeader*)hdrs, payload, sidecar, order.data(),
+        emu::launch(grid, kTeam, kDecSmemBytes[0][1], [&] {
+            rans_decode_kernel<false, true>(b.descs.data(), nf, cf, (const LaneHeader*)hdrs, payload, sidecar, order.data(),
                                       &ticket, (uint32_t)n, check_zero_lanes, status_out);
         });
     else
-        emu::launch(grid, kTeam, kDecSmemBytes4, [&] {
-            rans_decode_kernel<true>(b.descs.data(), nf, cf, (const LaneHeader*)hdrs, payload, sidecar, order.data(),
+        emu::launch(grid, kTeam, kDecSmemBytes[1][0], [&] {
+            rans_decode_kernel<true, false>(b.descs.data(), nf, cf, (const LaneHeader*)hdrs, payload, sidecar, order.data(),
                                      &ticket, (uint32_t)n, check_zero_lanes, status_out);
         });
 }
