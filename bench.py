@@ -277,7 +277,7 @@ def main():
     launches0 = ctx.kernel_launches()
     sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    enc_ms, dec_ms, split_ms, compact_ms, table_ms = [], [], [], [], []
+    enc_ms, dec_ms, split_ms, compact_ms, table_ms, cwall_ms, dwall_ms = [], [], [], [], [], [], []
     e0.record(lib_stream)
     for _ in range(args.steps):
         summ = step()
@@ -286,6 +286,8 @@ def main():
         split_ms.append(ctx.timing("split_hist_ms"))
         compact_ms.append(ctx.timing("compact_ms"))
         table_ms.append(ctx.timing("table_ms"))
+        cwall_ms.append(ctx.timing("compress_total_ms"))
+        dwall_ms.append(ctx.timing("decompress_total_ms"))
     e1.record(lib_stream)
     barrier()
     clocks = sampler.stop()
@@ -366,7 +368,8 @@ def main():
                 "per_kernel_ms": {k: v[0] for k, v in kernels.items()},
                 "per_kernel_algorithmic_gbs": {k: (v[1] / (v[0] * 1e-3) / 1e9 if v[0] > 0 else None)
                                                for k, v in kernels.items()},
-                "host_table_ms": float(np.mean(table_ms))}
+                "host_table_ms": float(np.mean(table_ms)),
+                "compress_call_ms": float(np.mean(cwall_ms)), "restore_call_ms": float(np.mean(dwall_ms))}
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:

@@ -119,9 +119,10 @@ struct Context {
     int host_threads = 0;
 
     // device buffers (grow-only, from the context's pool)
-    DevBuf d_descs, d_tiles, d_hist, d_sidecar, d_scratch, d_hdrs, d_lsrc, d_order, d_ticket, d_loff, d_psize, d_poff,
+    DevBuf d_descs, d_tiles, d_hist, d_sidecar, d_scratch, d_hdrs, d_lsrc, d_order, d_ticket, d_loff, d_psize, d_poff, d_nf16,
         d_payload, d_enc, d_freq, d_cum, d_status, d_stats_desc, d_stats_out;
     cudaStream_t side_stream = nullptr;
+    std::vector<cudaEvent_t> seg_events;
     int sm_count = 0;
     // pinned host staging
     PinBuf h_hist, h_hdrs, h_poff, h_descs, h_status, h_enc, h_stats, h_order;
@@ -374,7 +375,8 @@ static void compress(Context* c, bool host_images) {
     pin_ensure(c->h_poff, (W + 1) * 8);
     pin_ensure(c->h_descs, W * sizeof(TensorDesc));
     pin_ensure(c->h_status, 256);
-    pin_ensure(c->h_enc, T * (256 * sizeof(EncEntry) + 256 * 4 + 257 * 4));
+    pin_ensure(c->h_enc, T * 512);
+    dev_ensure(c, c->d_nf16, T * 512);
 
     std::memcpy(c->h_descs.p, c->descs.data(), W * sizeof(TensorDesc));
     CHK_CUDA(cudaEventRecord(c->ev[0], s));
@@ -382,32 +384,66 @@ static void compress(Context* c, bool host_images) {
     CHK_CUDA(cudaMemcpyAsync(c->d_tiles.p, tile_start.data(), (W + 1) * 4, cudaMemcpyHostToDevice, s));
     CHK_CUDA(cudaMemsetAsync(c->d_hist.p, 0, W * 1024, s));
 
-    // ---- stage 1: low bytes out, histograms
+    // ---- stage 1: low bytes out, histograms.  The batch is cut into a few segments of
+    // about equal bytes; each segment's histograms are copied back as soon as its launch
+    // is done, so the host normalises segment g while the device still counts g+1.
+    const size_t n_seg = W >= 64 ? 8 : 1;
+    std::vector<size_t> seg_end(n_seg, W);
     {
-        const uint32_t total_tiles = tile_start[W];
-        const uint32_t grid = total_tiles < 148u * 8u ? total_tiles : 148u * 8u;
-        split_hist_kernel<<<grid, 256, 0, s>>>(static_cast<const TensorDesc*>(c->d_descs.p),
-                                               static_cast<const uint32_t*>(c->d_tiles.p), (uint32_t)W, total_tiles,
-                                               static_cast<uint8_t*>(c->d_sidecar.p),
-                                               static_cast<uint32_t*>(c->d_hist.p));
-        CHK_CUDA(cudaGetLastError());
-        c->launches++;
+        unsigned long long acc = 0;
+        size_t g = 0;
+        for (size_t i = 0; i < W && g + 1 < n_seg; ++i) {
+            acc += c->descs[i].n_bytes;
+            if (acc >= bytes_total * (g + 1) / n_seg) seg_end[g++] = i + 1;
+        }
+    }
+    if (c->seg_events.size() < n_seg) {
+        const size_t old = c->seg_events.size();
+        c->seg_events.resize(n_seg);
+        for (size_t g = old; g < n_seg; ++g) CHK_CUDA(cudaEventCreateWithFlags(&c->seg_events[g], cudaEventDisableTiming));
+    }
+    for (size_t g = 0, a = 0; g < n_seg; ++g) {
+        const size_t b = seg_end[g];
+        if (b > a) {
+            const uint32_t tiles = tile_start[b] - tile_start[a];
+            const uint32_t grid = tiles < 148u * 8u ? tiles : 148u * 8u;
+            split_hist_kernel<<<grid, 256, 0, s>>>(static_cast<const TensorDesc*>(c->d_descs.p) + a,
+                                                   static_cast<const uint32_t*>(c->d_tiles.p) + a, (uint32_t)(b - a),
+                                                   tile_start[a], tiles, static_cast<uint8_t*>(c->d_sidecar.p),
+                                                   static_cast<uint32_t*>(c->d_hist.p) + a * 256);
+            CHK_CUDA(cudaGetLastError());
+            c->launches++;
+            CHK_CUDA(cudaMemcpyAsync(static_cast<uint8_t*>(c->h_hist.p) + a * 1024,
+                                     static_cast<const uint8_t*>(c->d_hist.p) + a * 1024, (b - a) * 1024,
+                                     cudaMemcpyDeviceToHost, s));
+        }
+        CHK_CUDA(cudaEventRecord(c->seg_events[g], s));
+        a = b;
     }
     CHK_CUDA(cudaEventRecord(c->ev[1], s));
-    CHK_CUDA(cudaMemcpyAsync(c->h_hist.p, c->d_hist.p, W * 1024, cudaMemcpyDeviceToHost, s));
-    CHK_CUDA(cudaStreamSynchronize(s));
 
-    // ---- tables on the host
+    // ---- tables on the host: worker threads take tensors in order and wait for the
+    // segment a tensor belongs to; the calling thread releases segments as their copies land.
     const auto t_tab = std::chrono::steady_clock::now();
-    EncEntry* h_enc = static_cast<EncEntry*>(c->h_enc.p);
-    uint32_t* h_freq = reinterpret_cast<uint32_t*>(h_enc + T * 256);
-    uint32_t* h_cum = h_freq + T * 256;
+    uint16_t* h_nf16 = static_cast<uint16_t*>(c->h_enc.p);
     {
         std::vector<size_t> owners;
-        for (size_t i = 0; i < W; ++i)
-            if (c->work[i].owns) owners.push_back(i);
+        std::vector<uint32_t> owner_seg;
+        for (size_t i = 0, g = 0; i < W; ++i) {
+            while (i >= seg_end[g]) ++g;
+            if (c->work[i].owns) {
+                owners.push_back(i);
+                owner_seg.push_back((uint32_t)g);
+            }
+        }
+        std::atomic<uint32_t> ready{0};  // segments whose histograms are on the host
+        std::atomic<bool> failed{false};
         const uint32_t* hist_all = static_cast<const uint32_t*>(c->h_hist.p);
-        parallel_for(owners.size(), c->host_threads, [&](size_t k) {
+        auto work_fn = [&](size_t k) {
+            while (ready.load(std::memory_order_acquire) <= owner_seg[k]) {
+                if (failed.load()) return;
+                std::this_thread::yield();
+            }
             const size_t i = owners[k];
             const WorkItem& w = c->work[i];
             uint32_t h[256];
@@ -417,16 +453,32 @@ static void compress(Context* c, bool host_images) {
             const bool full = is_cluster_anchor(c, w);
             FreqTable& ft = c->tables[w.table];
             normalize_histogram(h, full, full && c->repair_tables, ft);
-            build_enc_entries(ft, h_enc + (size_t)w.table * 256);
-            std::memcpy(h_freq + (size_t)w.table * 256, ft.norm_freq, 1024);
-            std::memcpy(h_cum + (size_t)w.table * 257, ft.cum_freq, 1028);
+            uint16_t* o = h_nf16 + (size_t)w.table * 256;
+            for (int sy = 0; sy < 256; ++sy) o[sy] = (uint16_t)ft.norm_freq[sy];
+        };
+        std::thread releaser([&] {
+            cudaSetDevice(c->device);
+            for (size_t g = 0; g < n_seg; ++g) {
+                if (cudaEventSynchronize(c->seg_events[g]) != cudaSuccess) {
+                    failed.store(true);
+                    return;
+                }
+                ready.store((uint32_t)g + 1, std::memory_order_release);
+            }
         });
+        parallel_for(owners.size(), c->host_threads, work_fn);
+        releaser.join();
+        if (failed.load()) CHK_CUDA(cudaStreamSynchronize(s));  // surfaces the device error
     }
     c->timing["table_ms"] = wall_ms(t_tab);
 
-    CHK_CUDA(cudaMemcpyAsync(c->d_enc.p, h_enc, T * 256 * sizeof(EncEntry), cudaMemcpyHostToDevice, s));
-    CHK_CUDA(cudaMemcpyAsync(c->d_freq.p, h_freq, T * 256 * 4, cudaMemcpyHostToDevice, s));
-    CHK_CUDA(cudaMemcpyAsync(c->d_cum.p, h_cum, T * 257 * 4, cudaMemcpyHostToDevice, s));
+    // frequencies up (512 B per table); prefix sums and encode entries are derived on the device
+    CHK_CUDA(cudaMemcpyAsync(c->d_nf16.p, h_nf16, T * 512, cudaMemcpyHostToDevice, s));
+    build_tables_kernel<<<(uint32_t)(T < 4096 ? T : 4096), 256, 0, s>>>(
+        static_cast<const uint16_t*>(c->d_nf16.p), static_cast<EncEntry*>(c->d_enc.p),
+        static_cast<uint32_t*>(c->d_freq.p), static_cast<uint32_t*>(c->d_cum.p), (uint32_t)T);
+    CHK_CUDA(cudaGetLastError());
+    c->launches++;
     CHK_CUDA(cudaEventRecord(c->ev[2], s));
 
     // ---- stage 2: encode
@@ -960,7 +1012,7 @@ int chk_context_destroy(chk_context* c) {
     cudaSetDevice(c->device);
     if (c->stream) cudaStreamSynchronize(c->stream);
     DevBuf* bufs[] = {&c->d_descs, &c->d_tiles, &c->d_hist, &c->d_sidecar, &c->d_scratch, &c->d_hdrs,
-                      &c->d_lsrc, &c->d_order, &c->d_ticket, &c->d_loff, &c->d_psize, &c->d_poff, &c->d_payload, &c->d_enc,
+                      &c->d_lsrc, &c->d_order, &c->d_ticket, &c->d_nf16, &c->d_loff, &c->d_psize, &c->d_poff, &c->d_payload, &c->d_enc,
                       &c->d_freq, &c->d_cum, &c->d_status, &c->d_stats_desc, &c->d_stats_out};
     for (DevBuf* b : bufs)
         if (b->p) cudaFreeAsync(b->p, c->stream);
@@ -970,6 +1022,8 @@ int chk_context_destroy(chk_context* c) {
     for (PinBuf* b : pins)
         if (b->p) cudaFreeHost(b->p);
     for (auto& e : c->ev)
+        if (e) cudaEventDestroy(e);
+    for (auto& e : c->seg_events)
         if (e) cudaEventDestroy(e);
     if (c->pool) cudaMemPoolDestroy(c->pool);
     if (c->side_stream) cudaStreamDestroy(c->side_stream);

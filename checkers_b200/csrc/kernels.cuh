@@ -189,8 +189,8 @@ __device__ __forceinline__ void split_one_byte(const TensorDesc& d, unsigned lon
 // one tensor and merges its bins into global memory once per tensor.
 __global__ void __launch_bounds__(256) split_hist_kernel(const TensorDesc* __restrict__ descs,
                                                          const uint32_t* __restrict__ tile_start,
-                                                         uint32_t n_tensors, uint32_t total_tiles,
-                                                         uint8_t* __restrict__ sidecar,
+                                                         uint32_t n_tensors, uint32_t tile_base,
+                                                         uint32_t total_tiles, uint8_t* __restrict__ sidecar,
                                                          uint32_t* __restrict__ hist) {
     CHK_SHARED uint32_t wh[8][256];
     CHK_SHARED uint32_t hot[8][kHotWords];
@@ -199,8 +199,10 @@ __global__ void __launch_bounds__(256) split_hist_kernel(const TensorDesc* __res
     for (uint32_t i = tid; i < 8 * kHotWords; i += 256) (&hot[0][0])[i] = 0;
     __syncthreads();
 
-    const uint32_t t0 = (uint32_t)((unsigned long long)total_tiles * blockIdx.x / gridDim.x);
-    const uint32_t t1 = (uint32_t)((unsigned long long)total_tiles * (blockIdx.x + 1) / gridDim.x);
+    // `descs`, `tile_start` and `hist` point at the first tensor of this launch's range;
+    // tile_start holds running totals over the whole batch, tile_base = tile_start[0]
+    const uint32_t t0 = tile_base + (uint32_t)((unsigned long long)total_tiles * blockIdx.x / gridDim.x);
+    const uint32_t t1 = tile_base + (uint32_t)((unsigned long long)total_tiles * (blockIdx.x + 1) / gridDim.x);
     if (t0 >= t1) return;
 
     // tensor holding tile t0: last index with tile_start[i] <= t0

@@ -28,6 +28,53 @@ __device__ __forceinline__ constexpr uint32_t chain_byte(int k) {
     return NV == 4 ? (uint32_t)k : (k == 0 ? (uint32_t)B0 : 3u);
 }
 
+// Device copy of every table of a batch from its 256 normalised frequencies
+// (16-bit, one block of 256 threads per table): the prefix sums, and the encode
+// entry of each symbol exactly as tables.hpp:build_enc_entries computes it.
+__global__ void __launch_bounds__(256) build_tables_kernel(const uint16_t* __restrict__ norm_freq16,
+                                                           EncEntry* __restrict__ enc, uint32_t* __restrict__ freq,
+                                                           uint32_t* __restrict__ cum, uint32_t n_tables) {
+    CHK_SHARED uint32_t warp_tot[8];
+    const uint32_t s = threadIdx.x, lane = s & 31, warp = s >> 5;
+    for (uint32_t t = blockIdx.x; t < n_tables; t += gridDim.x) {
+        const uint32_t f = norm_freq16[(size_t)t * 256 + s];
+        uint32_t v = f;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t n = __shfl_up_sync(0xffffffffu, v, o);
+            if (lane >= (uint32_t)o) v += n;
+        }
+        if (lane == 31) warp_tot[warp] = v;
+        __syncthreads();
+        uint32_t before = 0;
+#pragma unroll
+        for (int w = 0; w < 8; ++w)
+            if ((uint32_t)w < warp) before += warp_tot[w];
+        const uint32_t c = before + v - f;  // exclusive prefix
+        freq[(size_t)t * 256 + s] = f;
+        cum[(size_t)t * 257 + s] = c;
+        if (s == 255) cum[(size_t)t * 257 + 256] = c + f;
+        EncEntry e;
+        e.rcp = e.freq_shift = e.bias = e.cmpl = 0;
+        if (f == 1) {
+            e.rcp = 0xFFFFFFFFu;
+            e.freq_shift = 1u;
+            e.bias = c + (kM - 1);
+            e.cmpl = kM - 1;
+        } else if (f > 1) {
+            uint32_t sh = 0;
+            while ((1u << sh) < f) ++sh;
+            const unsigned long long num = 1ull << (31 + sh);
+            e.rcp = (uint32_t)((num + f - 1) / f);
+            e.freq_shift = f | ((sh - 1) << 16);
+            e.bias = c;
+            e.cmpl = kM - f;
+        }
+        enc[(size_t)t * 256 + s] = e;
+        __syncthreads();
+    }
+}
+
 // Shared memory of one encode team: table (256 x 16 B) + a 32-byte output ring
 // per chain.  Ring words are interleaved across the team (word w of thread j's
 // chain k sits at ring[(k*8 + w) * 64 + j]), so a warp never has a bank conflict

@@ -70,7 +70,7 @@ void emu_split_hist(size_t n, const uint8_t* const* srcs, const uint64_t* n_byte
     std::memset(hist_out, 0, n * 1024);
     const uint32_t total = b.tile_start[n];
     emu::launch(grid, 256, 0, [&] {
-        split_hist_kernel(b.descs.data(), b.tile_start.data(), (uint32_t)n, total, sidecar_out, hist_out);
+        split_hist_kernel(b.descs.data(), b.tile_start.data(), (uint32_t)n, 0u, total, sidecar_out, hist_out);
     });
 }
 
@@ -155,6 +155,20 @@ void emu_stats(size_t n, const void* const* ptrs, const uint64_t* n_elem, const 
     for (size_t i = 0; i < n; ++i) d[i] = StatsDesc{ptrs[i], n_elem[i], dtype[i], bins};
     std::memset(outs, 0, n * sizeof(StatsOut));
     emu::launch(grid, 256, 0, [&] { tensor_stats_kernel(d.data(), (StatsOut*)outs, (uint32_t)n); });
+}
+
+// enc_out: n_tables*256 entries of 4 words; freq_out n*256; cum_out n*257
+void emu_build_tables(size_t n_tables, const uint16_t* nf16, uint32_t* enc_out, uint32_t* freq_out, uint32_t* cum_out,
+                      uint32_t grid) {
+    emu::launch(grid, 256, 0, [&] { build_tables_kernel(nf16, (EncEntry*)enc_out, freq_out, cum_out, (uint32_t)n_tables); });
+}
+
+// the host routine the device kernel must agree with
+void emu_host_enc_entries(const uint32_t* nf, const uint32_t* cf, uint32_t* enc_out) {
+    FreqTable ft;
+    std::memcpy(ft.norm_freq, nf, 1024);
+    std::memcpy(ft.cum_freq, cf, 1028);
+    build_enc_entries(ft, (EncEntry*)enc_out);
 }
 
 uint32_t emu_stats_out_bytes() { return (uint32_t)sizeof(StatsOut); }

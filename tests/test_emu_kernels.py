@@ -130,3 +130,29 @@ def test_stats_kernel(emu, oracle):
             assert np.array_equal(res[i][1].view(np.uint32), mom.view(np.uint32)), i
             assert np.array_equal(res[i][2].view(np.uint32), mm.view(np.uint32)), i
             assert res[i][3][4] == np.float32(mm[1] - mm[0])
+
+
+def test_device_table_builder(emu, oracle):
+    """build_tables_kernel must give the prefix sums and encode entries the host routine gives."""
+    import ctypes as C
+    rng = np.random.default_rng(8)
+    tabs = []
+    for i in range(9):
+        h = np.zeros(256, np.uint32)
+        k = [1, 2, 256, 20, 100, 256, 7, 3, 50][i]
+        h[rng.choice(256, k, replace=False)] = rng.integers(1, 10 ** (1 + i % 6), k)
+        tabs.append(oracle.normalize(h, full=(i % 3 == 0)))
+    nf = np.stack([t[0] for t in tabs])
+    cf = np.stack([t[1] for t in tabs])
+    nf16 = nf.astype(np.uint16)
+    n = len(tabs)
+    enc = np.zeros((n, 256, 4), np.uint32)
+    freq, cum = np.zeros((n, 256), np.uint32), np.zeros((n, 257), np.uint32)
+    u32p = C.POINTER(C.c_uint32)
+    emu.lib.emu_build_tables(C.c_size_t(n), nf16.ctypes.data_as(C.POINTER(C.c_uint16)), enc.ctypes.data_as(u32p),
+                             freq.ctypes.data_as(u32p), cum.ctypes.data_as(u32p), C.c_uint32(3))
+    assert np.array_equal(freq, nf) and np.array_equal(cum, cf)
+    for i in range(n):
+        want = np.zeros((256, 4), np.uint32)
+        emu.lib.emu_host_enc_entries(nf[i].ctypes.data_as(u32p), cf[i].ctypes.data_as(u32p), want.ctypes.data_as(u32p))
+        assert np.array_equal(enc[i], want), i
