@@ -245,43 +245,40 @@ __global__ void __launch_bounds__(256) split_hist_kernel(const TensorDesc* __res
 
         if ((d.flags & kFlagAligned) && (d.es == 4 || d.es == 2) && d.spe * 2 == d.es) {
             const uint32_t nvec = nb >> 4;
+            // four independent 16-byte loads per thread are in flight before any of them is used
             const uint32_t iters = (nvec + 255) >> 8;
-            for (uint32_t it = 0; it < iters; ++it) {
-                const uint32_t v = it * 256 + tid;
-                const bool ok = v < nvec;
-                uint4 q = make_uint4(0, 0, 0, 0);
-                if (ok) q = ld_global_v4(d.src + base + (size_t)v * 16);
-                const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-                if (d.es == 4) {
-                    if (ok) {
-                        uint2 s;
-                        s.x = __byte_perm(w[0], w[1], 0x5410);
-                        s.y = __byte_perm(w[2], w[3], 0x5410);
-                        *reinterpret_cast<uint2*>(sidecar + d.sidecar_off + ((base + (size_t)v * 16) >> 1)) = s;
+            for (uint32_t it0 = 0; it0 < iters; it0 += 4) {
+                uint4 q[4];
+                bool ok[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const uint32_t v = (it0 + u) * 256 + tid;
+                    ok[u] = v < nvec;
+                    q[u] = make_uint4(0, 0, 0, 0);
+                    if (ok[u]) q[u] = ld_global_v4(d.src + base + (size_t)v * 16);
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    if (!ok[u]) continue;
+                    const uint32_t v = (it0 + u) * 256 + tid;
+                    const uint32_t w[4] = {q[u].x, q[u].y, q[u].z, q[u].w};
+                    uint2 s2;
+                    if (d.es == 4) {
+                        s2.x = __byte_perm(w[0], w[1], 0x5410);
+                        s2.y = __byte_perm(w[2], w[3], 0x5410);
+                    } else {
+                        s2.x = __byte_perm(w[0], w[1], 0x6420);
+                        s2.y = __byte_perm(w[2], w[3], 0x6420);
                     }
+                    *reinterpret_cast<uint2*>(sidecar + d.sidecar_off + ((base + (size_t)v * 16) >> 1)) = s2;
                     if (count) {
 #pragma unroll
                         for (int k = 0; k < 4; ++k) {
-                            if (ok) {
+                            if (d.es == 4)
                                 bin_add(mine, (w[k] >> 16) & 0xFF);
-                                bin_add_hot(mine_hot, w[k] >> 24);
-                            }
-                        }
-                    }
-                } else {
-                    if (ok) {
-                        uint2 s;
-                        s.x = __byte_perm(w[0], w[1], 0x6420);
-                        s.y = __byte_perm(w[2], w[3], 0x6420);
-                        *reinterpret_cast<uint2*>(sidecar + d.sidecar_off + ((base + (size_t)v * 16) >> 1)) = s;
-                    }
-                    if (count) {
-#pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            if (ok) {
+                            else
                                 bin_add_hot(mine_hot, (w[k] >> 8) & 0xFF);
-                                bin_add_hot(mine_hot, w[k] >> 24);
-                            }
+                            bin_add_hot(mine_hot, w[k] >> 24);
                         }
                     }
                 }
