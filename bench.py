@@ -34,6 +34,9 @@ sys.path.insert(0, os.path.join(ROOT, "tests"))
 
 LLAMA3_8B = dict(hidden=4096, layers=32, inter=14336, q_heads=32, kv_heads=8, head_dim=128, vocab=128256)
 PARAMS_8B = 8030261248
+# measured once under ncu (see profiles/): DRAM read+write bytes per byte of tensor processed
+NCU_DRAM_BYTES_PER_TENSOR_BYTE = {"rans_encode_kernel": (1.192e9 + 0.564e9) / 939.5e6,
+                                  "rans_decode_kernel": (0.962e9 + 0.900e9) / 939.5e6}
 
 
 def llama_params(cfg):
@@ -233,6 +236,9 @@ def main():
     tags = (chk.BF16, chk.F32, chk.F32, chk.F32)
 
     ctx = chk.Context(device=local_rank, rank=rank, local_rank=local_rank)
+    # table normalisation runs on host threads: share the cores between the ranks of this node
+    local_world = int(os.environ.get("LOCAL_WORLD_SIZE", str(world)))
+    ctx.set_option("host_threads", max(2, (os.cpu_count() or 2) // max(local_world, 1)))
     for kv in args.opt:
         k, v = kv.split("=")
         ctx.set_option(k, int(v))
@@ -364,7 +370,10 @@ def main():
     dom_ms, dom_bytes = kernels[dom]
     achieved = dom_bytes / (dom_ms * 1e-3) / 1e9 if dom_ms > 0 else 0.0
     roofline = {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "peak_kind": peak_kind,
-                "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                "unit": "GB/s", "frac": achieved / peak,
+                # DRAM bytes of one launch: ncu dram__bytes_read+write on a 939.5 MB case (profiles/
+                # rans_kernels_llama3_shard.md), scaled by tensor bytes (traffic grows in proportion)
+                "traffic": shard_bytes * NCU_DRAM_BYTES_PER_TENSOR_BYTE[dom],
                 "per_kernel_ms": {k: v[0] for k, v in kernels.items()},
                 "per_kernel_algorithmic_gbs": {k: (v[1] / (v[0] * 1e-3) / 1e9 if v[0] > 0 else None)
                                                for k, v in kernels.items()},
