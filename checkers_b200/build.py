@@ -7,7 +7,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 LIB_DIR = os.path.join(PKG, "lib")
 LIB = os.path.join(LIB_DIR, "libcheckers_b200.so")
-SOURCES = ["engine.cu"]
+SOURCES = ["engine.cu", "repair.cu"]
 HEADERS = ["kernels.cuh", "rans_kernels.cuh", "tables.hpp", "clusters.hpp",
            os.path.join("..", "..", "include", "checkers_b200.h")]
 

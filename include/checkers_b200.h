@@ -136,6 +136,31 @@ int chk_get_stream(chk_context* ctx, void** stream_out);
 /* Kernels launched by this context since creation. */
 int chk_kernel_launches(chk_context* ctx, uint64_t* count);
 
+/* ---- prefix-mask Re-Pair size estimator -----------------------------------
+ * The reference ships this as a stand-alone, single-threaded CPU tool
+ * (src/tensor_group_prefix_mask_repair.cpp).  These two calls are its compute
+ * core on the GPU; `python -m checkers_b200.repair <export_dir> [...]` is the
+ * command-line front end with the reference's arguments and report files.
+ * Token ids: masked word >> masked_bits for tensor words, 0x80000000 + r for
+ * the symbol introduced by rule r.  h_raw is HOST memory (the tool reads files):
+ * numel little-endian words of storage_bytes (2 or 4) bytes.
+ *
+ * chk_repair_build: build_masked_sequence + build_shared_grammar (:328-352,
+ *   :423-453) on the representative tensor.  Fills up to max_rules rules
+ *   (lhs, rhs ids and the pair count when it was chosen), the length of the
+ *   rewritten sequence, the largest pair count seen, and how many rounds had
+ *   several pairs at the maximum (resolved on the host in the reference's
+ *   hash-map order).
+ * chk_repair_apply: build_masked_sequence + apply_existing_grammar (:455-463)
+ *   on another tensor of the group; returns the rewritten length. */
+const char* chk_repair_last_error(void);
+int chk_repair_build(int device, const void* h_raw, uint64_t numel, uint32_t storage_bytes, uint32_t masked_bits,
+                     uint32_t max_rules, uint32_t* rule_lhs, uint32_t* rule_rhs, uint64_t* rule_freq,
+                     uint32_t* n_rules_out, uint64_t* tokens_out, uint64_t* max_pair_frequency_out,
+                     uint64_t* tie_rounds_out);
+int chk_repair_apply(int device, const void* h_raw, uint64_t numel, uint32_t storage_bytes, uint32_t masked_bits,
+                     const uint32_t* rule_lhs, const uint32_t* rule_rhs, uint32_t n_rules, uint64_t* tokens_out);
+
 /* ---- encode one tensor without allocating anything -----------------------
  * Has no counterpart in the reference (which allocates and frees device
  * buffers per tensor, src/ANSCompressor.cpp:348-388).

@@ -173,6 +173,24 @@ static inline unsigned __match_any_sync(unsigned, unsigned v) {
         return m;
     });
 }
+static inline unsigned __match_any_sync(unsigned, unsigned long long v) {
+    return (unsigned)emu::warp_collective(v, [](const unsigned long long* a, unsigned n, unsigned me) {
+        unsigned long long m = 0;
+        for (unsigned i = 0; i < n; ++i)
+            if (a[i] == a[me]) m |= 1ull << i;
+        return m;
+    });
+}
+static inline unsigned long long atomicCAS(unsigned long long* p, unsigned long long cmp, unsigned long long val) {
+    const unsigned long long old = *p;
+    if (old == cmp) *p = val;
+    return old;
+}
+static inline unsigned atomicMin(unsigned* p, unsigned v) {
+    const unsigned old = *p;
+    *p = std::min(old, v);
+    return old;
+}
 static inline unsigned __ballot_sync(unsigned, int p) {
     return (unsigned)emu::warp_collective(p ? 1 : 0, [](const unsigned long long* a, unsigned n, unsigned) {
         unsigned long long m = 0;

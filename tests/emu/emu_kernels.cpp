@@ -174,3 +174,69 @@ void emu_host_enc_entries(const uint32_t* nf, const uint32_t* cf, uint32_t* enc_
 uint32_t emu_stats_out_bytes() { return (uint32_t)sizeof(StatsOut); }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------- Re-Pair kernels
+#include "repair_kernels.cuh"
+
+extern "C" {
+
+// Pair table of a token sequence: returns the number of occupied slots; keys/counts/first get the
+// occupied entries (capacity n), best[0] the largest count, best[1] how many keys reach it.
+uint32_t emu_repair_count(const uint32_t* tokens, uint32_t n, unsigned long long* keys_out, uint32_t* counts_out,
+                          uint32_t* first_out, uint32_t* best, uint32_t grid) {
+    using namespace chkrp;
+    uint32_t cap = 1024;
+    while (cap < 2ull * n) cap <<= 1;
+    std::vector<unsigned long long> keys(cap, kEmptyKey), tie_keys(8);
+    std::vector<uint32_t> counts(cap, 0), first(cap, 0xFFFFFFFFu), tie_first(8);
+    uint32_t small[4] = {0, 0, 0, 0};
+    emu::launch(grid, 256, 0, [&] { pair_count_kernel(tokens, n, keys.data(), counts.data(), first.data(), cap - 1, small + 2); });
+    emu::launch(grid, 256, 0, [&] { pair_max_kernel(counts.data(), cap, small); });
+    emu::launch(grid, 256, 0, [&] {
+        pair_ties_kernel(keys.data(), counts.data(), first.data(), cap, small, tie_keys.data(), tie_first.data());
+    });
+    emu::launch(grid, 256, 0, [&] {
+        pair_dump_kernel(keys.data(), counts.data(), first.data(), cap, small + 3, keys_out, counts_out, first_out);
+    });
+    best[0] = small[0];
+    best[1] = small[1];
+    best[2] = small[2];
+    return small[3];
+}
+
+// One rule application; returns the new length.
+uint32_t emu_repair_apply(const uint32_t* tokens, uint32_t n, uint32_t lhs, uint32_t rhs, uint32_t new_sym,
+                          uint32_t* out, uint32_t grid) {
+    using namespace chkrp;
+    if (!n) return 0;
+    const uint32_t nb = (n + kScanBlock - 1) / kScanBlock;
+    std::vector<uint32_t> mark(n), run_start(n, 0xDEADBEEF), keep(n), pos(n), blocks(nb + 8);
+    auto scan = [&](int op, const uint32_t* in, uint32_t* o) {
+        if (op == 0) {
+            emu::launch(nb, 256, 0, [&] { scan_reduce_kernel<0>(in, n, blocks.data()); });
+            emu::launch(1, 256, 0, [&] { scan_blocks_kernel<0>(blocks.data(), nb); });
+            emu::launch(nb, 256, 0, [&] { scan_apply_kernel<0>(in, n, blocks.data(), o); });
+        } else {
+            emu::launch(nb, 256, 0, [&] { scan_reduce_kernel<1>(in, n, blocks.data()); });
+            emu::launch(1, 256, 0, [&] { scan_blocks_kernel<1>(blocks.data(), nb); });
+            emu::launch(nb, 256, 0, [&] { scan_apply_kernel<1>(in, n, blocks.data(), o); });
+        }
+    };
+    if (lhs == rhs) {
+        emu::launch(grid, 256, 0, [&] { run_mark_kernel(tokens, n, lhs, mark.data()); });
+        scan(1, mark.data(), run_start.data());
+    }
+    emu::launch(grid, 256, 0, [&] { rule_flags_kernel(tokens, n, lhs, rhs, run_start.data(), keep.data()); });
+    scan(0, keep.data(), pos.data());
+    emu::launch(grid, 256, 0, [&] {
+        rule_scatter_kernel(tokens, n, lhs, rhs, new_sym, run_start.data(), keep.data(), pos.data(), out);
+    });
+    return blocks[nb];
+}
+
+void emu_repair_mask(const uint8_t* raw, uint64_t n, uint32_t storage_bytes, uint32_t masked_bits, uint32_t* tokens,
+                     uint32_t grid) {
+    emu::launch(grid, 256, 0, [&] { chkrp::mask_words_kernel(raw, n, storage_bytes, masked_bits, tokens); });
+}
+
+}  // extern "C"
