@@ -67,19 +67,39 @@ struct PairKeyHash {  // same mixing as the reference's PairKeyHash (:363-371)
     }
 };
 
+// Device working set of one call.  One instance per device is kept for the life of the process and
+// only grows, so a run over many tensors does not pay an allocation per tensor.
 struct Workspace {
     uint32_t n_cap = 0, capacity = 0;
+    size_t raw_cap = 0;
+    bool ready = false;
     Dev tok_a, tok_b, mark, run_start, keep, pos, blocks, keys, counts, first, small, tie_keys, tie_first, dump_keys,
         dump_counts, dump_first, raw;
     cudaStream_t s = nullptr;
     ~Workspace() {
         if (s) cudaStreamDestroy(s);
     }
+    void release() {
+        Dev* all[] = {&tok_a, &tok_b, &mark, &run_start, &keep, &pos, &blocks, &keys, &counts, &first, &small, &tie_keys,
+                      &tie_first, &dump_keys, &dump_counts, &dump_first, &raw};
+        for (Dev* d : all) {
+            if (d->p) cudaFree(d->p);
+            d->p = nullptr;
+        }
+    }
     void init(uint32_t n, size_t raw_bytes) {
+        if (ready && n <= n_cap && raw_bytes <= raw_cap) {
+            capacity = 1024;  // table sized for THIS tensor: the hash mask must match what is cleared
+            while (capacity < 2ull * n) capacity <<= 1;
+            return;
+        }
+        release();
         n_cap = n;
+        raw_cap = raw_bytes;
         capacity = 1024;
         while (capacity < 2ull * n) capacity <<= 1;
-        RP_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+        if (!s) RP_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+        ready = true;
         const size_t nb = (size_t)(n ? n : 1) * 4;
         tok_a.alloc(nb);
         tok_b.alloc(nb);
@@ -141,6 +161,13 @@ static void upload_tokens(Workspace& w, const void* h_raw, uint64_t numel, uint3
     RP_CUDA(cudaGetLastError());
 }
 
+static Workspace& workspace_for(int device) {
+    static Workspace* per_device[64] = {};
+    if (device < 0 || device >= 64) throw Error{CHK_ERR_INVALID, "device ordinal out of range"};
+    if (!per_device[device]) per_device[device] = new Workspace();
+    return *per_device[device];
+}
+
 static void check_args(uint64_t numel, uint32_t storage_bytes, uint32_t masked_bits) {
     if (storage_bytes != 2 && storage_bytes != 4) throw Error{CHK_ERR_INVALID, "storage_bytes must be 2 or 4"};
     if (masked_bits > storage_bytes * 8) throw Error{CHK_ERR_INVALID, "masked_bits exceeds the word width"};
@@ -179,7 +206,7 @@ int chk_repair_build(int device, const void* h_raw, uint64_t numel, uint32_t sto
     if (!n_rules_out || !tokens_out) throw Error{CHK_ERR_INVALID, "NULL output"};
     check_args(numel, storage_bytes, masked_bits);
     RP_CUDA(cudaSetDevice(device));
-    Workspace w;
+    Workspace& w = workspace_for(device);
     w.init((uint32_t)numel, numel * storage_bytes);
     upload_tokens(w, h_raw, numel, storage_bytes, masked_bits);
     uint32_t* cur = w.tok_a.as<uint32_t>();
@@ -276,7 +303,7 @@ int chk_repair_apply(int device, const void* h_raw, uint64_t numel, uint32_t sto
     if (n_rules && (!rule_lhs || !rule_rhs)) throw Error{CHK_ERR_INVALID, "NULL rules"};
     check_args(numel, storage_bytes, masked_bits);
     RP_CUDA(cudaSetDevice(device));
-    Workspace w;
+    Workspace& w = workspace_for(device);
     w.init((uint32_t)numel, numel * storage_bytes);
     upload_tokens(w, h_raw, numel, storage_bytes, masked_bits);
     uint32_t* cur = w.tok_a.as<uint32_t>();
