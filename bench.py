@@ -202,6 +202,9 @@ def main():
     ap.add_argument("--limit-elems", type=int, default=0, help="use only this many parameters of the shard (tests)")
     ap.add_argument("--e2e-elems", type=int, default=256 << 20, help="parameters in the host-buffer end-to-end leg")
     ap.add_argument("--e2e-steps", type=int, default=2)
+    ap.add_argument("--e2e-workers", type=int, default=4, help="host threads driving chunks of the pipeline")
+    ap.add_argument("--e2e-chunk-bytes", type=int, default=256 << 20,
+                    help="tensor bytes per chunk of the host-buffer pipeline")
     ap.add_argument("--cpu-sample-elems", type=int, default=32 << 20, help="parameters in the timed CPU sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--seed", type=int, default=0)
@@ -313,28 +316,25 @@ def main():
     h_out = [torch.empty(e_elems, dtype=b.dtype).pin_memory() for b in bufs]
     for h, b in zip(h_in, bufs):
         h.copy_(b[:e_elems])
-    d_in = [torch.empty(e_elems, dtype=b.dtype, device=device) for b in bufs]
-    ctx2 = chk.Context(device=local_rank, rank=rank, local_rank=local_rank)
+    from checkers_b200.streaming import ChunkedHostPipeline, HostTensor
+    h_tensors, h_targets = [], []
     for name, off, n, _ in e_pieces:
-        for (prefix, _), d, tag in zip(STATE_KINDS, d_in, tags):
-            ctx2.register_pointer(prefix + name, d.data_ptr() + off * d.element_size(), n, tag)
+        for (prefix, _), hi, ho, tag in zip(STATE_KINDS, h_in, h_out, tags):
+            h_tensors.append(HostTensor(prefix + name, hi[off:off + n], tag))
+            h_targets.append(ho[off:off + n])
+    pipe = ChunkedHostPipeline(h_tensors, device=local_rank, rank=rank, chunk_bytes=args.e2e_chunk_bytes,
+                               workers=args.e2e_workers)
+    for ch in pipe.chunks:
+        ch.ctx.set_option("host_threads", max(2, (os.cpu_count() or 2) // max(args.e2e_workers * local_world, 1)))
     e_bytes = sum(h.numel() * h.element_size() for h in h_in)
     img_bytes = 0
 
     def e2e_step():
         nonlocal img_bytes
-        for d, h in zip(d_in, h_in):
-            d.copy_(h, non_blocking=True)
-        torch.cuda.synchronize()
-        ctx2.compress(host_images=True)                      # D2H of the three file images inside
-        imgs = [ctx2.image(k) for k in range(3)]
-        img_bytes = sum(int(i.size) for i in imgs)
-        for d in d_in:
-            d.zero_()
-        torch.cuda.synchronize()
-        ctx2.decompress_images(*imgs)                        # H2D of the images inside
-        for h, d in zip(h_out, d_in):
-            h.copy_(d, non_blocking=True)
+        pipe.compress()              # H2D of every chunk, kernels, D2H of each chunk's three file images
+        s = pipe.summary()
+        img_bytes = s["states_bytes"] + s["mantissa_bytes"] + s["dict_bytes"]
+        pipe.restore(h_targets)      # H2D of the images, decode, D2H of the restored tensors
         torch.cuda.synchronize()
 
     e2e_step()
@@ -421,7 +421,8 @@ def main():
                 "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": int(e_bytes + img_bytes),
                         "d2h_bytes_per_step": int(img_bytes + e_bytes), "steps": args.e2e_steps,
                         "sample": f"{e_bytes / 2**30:.2f} GiB of the shard per GPU from pinned host buffers: "
-                                  "H2D, compress, D2H of the 3 file images, H2D of the images, restore, D2H"},
+                                  f"in {len(pipe.chunks)} chunks with copies and kernels overlapped: H2D, compress, D2H of "
+                                  "the file images; then H2D of the images, restore, D2H"},
                 "gpu_launches": int(launches), "clocks": clocks}
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -17,6 +17,7 @@
 
 #include <atomic>
 #include <chrono>
+#include <condition_variable>
 #include <cstdio>
 #include <cstring>
 #include <filesystem>
@@ -125,7 +126,7 @@ struct Context {
     std::vector<cudaEvent_t> seg_events;
     int sm_count = 0;
     // pinned host staging
-    PinBuf h_hist, h_hdrs, h_poff, h_descs, h_status, h_enc, h_stats, h_order;
+    PinBuf h_hist, h_hdrs, h_poff, h_descs, h_status, h_enc, h_stats, h_order, h_tiles;
     PinBuf img[3];  // states, mantissa, tables
 
     // result of the last compression
@@ -160,7 +161,8 @@ static void pin_ensure(PinBuf& b, size_t bytes) {
     b.p = nullptr;
     b.cap = 0;
     const size_t want = bytes + bytes / 16;
-    CHK_CUDA(cudaHostAlloc(&b.p, want, cudaHostAllocDefault));
+    // mapped: the control kernels below read and write this memory directly
+    CHK_CUDA(cudaHostAlloc(&b.p, want, cudaHostAllocMapped | cudaHostAllocPortable));
     b.cap = want;
 }
 
@@ -173,11 +175,44 @@ static double wall_ms(std::chrono::steady_clock::time_point t0) {
     return std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
 }
 
+// Control data (descriptors, histograms, offsets, status words) moves between pinned host
+// memory and the device through these kernels, not through the copy engines.  A copy engine
+// serves transfers in submission order across all streams, so a few KB of control data would
+// wait behind every bulk transfer that a pipelined caller (several contexts, chunked
+// host-resident state) has queued; a kernel that loads or stores the pinned pages directly
+// does not queue there.
+__global__ void control_copy_kernel(uint32_t* __restrict__ dst, const uint32_t* __restrict__ src, size_t n_words) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_words; i += (size_t)gridDim.x * blockDim.x)
+        dst[i] = src[i];
+}
+__global__ void control_fill_kernel(uint32_t* __restrict__ dst, size_t n_words) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_words; i += (size_t)gridDim.x * blockDim.x)
+        dst[i] = 0u;
+}
+static uint32_t control_grid(size_t n_words) {
+    const size_t blocks = (n_words + 255) / 256;
+    return (uint32_t)(blocks < 592 ? (blocks ? blocks : 1) : 592);
+}
+// bytes must be a multiple of 4; one side is device memory, the other pinned (mapped) host memory
+static void control_copy(Context* c, void* dst, const void* src, size_t bytes, cudaStream_t s) {
+    if (bytes == 0) return;
+    control_copy_kernel<<<control_grid(bytes / 4), 256, 0, s>>>(static_cast<uint32_t*>(dst),
+                                                                static_cast<const uint32_t*>(src), bytes / 4);
+    CHK_CUDA(cudaGetLastError());
+    c->launches++;
+}
+static void control_zero(Context* c, void* dst, size_t bytes, cudaStream_t s) {
+    if (bytes == 0) return;
+    control_fill_kernel<<<control_grid(bytes / 4), 256, 0, s>>>(static_cast<uint32_t*>(dst), bytes / 4);
+    CHK_CUDA(cudaGetLastError());
+    c->launches++;
+}
+
 template <typename F>
 static void parallel_for(size_t n, int threads, F&& fn) {
     if (threads <= 0) threads = (int)std::thread::hardware_concurrency();
     if (threads < 1) threads = 1;
-    if ((size_t)threads > n) threads = (int)n;
+    if ((size_t)threads > (n + 15) / 16) threads = (int)((n + 15) / 16);  // work is handed out 16 items at a time
     if (threads <= 1) {
         for (size_t i = 0; i < n; ++i) fn(i);
         return;
@@ -283,8 +318,8 @@ static void upload_order(Context* c, size_t W, SizeFn&& size_of) {
     std::memcpy(c->h_order.p, order.data(), W * 4);
     dev_ensure(c, c->d_order, W * 4);
     dev_ensure(c, c->d_ticket, 256);
-    CHK_CUDA(cudaMemcpyAsync(c->d_order.p, c->h_order.p, W * 4, cudaMemcpyHostToDevice, c->stream));
-    CHK_CUDA(cudaMemsetAsync(c->d_ticket.p, 0, 256, c->stream));
+    control_copy(c, c->d_order.p, c->h_order.p, W * 4, c->stream);
+    control_zero(c, c->d_ticket.p, 256, c->stream);
 }
 
 // Grid of a persistent team kernel: as many teams as fit on the device at once.
@@ -308,7 +343,9 @@ static void compress(Context* c, bool host_images) {
     cudaStream_t s = c->stream;
 
     c->descs.assign(W, TensorDesc{});
-    std::vector<uint32_t> tile_start(W + 1, 0);
+    pin_ensure(c->h_tiles, (W + 1) * 4);
+    uint32_t* tile_start = static_cast<uint32_t*>(c->h_tiles.p);
+    tile_start[0] = 0;
     unsigned long long sidecar_total = 0, scratch_total = 0, bytes_total = 0;
     size_t n_sidecars = 0;
     for (size_t i = 0; i < W; ++i) {
@@ -380,9 +417,9 @@ static void compress(Context* c, bool host_images) {
 
     std::memcpy(c->h_descs.p, c->descs.data(), W * sizeof(TensorDesc));
     CHK_CUDA(cudaEventRecord(c->ev[0], s));
-    CHK_CUDA(cudaMemcpyAsync(c->d_descs.p, c->h_descs.p, W * sizeof(TensorDesc), cudaMemcpyHostToDevice, s));
-    CHK_CUDA(cudaMemcpyAsync(c->d_tiles.p, tile_start.data(), (W + 1) * 4, cudaMemcpyHostToDevice, s));
-    CHK_CUDA(cudaMemsetAsync(c->d_hist.p, 0, W * 1024, s));
+    control_copy(c, c->d_descs.p, c->h_descs.p, W * sizeof(TensorDesc), s);
+    control_copy(c, c->d_tiles.p, c->h_tiles.p, (W + 1) * 4, s);
+    control_zero(c, c->d_hist.p, W * 1024, s);
 
     // ---- stage 1: low bytes out, histograms.  The batch is cut into a few segments of
     // about equal bytes; each segment's histograms are copied back as soon as its launch
@@ -413,9 +450,8 @@ static void compress(Context* c, bool host_images) {
                                                    static_cast<uint32_t*>(c->d_hist.p) + a * 256);
             CHK_CUDA(cudaGetLastError());
             c->launches++;
-            CHK_CUDA(cudaMemcpyAsync(static_cast<uint8_t*>(c->h_hist.p) + a * 1024,
-                                     static_cast<const uint8_t*>(c->d_hist.p) + a * 1024, (b - a) * 1024,
-                                     cudaMemcpyDeviceToHost, s));
+            control_copy(c, static_cast<uint8_t*>(c->h_hist.p) + a * 1024,
+                         static_cast<const uint8_t*>(c->d_hist.p) + a * 1024, (b - a) * 1024, s);
         }
         CHK_CUDA(cudaEventRecord(c->seg_events[g], s));
         a = b;
@@ -438,12 +474,15 @@ static void compress(Context* c, bool host_images) {
         }
         std::atomic<uint32_t> ready{0};  // segments whose histograms are on the host
         std::atomic<bool> failed{false};
+        std::mutex mu;
+        std::condition_variable cv;
         const uint32_t* hist_all = static_cast<const uint32_t*>(c->h_hist.p);
         auto work_fn = [&](size_t k) {
-            while (ready.load(std::memory_order_acquire) <= owner_seg[k]) {
-                if (failed.load()) return;
-                std::this_thread::yield();
+            if (ready.load(std::memory_order_acquire) <= owner_seg[k]) {
+                std::unique_lock<std::mutex> lk(mu);
+                cv.wait(lk, [&] { return ready.load(std::memory_order_acquire) > owner_seg[k] || failed.load(); });
             }
+            if (failed.load()) return;
             const size_t i = owners[k];
             const WorkItem& w = c->work[i];
             uint32_t h[256];
@@ -459,11 +498,13 @@ static void compress(Context* c, bool host_images) {
         std::thread releaser([&] {
             cudaSetDevice(c->device);
             for (size_t g = 0; g < n_seg; ++g) {
-                if (cudaEventSynchronize(c->seg_events[g]) != cudaSuccess) {
-                    failed.store(true);
-                    return;
+                const bool ok = cudaEventSynchronize(c->seg_events[g]) == cudaSuccess;
+                {
+                    std::lock_guard<std::mutex> lk(mu);
+                    if (ok) ready.store((uint32_t)g + 1, std::memory_order_release); else failed.store(true);
                 }
-                ready.store((uint32_t)g + 1, std::memory_order_release);
+                cv.notify_all();
+                if (!ok) return;
             }
         });
         parallel_for(owners.size(), c->host_threads, work_fn);
@@ -473,7 +514,7 @@ static void compress(Context* c, bool host_images) {
     c->timing["table_ms"] = wall_ms(t_tab);
 
     // frequencies up (512 B per table); prefix sums and encode entries are derived on the device
-    CHK_CUDA(cudaMemcpyAsync(c->d_nf16.p, h_nf16, T * 512, cudaMemcpyHostToDevice, s));
+    control_copy(c, c->d_nf16.p, h_nf16, T * 512, s);
     build_tables_kernel<<<(uint32_t)(T < 4096 ? T : 4096), 256, 0, s>>>(
         static_cast<const uint16_t*>(c->d_nf16.p), static_cast<EncEntry*>(c->d_enc.p),
         static_cast<uint32_t*>(c->d_freq.p), static_cast<uint32_t*>(c->d_cum.p), (uint32_t)T);
@@ -543,10 +584,9 @@ static void compress(Context* c, bool host_images) {
         c->launches += 3;
     }
     CHK_CUDA(cudaEventRecord(c->ev[4], s));
-    CHK_CUDA(cudaMemcpyAsync(c->h_poff.p, c->d_poff.p, (W + 1) * 8, cudaMemcpyDeviceToHost, s));
-    CHK_CUDA(cudaMemcpyAsync(c->h_descs.p, c->d_descs.p, W * sizeof(TensorDesc), cudaMemcpyDeviceToHost, s));
-    if (host_images)
-        CHK_CUDA(cudaMemcpyAsync(c->h_hdrs.p, c->d_hdrs.p, W * 4096, cudaMemcpyDeviceToHost, s));
+    control_copy(c, c->h_poff.p, c->d_poff.p, (W + 1) * 8, s);
+    control_copy(c, c->h_descs.p, c->d_descs.p, W * sizeof(TensorDesc), s);
+    if (host_images) control_copy(c, c->h_hdrs.p, c->d_hdrs.p, W * 4096, s);
     CHK_CUDA(cudaStreamSynchronize(s));
 
     c->timing["split_hist_ms"] = ms_between(c->ev[0], c->ev[1]);
@@ -683,7 +723,7 @@ static void run_decode(Context* c, size_t W, const uint8_t* d_payload, const uin
     cudaStream_t s = c->stream;
     dev_ensure(c, c->d_status, W * 4 + 256);
     pin_ensure(c->h_status, W * 4 + 256);
-    CHK_CUDA(cudaMemsetAsync(c->d_status.p, 0, W * 4, s));
+    control_zero(c, c->d_status.p, W * 4, s);
     // integer tensors run four chains per thread and need the larger ring area
     bool any_int = false;
     const TensorDesc* hd = static_cast<const TensorDesc*>(c->h_descs.p);
@@ -702,9 +742,11 @@ static void run_decode(Context* c, size_t W, const uint8_t* d_payload, const uin
     CHK_CUDA(cudaGetLastError());
     c->launches++;
     CHK_CUDA(cudaEventRecord(c->ev[2], s));
-    CHK_CUDA(cudaMemcpyAsync(c->h_status.p, c->d_status.p, W * 4, cudaMemcpyDeviceToHost, s));
+    control_copy(c, c->h_status.p, c->d_status.p, W * 4, s);
+    CHK_CUDA(cudaEventRecord(c->ev[4], s));
     CHK_CUDA(cudaStreamSynchronize(s));
     c->timing["decode_ms"] = ms_between(c->ev[1], c->ev[2]);
+    c->timing["decode_tail_ms"] = ms_between(c->ev[2], c->ev[4]);
     const uint32_t* st = static_cast<const uint32_t*>(c->h_status.p);
     for (size_t i = 0; i < W; ++i)
         if (st[i])
@@ -747,7 +789,7 @@ static void decompress_resident(Context* c, void* const* dst) {
     pin_ensure(c->h_descs, W * sizeof(TensorDesc));
     std::memcpy(c->h_descs.p, run.data(), W * sizeof(TensorDesc));
     dev_ensure(c, c->d_descs, W * sizeof(TensorDesc));
-    CHK_CUDA(cudaMemcpyAsync(c->d_descs.p, c->h_descs.p, W * sizeof(TensorDesc), cudaMemcpyHostToDevice, c->stream));
+    control_copy(c, c->d_descs.p, c->h_descs.p, W * sizeof(TensorDesc), c->stream);
     run_decode(c, W, static_cast<const uint8_t*>(c->d_payload.p), static_cast<const uint8_t*>(c->d_sidecar.p),
                static_cast<const uint32_t*>(c->d_freq.p), static_cast<const uint32_t*>(c->d_cum.p),
                static_cast<const LaneHeader*>(c->d_hdrs.p), names);
@@ -852,10 +894,10 @@ static void decompress_images(Context* c, const uint8_t* st, size_t st_n, const 
     pin_ensure(c->h_descs, W * sizeof(TensorDesc));
     std::memcpy(c->h_descs.p, run.data(), W * sizeof(TensorDesc));
 
+    c->timing["parse_ms"] = wall_ms(t_total);
     CHK_CUDA(cudaEventRecord(c->ev[0], s));
-    CHK_CUDA(cudaMemcpyAsync(c->d_descs.p, c->h_descs.p, W * sizeof(TensorDesc), cudaMemcpyHostToDevice, s));
-    if (payload_total) CHK_CUDA(cudaMemcpyAsync(c->d_payload.p, st + st_data, payload_total, cudaMemcpyHostToDevice, s));
-    if (sidecar_total) CHK_CUDA(cudaMemcpyAsync(c->d_sidecar.p, mt + mt_data, sidecar_total, cudaMemcpyHostToDevice, s));
+    control_copy(c, c->d_descs.p, c->h_descs.p, W * sizeof(TensorDesc), s);
+    // index data first, so it does not queue behind this call's own bulk copies
     // lane headers: one strided copy per run of consecutive entries
     for (size_t k = 0; k < W;) {
         size_t j = k + 1;
@@ -871,11 +913,14 @@ static void decompress_images(Context* c, const uint8_t* st, size_t st_n, const 
         CHK_CUDA(cudaMemcpy2DAsync(c->d_cum.p, 1028, dc + kFileHeader + 1280, kDictEntry, 1028, n_dc,
                                    cudaMemcpyHostToDevice, s));
     }
+    if (payload_total) CHK_CUDA(cudaMemcpyAsync(c->d_payload.p, st + st_data, payload_total, cudaMemcpyHostToDevice, s));
+    if (sidecar_total) CHK_CUDA(cudaMemcpyAsync(c->d_sidecar.p, mt + mt_data, sidecar_total, cudaMemcpyHostToDevice, s));
     CHK_CUDA(cudaEventRecord(c->ev[3], s));
     run_decode(c, W, static_cast<const uint8_t*>(c->d_payload.p), static_cast<const uint8_t*>(c->d_sidecar.p),
                static_cast<const uint32_t*>(c->d_freq.p), static_cast<const uint32_t*>(c->d_cum.p),
                static_cast<const LaneHeader*>(c->d_hdrs.p), names);
     c->timing["h2d_ms"] = ms_between(c->ev[0], c->ev[3]);
+    c->timing["decode_wait_ms"] = ms_between(c->ev[3], c->ev[1]);
     c->timing["decompress_total_ms"] = wall_ms(t_total);
 }
 
@@ -1017,7 +1062,7 @@ int chk_context_destroy(chk_context* c) {
     for (DevBuf* b : bufs)
         if (b->p) cudaFreeAsync(b->p, c->stream);
     if (c->stream) cudaStreamSynchronize(c->stream);
-    PinBuf* pins[] = {&c->h_hist, &c->h_hdrs, &c->h_poff, &c->h_descs, &c->h_status, &c->h_enc, &c->h_stats, &c->h_order,
+    PinBuf* pins[] = {&c->h_hist, &c->h_hdrs, &c->h_poff, &c->h_descs, &c->h_status, &c->h_enc, &c->h_stats, &c->h_order, &c->h_tiles,
                       &c->img[0], &c->img[1], &c->img[2]};
     for (PinBuf* b : pins)
         if (b->p) cudaFreeHost(b->p);

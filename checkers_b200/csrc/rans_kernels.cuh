@@ -577,9 +577,10 @@ __device__ __forceinline__ uint32_t dec_step(DecChain& c, const uint32_t* dtab, 
     }
     const uint8_t* rp = ring_bytes + (c.rel & 63);
     const uint32_t top = __byte_perm(rp[0], rp[1], 0x0411);  // rp[0] to bits 31..24, rp[1] to bits 23..16
-    const uint32_t n = (x < kL ? 1u : 0u) + (x < (1u << 15) ? 1u : 0u);
-    c.x = __funnelshift_l(top, x, n * 8);
-    c.rel += n;
+    // bytes to pull in: 0 for x >= 2^23, 1 for x >= 2^15, else 2 (a valid state is never below 2^11)
+    const uint32_t t = (uint32_t)__clz((int)x) - 1u;
+    c.x = __funnelshift_l(top, x, t & 24u);
+    c.rel += t >> 3;
     return sym;
 }
 

@@ -253,6 +253,7 @@ static inline unsigned atomicMax(unsigned* p, unsigned v) {
 static inline unsigned __umulhi(unsigned a, unsigned b) { return (unsigned)(((unsigned long long)a * b) >> 32); }
 static inline int __popc(unsigned v) { return __builtin_popcount(v); }
 static inline int __ffs(unsigned v) { return __builtin_ffs((int)v); }
+static inline int __clz(int v) { return v ? __builtin_clz((unsigned)v) : 32; }
 static inline unsigned __funnelshift_r(unsigned lo, unsigned hi, unsigned sh) {
     unsigned long long v = ((unsigned long long)hi << 32) | lo;
     return (unsigned)(v >> (sh & 31));
