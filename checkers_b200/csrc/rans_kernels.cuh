@@ -500,52 +500,67 @@ __global__ void __launch_bounds__(256) compact_kernel(const TensorDesc* __restri
 //   two levels: slot -> symbol (1 byte), symbol -> freq[0:16) | cum[16:32)              5 KiB per tensor
 // The second costs one more dependent shared-memory load per symbol but lets about
 // twice as many teams be resident on an SM.
+constexpr uint32_t kRingWords = 20;
 template <int NV, bool TL>
 struct DecSmem {
     uint32_t dtab[TL ? 256 : kM];  // two levels: freq | cum<<16 per symbol
     uint8_t slot_sym[TL ? kM : 4];
     // 64-byte input ring per chain plus one word whose first byte mirrors ring byte 0
-    // (so byte p+1 is always at address p+1); 17 words apart keeps a warp conflict-free
-    uint32_t ring[NV * kTeam * 17];
+    // (so byte p+1 is always at address p+1); 80 bytes apart keeps 16-byte stores aligned
+    alignas(16) uint32_t ring[NV * kTeam * kRingWords];
     uint32_t cum[260];
 };
 // shared memory per team: [chains per thread: 2 = float tensors only, 4 = integers present][table shape]
 constexpr uint32_t kDecSmemBytes[2][2] = {{(uint32_t)sizeof(DecSmem<2, false>), (uint32_t)sizeof(DecSmem<2, true>)},
                                           {(uint32_t)sizeof(DecSmem<4, false>), (uint32_t)sizeof(DecSmem<4, true>)}};
 
+__device__ __forceinline__ void prefetch_l2(const void* p) {
+#ifndef CHK_CPU_EMULATION
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+#else
+    (void)p;
+#endif
+}
+
 struct DecChain {
     uint32_t x;
-    uint32_t rel;      // read position relative to blk0 * 16
+    uint32_t rel;      // read position relative to blk0 * 32
     uint32_t rel_end;  // where a valid stream ends
-    uint32_t loaded;   // 16-byte blocks requested so far
+    uint32_t loaded;   // 32-byte blocks requested so far
     uint32_t max_blocks;
     unsigned long long blk0;
-    uint4 pend;        // block requested at the previous check, not yet in the ring
+    uint4 pend0, pend1;  // block requested at the previous check, not yet in the ring
     bool has_pend;
 };
 
-// A lane reads its stream forward in aligned 16-byte blocks.  A block is
-// REQUESTED at one check point and only moved into the ring at the next one
-// (8 symbols later), so the load latency hides behind decode work; at least 16
-// unread bytes are in the ring whenever a group of 8 symbols starts.
-// A valid stream never needs bytes past its own end; a damaged one could run
-// ahead, so requests stop one block after the lane's last byte (the lane then
-// decodes garbage and fails its end check).
+// A lane reads its stream forward in aligned 32-byte blocks -- one DRAM sector each, so the
+// scattered requests of a warp's lanes are as few as they can be -- into a ring of two.
+// The next block is REQUESTED at the first check point after the read position has entered
+// the newer of the two blocks, and is only moved into the ring (over the older one) at the
+// following check point, 8 symbols later, so the load latency hides behind decode work.  A
+// group of 8 symbols consumes at most 16 bytes, so more than 16 unread bytes are in the
+// ring at the request and the new block is in place before they run out.
+// A valid stream never needs bytes past its own end; a damaged one could run ahead, so
+// requests stop one block after the lane's last byte (the lane then decodes stale bytes
+// and fails its end check).
 __device__ __forceinline__ void dec_request(DecChain& c, const uint8_t* __restrict__ payload) {
     if (c.loaded < c.max_blocks) {
-        c.pend = ld_global_v4(payload + (c.blk0 + c.loaded) * 16);
+        const uint8_t* src = payload + (c.blk0 + c.loaded) * 32;
+        c.pend0 = ld_global_v4(src);
+        c.pend1 = ld_global_v4(src + 16);
         c.has_pend = true;
+        // start the block after this one on its way from DRAM to L2: by the time it is
+        // requested (some 36 symbols from now) the request is a short L2 hit
+        if (c.loaded + 1 < c.max_blocks) prefetch_l2(src + 32);
     }
     ++c.loaded;
 }
 __device__ __forceinline__ void dec_commit(DecChain& c, uint32_t* ring_words) {
     if (c.has_pend) {
-        const uint32_t r = ((c.loaded - 1) & 3) * 4;
-        ring_words[r + 0] = c.pend.x;
-        ring_words[r + 1] = c.pend.y;
-        ring_words[r + 2] = c.pend.z;
-        ring_words[r + 3] = c.pend.w;
-        if (r == 0) ring_words[16] = c.pend.x;  // mirror of byte 0 behind byte 63
+        const uint32_t r = ((c.loaded - 1) & 1) * 8;
+        *reinterpret_cast<uint4*>(ring_words + r) = c.pend0;
+        *reinterpret_cast<uint4*>(ring_words + r + 4) = c.pend1;
+        if (r == 0) ring_words[16] = c.pend0.x;  // mirror of byte 0 behind byte 63
         c.has_pend = false;
     }
 }
@@ -597,7 +612,7 @@ __device__ __forceinline__ void decode_tensor(const TensorDesc& d, uint32_t ti,
     const unsigned long long B = d.n_bytes;
 
     // ---- slot table
-    const uint32_t* fq = freq_tables + (size_t)d.table_idx * 256;
+    (void)freq_tables;  // frequencies are differences of the prefix sums
     const uint32_t* cq = cum_tables + (size_t)d.table_idx * 257;
     for (uint32_t i = j; i < 257; i += kTeam) sm->cum[i] = cq[i];
     __syncthreads();
@@ -610,10 +625,10 @@ __device__ __forceinline__ void decode_tensor(const TensorDesc& d, uint32_t ti,
         if (TL)
             sm->slot_sym[slot] = (uint8_t)lo;
         else
-            sm->dtab[slot] = lo | ((fq[lo] - 1) << 8) | ((slot - sm->cum[lo]) << 20);
+            sm->dtab[slot] = lo | ((sm->cum[lo + 1] - sm->cum[lo] - 1) << 8) | ((slot - sm->cum[lo]) << 20);
     }
     if (TL)
-        for (uint32_t sy = j; sy < 256; sy += kTeam) sm->dtab[sy] = fq[sy] | (sm->cum[sy] << 16);
+        for (uint32_t sy = j; sy < 256; sy += kTeam) sm->dtab[sy] = (sm->cum[sy + 1] - sm->cum[sy]) | (sm->cum[sy] << 16);
 
     DecChain ch[NV];
     uint32_t* ringw[NV];
@@ -624,17 +639,17 @@ __device__ __forceinline__ void decode_tensor(const TensorDesc& d, uint32_t ti,
         const LaneHeader h = hdrs[(size_t)ti * kLanes + t];
         const unsigned long long p_abs = d.payload_off + h.buf_offset;
         ch[k].x = h.final_state;
-        ch[k].blk0 = p_abs >> 4;
-        ch[k].rel = (uint32_t)(p_abs & 15);
+        ch[k].blk0 = p_abs >> 5;
+        ch[k].rel = (uint32_t)(p_abs & 31);
         ch[k].rel_end = ch[k].rel + h.byte_count;
-        ch[k].max_blocks = ((ch[k].rel_end + 15) >> 4) + 1;
+        ch[k].max_blocks = ((ch[k].rel_end + 31) >> 5) + 1;
         ch[k].loaded = 0;
         ch[k].has_pend = false;
-        ringw[k] = sm->ring + (size_t)(k * kTeam + j) * 17;
+        ringw[k] = sm->ring + (size_t)(k * kTeam + j) * kRingWords;
         ringb[k] = reinterpret_cast<const uint8_t*>(ringw[k]);
-        if (B > t) {  // the lane has symbols: start with three blocks in the ring
+        if (B > t) {  // the lane has symbols: start with both blocks of the ring filled
 #pragma unroll
-            for (int i = 0; i < 3; ++i) {
+            for (int i = 0; i < 2; ++i) {
                 dec_request(ch[k], payload);
                 dec_commit(ch[k], ringw[k]);
             }
@@ -692,8 +707,8 @@ __device__ __forceinline__ void decode_tensor(const TensorDesc& d, uint32_t ti,
 #pragma unroll
         for (int k = 0; k < NV; ++k) {
             dec_commit(ch[k], ringw[k]);
-            // fewer than 33 unread bytes in the ring: request the next block now
-            if (ch[k].rel + 32 >= ch[k].loaded * 16) dec_request(ch[k], payload);
+            // reading from the newer block: the older one can be replaced
+            if (ch[k].rel >= (ch[k].loaded - 1) * 32) dec_request(ch[k], payload);
         }
         r += 8;
     }

@@ -113,6 +113,9 @@ class Emu:
         poff = np.ascontiguousarray(poff, np.uint64)
         raw = np.ascontiguousarray(raw, np.uint8)
         status = np.zeros(n, np.uint32)
+        padded = aligned(len(payload) + 128)  # the kernel reads whole 32-byte blocks, up to 63 bytes past the end
+        padded[:len(payload)] = np.frombuffer(payload, np.uint8) if not isinstance(payload, np.ndarray) else payload
+        payload = padded
         self.lib.emu_decode(C.c_size_t(n), ptrs, _p(nb, u64p), _p(es_a, u32p), _p(spe_a, u32p), _p(ti, u32p),
                             _p(nf, u32p), _p(cf, u32p), _p(hdrs, u32p), _p(payload), _p(poff, u64p), _p(raw),
                             _p(sidecar), C.c_uint32(check_zero), _p(status, u32p), C.c_uint32(grid),
