@@ -476,19 +476,31 @@ __global__ void __launch_bounds__(256) compact_kernel(const TensorDesc* __restri
         uint8_t* ov = o + head;
         const uint32_t mis = (uint32_t)(reinterpret_cast<uintptr_t>(sv) & 3);
         const uint32_t* sw = reinterpret_cast<const uint32_t*>(sv - mis);
-        for (uint32_t v = lane; v < nvec; v += 32) {
-            const uint32_t a0 = sw[v * 4 + 0], a1 = sw[v * 4 + 1], a2 = sw[v * 4 + 2], a3 = sw[v * 4 + 3];
-            uint4 r;
-            if (mis) {
-                const uint32_t a4 = sw[v * 4 + 4];
-                r.x = __funnelshift_r(a0, a1, mis * 8);
-                r.y = __funnelshift_r(a1, a2, mis * 8);
-                r.z = __funnelshift_r(a2, a3, mis * 8);
-                r.w = __funnelshift_r(a3, a4, mis * 8);
-            } else {
-                r = make_uint4(a0, a1, a2, a3);
+        // four 16-byte pieces per thread and step: all their loads are issued before the first
+        // is used, so a warp keeps 2 KiB in flight instead of 512 bytes
+        for (uint32_t v0 = lane; v0 < nvec; v0 += 128) {
+            uint32_t a[4][5];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const uint32_t v = v0 + 32 * u;
+                if (v < nvec) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) a[u][i] = sw[v * 4 + i];
+                    a[u][4] = mis ? sw[v * 4 + 4] : 0u;
+                }
             }
-            *reinterpret_cast<uint4*>(ov + (size_t)v * 16) = r;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const uint32_t v = v0 + 32 * u;
+                if (v < nvec) {
+                    uint4 r;
+                    r.x = __funnelshift_r(a[u][0], a[u][1], mis * 8);
+                    r.y = __funnelshift_r(a[u][1], a[u][2], mis * 8);
+                    r.z = __funnelshift_r(a[u][2], a[u][3], mis * 8);
+                    r.w = __funnelshift_r(a[u][3], a[u][4], mis * 8);
+                    *reinterpret_cast<uint4*>(ov + (size_t)v * 16) = r;
+                }
+            }
         }
         for (uint32_t i = head + (nvec << 4) + lane; i < cnt; i += 32) o[i] = s[i];
     }
