@@ -251,6 +251,7 @@ def main():
             es = b.element_size()
             ctx.register_pointer(prefix + name, b.data_ptr() + off * es, n, tag)
             dst.append(o.data_ptr() + off * es)
+    dst = np.asarray(dst, dtype=np.uint64)
     shard_bytes = sum(b.numel() * b.element_size() for b in bufs)
     torch.cuda.synchronize()
 

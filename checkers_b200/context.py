@@ -154,8 +154,9 @@ class Context:
         if dst_ptrs is None:
             check(lib.chk_decompress_resident(self._h, None))
         else:
-            arr = (C.c_void_p * len(dst_ptrs))(*[C.c_void_p(int(p)) for p in dst_ptrs])
-            check(lib.chk_decompress_resident(self._h, arr))
+            # one pointer per registered tensor (0 = skip); a uint64 numpy array is passed as is
+            arr = np.ascontiguousarray(dst_ptrs, dtype=np.uint64)
+            check(lib.chk_decompress_resident(self._h, arr.ctypes.data_as(C.POINTER(C.c_void_p))))
         return self.restored_count()
 
     def restored_count(self):

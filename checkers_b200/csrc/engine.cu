@@ -277,7 +277,7 @@ static void build_work(Context* c) {
         c->work.push_back(std::move(w));
     }
     // whether a table is built with the full alphabet: owner that is a cluster anchor
-    c->tables.assign(n_tables, FreqTable{});
+    c->tables.resize(n_tables);  // every entry is rewritten by normalize_histogram before it is read
 }
 
 static bool is_cluster_anchor(const Context* c, const WorkItem& w) {
@@ -416,14 +416,15 @@ static void compress(Context* c, bool host_images) {
     dev_ensure(c, c->d_nf16, T * 512);
 
     std::memcpy(c->h_descs.p, c->descs.data(), W * sizeof(TensorDesc));
+    c->timing["prepare_ms"] = wall_ms(t_total);
     CHK_CUDA(cudaEventRecord(c->ev[0], s));
     control_copy(c, c->d_descs.p, c->h_descs.p, W * sizeof(TensorDesc), s);
     control_copy(c, c->d_tiles.p, c->h_tiles.p, (W + 1) * 4, s);
     control_zero(c, c->d_hist.p, W * 1024, s);
 
-    // ---- stage 1: low bytes out, histograms.  The batch is cut into a few segments of
-    // about equal bytes; each segment's histograms are copied back as soon as its launch
-    // is done, so the host normalises segment g while the device still counts g+1.
+    // ---- stage 1: low bytes out, histograms.  The batch is cut into a few segments; each
+    // segment's histograms are copied back as soon as its launch is done, so the host
+    // normalises segment g while the device still counts g+1.
     const size_t n_seg = W >= 64 ? 8 : 1;
     std::vector<size_t> seg_end(n_seg, W);
     {
@@ -431,7 +432,9 @@ static void compress(Context* c, bool host_images) {
         size_t g = 0;
         for (size_t i = 0; i < W && g + 1 < n_seg; ++i) {
             acc += c->descs[i].n_bytes;
-            if (acc >= bytes_total * (g + 1) / n_seg) seg_end[g++] = i + 1;
+            // later segments are smaller, so little table work is left when the last one lands
+            static const unsigned kCut[8] = {16, 32, 47, 61, 74, 85, 94, 100};
+            if (acc * 100 >= bytes_total * kCut[g]) seg_end[g++] = i + 1;
         }
     }
     if (c->seg_events.size() < n_seg) {
@@ -592,6 +595,9 @@ static void compress(Context* c, bool host_images) {
     c->timing["split_hist_ms"] = ms_between(c->ev[0], c->ev[1]);
     c->timing["encode_ms"] = ms_between(c->ev[2], c->ev[3]);
     c->timing["compact_ms"] = ms_between(c->ev[3], c->ev[4]);
+    c->timing["table_gap_ms"] = ms_between(c->ev[1], c->ev[2]);  // device idle between counting and encoding
+    c->timing["device_span_ms"] = ms_between(c->ev[0], c->ev[4]);
+    c->timing["to_sync_ms"] = wall_ms(t_total);
     c->timing["compress_device_ms"] =
         c->timing["split_hist_ms"] + c->timing["encode_ms"] + c->timing["compact_ms"];
 
