@@ -35,8 +35,8 @@ sys.path.insert(0, os.path.join(ROOT, "tests"))
 LLAMA3_8B = dict(hidden=4096, layers=32, inter=14336, q_heads=32, kv_heads=8, head_dim=128, vocab=128256)
 PARAMS_8B = 8030261248
 # measured once under ncu (see profiles/): DRAM read+write bytes per byte of tensor processed
-NCU_DRAM_BYTES_PER_TENSOR_BYTE = {"rans_encode_kernel": (1.192e9 + 0.564e9) / 939.5e6,
-                                  "rans_decode_kernel": (0.962e9 + 0.900e9) / 939.5e6}
+NCU_DRAM_BYTES_PER_TENSOR_BYTE = {"rans_encode_kernel": (1.013e9 + 0.426e9) / 939.5e6,
+                                  "rans_decode_kernel": (0.901e9 + 0.901e9) / 939.5e6}
 
 
 def llama_params(cfg):
@@ -200,7 +200,9 @@ def main():
     ap.add_argument("--world-shards", type=int, default=8, help="flat-index shards of the model; one per rank")
     ap.add_argument("--chunk-elems", type=int, default=1 << 20, help="elements per registered tensor")
     ap.add_argument("--limit-elems", type=int, default=0, help="use only this many parameters of the shard (tests)")
-    ap.add_argument("--e2e-elems", type=int, default=256 << 20, help="parameters in the host-buffer end-to-end leg")
+    ap.add_argument("--e2e-elems", type=int, default=0,
+                    help="parameters in the host-buffer end-to-end leg (default: 256 Mi on one GPU, 128 Mi per GPU on several, "
+                         "to bound pinned host memory)")
     ap.add_argument("--e2e-steps", type=int, default=2)
     ap.add_argument("--e2e-workers", type=int, default=4, help="host threads driving chunks of the pipeline")
     ap.add_argument("--e2e-chunk-bytes", type=int, default=256 << 20,
@@ -311,7 +313,7 @@ def main():
     value = shard_bytes * world / (ms_per_step * 1e-3) / 1e9
 
     # ---- end-to-end leg through the C ABI with HOST buffers (pinned), copies timed
-    e_elems = min(args.e2e_elems, n_elems)
+    e_elems = min(args.e2e_elems or ((256 << 20) if world == 1 else (128 << 20)), n_elems)
     e_pieces = [(nm, off, min(n, e_elems - off), nrm) for nm, off, n, nrm in pieces if off < e_elems]
     h_in = [torch.empty(e_elems, dtype=b.dtype).pin_memory() for b in bufs]
     h_out = [torch.empty(e_elems, dtype=b.dtype).pin_memory() for b in bufs]
