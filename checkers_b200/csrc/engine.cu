@@ -5,14 +5,16 @@
 // How the reference's per-tensor, mutex-serialised loop
 // (ANSCompressor::compress_and_save_all, src/ANSCompressor.cpp:1014-1401 in the
 // Checkers tree: >= 8 stream syncs and 3 device-to-host copies per tensor) is
-// re-shaped here: all tensors of a rank go through each stage in ONE launch --
-//   split_hist_kernel   (low bytes -> final .mant data layout, histograms)
-//   one D2H of all histograms, table normalisation on host threads, one H2D
-//   rans_encode_kernel  (one CTA per tensor, 256 lanes)
+// re-shaped here: all tensors of a rank go through each stage together --
+//   split_hist_kernel   (low bytes -> final .mant data layout, histograms), in a few
+//                       segments whose histograms the host normalises while the next
+//                       segment is counted; build_tables_kernel derives the encode tables
+//   rans_encode_kernel  (persistent grid of 64-thread teams, one tensor at a time each,
+//                       largest tensors first) + zero_lane_kernel on a side stream
 //   lane_scan_kernel / tensor_scan_kernel / compact_kernel
 //                       (payload laid out exactly as the .ansc data section)
-// so the host synchronises twice per checkpoint instead of per tensor, and the
-// file images are filled by three large copies.
+// so the host synchronises a handful of times per checkpoint instead of per tensor, and
+// the file images are filled by three large copies.
 #include <cuda_runtime.h>
 
 #include <atomic>

@@ -86,73 +86,14 @@ struct EncEntry {
     unsigned char* p = chk_dyn_smem_
 #endif
 
-// ------------------------------------------------------------------ async tile copies
-// A tile is brought into shared memory with one bulk asynchronous copy issued
-// by a single thread and tracked by an mbarrier; every wait is bounded and
-// reports a timeout through a status word instead of spinning forever.
-__device__ __forceinline__ uint32_t smem_addr(const void* p) {
-#ifdef CHK_CPU_EMULATION
-    return 0;
-#else
-    return (uint32_t)__cvta_generic_to_shared(p);
-#endif
-}
-
-__device__ __forceinline__ void tile_barrier_init(unsigned long long* bar) {
-#ifndef CHK_CPU_EMULATION
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(bar)) : "memory");
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-#else
-    *bar = 0;
-#endif
-}
-
-// Issued by ONE thread: announce `bytes` and start the copy (16-byte aligned, size % 16 == 0).
-__device__ __forceinline__ void tile_copy_async(void* sdst, const void* gsrc, uint32_t bytes,
-                                                unsigned long long* bar) {
-#ifndef CHK_CPU_EMULATION
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes)
-                 : "memory");
-    asm volatile(
-        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-            smem_addr(sdst)),
-        "l"(gsrc), "r"(bytes), "r"(smem_addr(bar))
-        : "memory");
-#else
-    const unsigned char* s = (const unsigned char*)gsrc;
-    unsigned char* d = (unsigned char*)sdst;
-    for (uint32_t i = 0; i < bytes; ++i) d[i] = s[i];
-    (void)bar;
-#endif
-}
-
-// All threads: wait for the phase with the given parity.  Returns false on timeout.
-__device__ __forceinline__ bool tile_barrier_wait(unsigned long long* bar, uint32_t parity) {
-#ifndef CHK_CPU_EMULATION
-    const uint32_t a = smem_addr(bar);
-    for (uint32_t spin = 0; spin < (1u << 22); ++spin) {
-        uint32_t ok;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(ok)
-            : "r"(a), "r"(parity)
-            : "memory");
-        if (ok) return true;
-    }
-    return false;
-#else
-    (void)bar;
-    (void)parity;
-    return true;
-#endif
-}
-
 __device__ __forceinline__ uint4 ld_global_v4(const void* p) { return *reinterpret_cast<const uint4*>(p); }
 
 // ------------------------------------------------------------------ split + histogram
-constexpr uint32_t kSplitTileBytes = 32768;
+#ifndef CHK_SPLIT_TILE
+#define CHK_SPLIT_TILE 32768
+#endif
+constexpr uint32_t kSplitTileBytes = CHK_SPLIT_TILE;
+constexpr int kSplitLoads = kSplitTileBytes / (256 * 16);  // 16-byte loads per thread and tile
 
 // Count one byte value in this warp's private bins.
 __device__ __forceinline__ void bin_add(uint32_t* wh, uint32_t b) { atomicAdd(&wh[b], 1u); }
@@ -245,20 +186,20 @@ __global__ void __launch_bounds__(256) split_hist_kernel(const TensorDesc* __res
 
         if ((d.flags & kFlagAligned) && (d.es == 4 || d.es == 2) && d.spe * 2 == d.es) {
             const uint32_t nvec = nb >> 4;
-            // four independent 16-byte loads per thread are in flight before any of them is used
+            // a whole tile (kSplitLoads independent 16-byte loads per thread) is in flight before any of it is used
             const uint32_t iters = (nvec + 255) >> 8;
-            for (uint32_t it0 = 0; it0 < iters; it0 += 4) {
-                uint4 q[4];
-                bool ok[4];
+            for (uint32_t it0 = 0; it0 < iters; it0 += kSplitLoads) {
+                uint4 q[kSplitLoads];
+                bool ok[kSplitLoads];
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
+                for (int u = 0; u < kSplitLoads; ++u) {
                     const uint32_t v = (it0 + u) * 256 + tid;
                     ok[u] = v < nvec;
                     q[u] = make_uint4(0, 0, 0, 0);
                     if (ok[u]) q[u] = ld_global_v4(d.src + base + (size_t)v * 16);
                 }
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
+                for (int u = 0; u < kSplitLoads; ++u) {
                     if (!ok[u]) continue;
                     const uint32_t v = (it0 + u) * 256 + tid;
                     const uint32_t w[4] = {q[u].x, q[u].y, q[u].z, q[u].w};

@@ -39,6 +39,30 @@ class _Chunk:
         self.ctx = self.dev = self.ready = None
 
 
+def plan_chunks(sizes, chunk_bytes):
+    """Cut a sequence of tensor sizes (bytes) into consecutive chunks of at most chunk_bytes;
+    a tensor larger than that gets a chunk of its own.  Returns a list of index lists."""
+    chunks, cur, cur_bytes = [], [], 0
+    for i, n in enumerate(sizes):
+        if cur and cur_bytes + n > chunk_bytes:
+            chunks.append(cur)
+            cur, cur_bytes = [], 0
+        cur.append(i)
+        cur_bytes += n
+    if cur:
+        chunks.append(cur)
+    return chunks
+
+
+def staging_offsets(sizes, align=256):
+    """Offsets of a chunk's tensors inside its staging buffer (each aligned) and the buffer size."""
+    offs, total = [], 0
+    for n in sizes:
+        offs.append(total)
+        total += (n + align - 1) & ~(align - 1)
+    return offs, total
+
+
 class ChunkedHostPipeline:
     """Fixed set of host tensors <-> compressed parts, through per-chunk device buffers.
 
@@ -52,24 +76,18 @@ class ChunkedHostPipeline:
         import torch
         self.torch, self.device, self.rank, self.workers = torch, int(device), int(rank), max(1, int(workers))
         self.dev = torch.device("cuda", self.device)
+        host_tensors = list(host_tensors)
         self.chunks = []
-        cur = _Chunk(0)
-        for ht in host_tensors:
-            if cur.items and cur.nbytes + ht.nbytes > chunk_bytes:
-                self.chunks.append(cur)
-                cur = _Chunk(len(self.chunks))
-            cur.items.append(ht)
-            cur.nbytes += ht.nbytes
-        if cur.items:
-            self.chunks.append(cur)
+        for idx in plan_chunks([ht.nbytes for ht in host_tensors], chunk_bytes):
+            ch = _Chunk(len(self.chunks))
+            ch.items = [host_tensors[i] for i in idx]
+            ch.nbytes = sum(ht.nbytes for ht in ch.items)
+            self.chunks.append(ch)
         self.copy_in = torch.cuda.Stream(device=self.dev)
         self.copy_out = torch.cuda.Stream(device=self.dev)
         for ch in self.chunks:
             # one staging allocation per chunk; every tensor starts on a 256-byte boundary
-            offs, total = [], 0
-            for ht in ch.items:
-                offs.append(total)
-                total += (ht.nbytes + 255) & ~255
+            offs, total = staging_offsets([ht.nbytes for ht in ch.items])
             ch.dev = torch.empty(max(total, 1), dtype=torch.uint8, device=self.dev)
             ch.views = [ch.dev[o:o + ht.nbytes] for o, ht in zip(offs, ch.items)]
             ch.ctx = Context(device=self.device, rank=self.rank)
