@@ -25,7 +25,9 @@
 #include <filesystem>
 #include <fstream>
 #include <cstddef>
+#include <algorithm>
 #include <map>
+#include <memory>
 #include <mutex>
 #include <string>
 #include <thread>
@@ -125,7 +127,13 @@ struct Context {
     DevBuf d_descs, d_tiles, d_hist, d_sidecar, d_scratch, d_hdrs, d_lsrc, d_order, d_ticket, d_loff, d_psize, d_poff, d_nf16,
         d_payload, d_enc, d_freq, d_cum, d_status, d_stats_desc, d_stats_out;
     cudaStream_t side_stream = nullptr;
-    std::vector<cudaEvent_t> seg_events;
+    // compress pipeline: counting (stream), encoding, compaction and the zero-lane chains each have their own stream
+    cudaStream_t enc_streams[8] = {}, cmp_stream = nullptr, zero_streams[4] = {};
+    std::vector<cudaEvent_t> seg_events, ev_tab, ev_zero, ev_enc0, ev_enc1, ev_cmp0, ev_cmp1;
+    int segments = 3;             // launches the batch is cut into (1 = no overlap between stages)
+    int first_segment_pct = 0;    // share of the batch in the first segment (0 = equal shares)
+    int encode_after_count = 0;   // 1: encode grids start only when the whole batch has been counted
+    int encode_teams_per_sm = 0;  // cap on resident encode teams per SM and launch (0 = as many as fit)
     int sm_count = 0;
     // pinned host staging
     PinBuf h_hist, h_hdrs, h_poff, h_descs, h_status, h_enc, h_stats, h_order, h_tiles;
@@ -324,10 +332,19 @@ static void upload_order(Context* c, size_t W, SizeFn&& size_of) {
     control_zero(c, c->d_ticket.p, 256, c->stream);
 }
 
+static void ensure_events(std::vector<cudaEvent_t>& v, size_t n, bool timing) {
+    while (v.size() < n) {
+        cudaEvent_t e = nullptr;
+        CHK_CUDA(cudaEventCreateWithFlags(&e, timing ? cudaEventDefault : cudaEventDisableTiming));
+        v.push_back(e);
+    }
+}
+
 // Grid of a persistent team kernel: as many teams as fit on the device at once.
-static uint32_t persistent_grid(Context* c, const void* kernel, size_t smem, size_t W) {
+static uint32_t persistent_grid(Context* c, const void* kernel, size_t smem, size_t W, int cap_per_sm = 0) {
     int per_sm = 0;
     CHK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, (int)kTeam, smem));
+    if (cap_per_sm > 0 && per_sm > cap_per_sm) per_sm = cap_per_sm;
     if (per_sm < 1) per_sm = 1;
     const size_t cap = (size_t)per_sm * (size_t)(c->sm_count > 0 ? c->sm_count : 1);
     return (uint32_t)(W < cap ? W : cap);
@@ -400,7 +417,9 @@ static void compress(Context* c, bool host_images) {
     dev_ensure(c, c->d_scratch, scratch_total + 64);
     dev_ensure(c, c->d_hdrs, W * 4096);
     dev_ensure(c, c->d_lsrc, W * 2048);
-    upload_order(c, W, [&](size_t i) { return c->descs[i].n_bytes; });
+    dev_ensure(c, c->d_order, W * 4);
+    dev_ensure(c, c->d_ticket, 256);
+    pin_ensure(c->h_order, W * 4);
     dev_ensure(c, c->d_loff, W * 1024);
     dev_ensure(c, c->d_psize, W * 8);
     dev_ensure(c, c->d_poff, (W + 1) * 8);
@@ -427,22 +446,39 @@ static void compress(Context* c, bool host_images) {
     // ---- stage 1: low bytes out, histograms.  The batch is cut into a few segments; each
     // segment's histograms are copied back as soon as its launch is done, so the host
     // normalises segment g while the device still counts g+1.
-    const size_t n_seg = W >= 64 ? 8 : 1;
+    const size_t n_seg = W >= 64 ? (size_t)c->segments : 1;
     std::vector<size_t> seg_end(n_seg, W);
     {
         unsigned long long acc = 0;
         size_t g = 0;
         for (size_t i = 0; i < W && g + 1 < n_seg; ++i) {
             acc += c->descs[i].n_bytes;
-            // later segments are smaller, so little table work is left when the last one lands
-            static const unsigned kCut[8] = {16, 32, 47, 61, 74, 85, 94, 100};
-            if (acc * 100 >= bytes_total * kCut[g]) seg_end[g++] = i + 1;
+            // a smaller first segment gets the first encode grid going early; the rest are equal
+            const unsigned first = c->first_segment_pct > 0 ? (unsigned)c->first_segment_pct : (unsigned)(100 / n_seg);
+            const unsigned cut = first + (unsigned)((100 - first) * g / (n_seg - 1));
+            if (acc * 100 >= bytes_total * cut) seg_end[g++] = i + 1;
         }
     }
-    if (c->seg_events.size() < n_seg) {
-        const size_t old = c->seg_events.size();
-        c->seg_events.resize(n_seg);
-        for (size_t g = old; g < n_seg; ++g) CHK_CUDA(cudaEventCreateWithFlags(&c->seg_events[g], cudaEventDisableTiming));
+    ensure_events(c->seg_events, n_seg, false);
+    ensure_events(c->ev_tab, n_seg, false);
+    ensure_events(c->ev_zero, n_seg, false);
+    ensure_events(c->ev_enc0, n_seg, true);
+    ensure_events(c->ev_enc1, n_seg, true);
+    ensure_events(c->ev_cmp0, n_seg, true);
+    ensure_events(c->ev_cmp1, n_seg, true);
+    {
+        // every segment has its own largest-first order (indices relative to the segment) and ticket counter
+        uint32_t* ord = static_cast<uint32_t*>(c->h_order.p);
+        for (size_t g = 0, a = 0; g < n_seg; ++g) {
+            const size_t b = seg_end[g];
+            for (size_t i = a; i < b; ++i) ord[i] = (uint32_t)(i - a);
+            std::stable_sort(ord + a, ord + b, [&](uint32_t x, uint32_t y) {
+                return c->descs[a + x].n_bytes > c->descs[a + y].n_bytes;
+            });
+            a = b;
+        }
+        control_copy(c, c->d_order.p, c->h_order.p, W * 4, s);
+        control_zero(c, c->d_ticket.p, 256, s);
     }
     for (size_t g = 0, a = 0; g < n_seg; ++g) {
         const size_t b = seg_end[g];
@@ -463,18 +499,35 @@ static void compress(Context* c, bool host_images) {
     }
     CHK_CUDA(cudaEventRecord(c->ev[1], s));
 
-    // ---- tables on the host: worker threads take tensors in order and wait for the
-    // segment a tensor belongs to; the calling thread releases segments as their copies land.
+    // ---- tables on the host, and everything after them, segment by segment.
+    // Worker threads normalise tensors in order, waiting for the segment a tensor belongs to;
+    // a releaser thread marks segments whose histograms have landed.  The calling thread
+    // launches, for each segment in turn as soon as its tables are done: table upload and
+    // build_tables_kernel, the encode grid (a stream per segment, so the grids of several
+    // segments share the device: one segment alone has too few tensors to fill it), the shared
+    // zero-lane chains (their own streams), then offsets and compaction (compaction stream).
+    // The device thus counts later segments and compacts earlier ones (memory-bound work)
+    // while it encodes (issue-bound work).
     const auto t_tab = std::chrono::steady_clock::now();
     uint16_t* h_nf16 = static_cast<uint16_t*>(c->h_enc.p);
+    bool any_int = false;
+    for (size_t i = 0; i < W && !any_int; ++i) any_int = c->work[i].spe * 2 != c->work[i].es;
+    std::vector<bool> launched(n_seg, false);
     {
         std::vector<size_t> owners;
         std::vector<uint32_t> owner_seg;
+        std::vector<size_t> tab_lo(n_seg, 0), tab_hi(n_seg, 0);  // tables owned inside each segment: [lo, hi)
+        std::unique_ptr<std::atomic<uint32_t>[]> seg_left(new std::atomic<uint32_t>[n_seg]);
+        for (size_t g = 0; g < n_seg; ++g) seg_left[g].store(0);
         for (size_t i = 0, g = 0; i < W; ++i) {
             while (i >= seg_end[g]) ++g;
             if (c->work[i].owns) {
+                const size_t t = (size_t)c->work[i].table;
+                if (tab_hi[g] == tab_lo[g]) tab_lo[g] = t;
+                tab_hi[g] = t + 1;
                 owners.push_back(i);
                 owner_seg.push_back((uint32_t)g);
+                seg_left[g].fetch_add(1);
             }
         }
         std::atomic<uint32_t> ready{0};  // segments whose histograms are on the host
@@ -483,22 +536,28 @@ static void compress(Context* c, bool host_images) {
         std::condition_variable cv;
         const uint32_t* hist_all = static_cast<const uint32_t*>(c->h_hist.p);
         auto work_fn = [&](size_t k) {
-            if (ready.load(std::memory_order_acquire) <= owner_seg[k]) {
+            const uint32_t g = owner_seg[k];
+            if (ready.load(std::memory_order_acquire) <= g) {
                 std::unique_lock<std::mutex> lk(mu);
-                cv.wait(lk, [&] { return ready.load(std::memory_order_acquire) > owner_seg[k] || failed.load(); });
+                cv.wait(lk, [&] { return ready.load(std::memory_order_acquire) > g || failed.load(); });
             }
-            if (failed.load()) return;
-            const size_t i = owners[k];
-            const WorkItem& w = c->work[i];
-            uint32_t h[256];
-            std::memcpy(h, hist_all + i * 256, 1024);
-            // the zeroed low bytes of every element are part of the codec input
-            h[0] += (uint32_t)((uint64_t)c->tensors[w.idx].n_elem * w.spe);
-            const bool full = is_cluster_anchor(c, w);
-            FreqTable& ft = c->tables[w.table];
-            normalize_histogram(h, full, full && c->repair_tables, ft);
-            uint16_t* o = h_nf16 + (size_t)w.table * 256;
-            for (int sy = 0; sy < 256; ++sy) o[sy] = (uint16_t)ft.norm_freq[sy];
+            if (!failed.load()) {
+                const size_t i = owners[k];
+                const WorkItem& w = c->work[i];
+                uint32_t h[256];
+                std::memcpy(h, hist_all + i * 256, 1024);
+                // the zeroed low bytes of every element are part of the codec input
+                h[0] += (uint32_t)((uint64_t)c->tensors[w.idx].n_elem * w.spe);
+                const bool full = is_cluster_anchor(c, w);
+                FreqTable& ft = c->tables[w.table];
+                normalize_histogram(h, full, full && c->repair_tables, ft);
+                uint16_t* o = h_nf16 + (size_t)w.table * 256;
+                for (int sy = 0; sy < 256; ++sy) o[sy] = (uint16_t)ft.norm_freq[sy];
+            }
+            if (seg_left[g].fetch_sub(1) == 1) {  // last table of its segment: wake the launcher
+                std::lock_guard<std::mutex> lk(mu);
+                cv.notify_all();
+            }
         };
         std::thread releaser([&] {
             cudaSetDevice(c->device);
@@ -512,93 +571,134 @@ static void compress(Context* c, bool host_images) {
                 if (!ok) return;
             }
         });
-        parallel_for(owners.size(), c->host_threads, work_fn);
+        std::thread normaliser([&] { parallel_for(owners.size(), c->host_threads, work_fn); });
+
+        auto launch_segment = [&](size_t g, size_t a, size_t b) {
+            const size_t n = b - a;
+            cudaStream_t sB = c->enc_streams[g % 8], sC = c->cmp_stream, sZ = c->zero_streams[g % 4];
+            const TensorDesc* descs_g = static_cast<const TensorDesc*>(c->d_descs.p) + a;
+            LaneHeader* hdrs_g = static_cast<LaneHeader*>(c->d_hdrs.p) + a * 256;
+            unsigned long long* lsrc_g = static_cast<unsigned long long*>(c->d_lsrc.p) + a * 256;
+            uint32_t* loff_g = static_cast<uint32_t*>(c->d_loff.p) + a * 256;
+            const EncEntry* enc = static_cast<const EncEntry*>(c->d_enc.p);
+            CHK_CUDA(cudaStreamWaitEvent(sB, c->encode_after_count ? c->ev[1] : c->seg_events[g], 0));
+            // frequencies up (512 B per table); prefix sums and encode entries are derived on the device
+            if (tab_hi[g] > tab_lo[g]) {
+                const size_t t0 = tab_lo[g], nt = tab_hi[g] - tab_lo[g];
+                control_copy(c, static_cast<uint16_t*>(c->d_nf16.p) + t0 * 256, h_nf16 + t0 * 256, nt * 512, sB);
+                build_tables_kernel<<<(uint32_t)(nt < 4096 ? nt : 4096), 256, 0, sB>>>(
+                    static_cast<const uint16_t*>(c->d_nf16.p) + t0 * 256, static_cast<EncEntry*>(c->d_enc.p) + t0 * 256,
+                    static_cast<uint32_t*>(c->d_freq.p) + t0 * 256, static_cast<uint32_t*>(c->d_cum.p) + t0 * 257,
+                    (uint32_t)nt);
+                CHK_CUDA(cudaGetLastError());
+                c->launches++;
+            }
+            CHK_CUDA(cudaEventRecord(c->ev_tab[g], sB));
+            // the shared symbol-0 chain of every tensor (one thread each) runs next to the value lanes
+            CHK_CUDA(cudaStreamWaitEvent(sZ, c->ev_tab[g], 0));
+            zero_lane_kernel<<<(uint32_t)((n + 127) / 128), 128, 0, sZ>>>(descs_g, enc, static_cast<uint8_t*>(c->d_scratch.p),
+                                                                          hdrs_g, lsrc_g, (uint32_t)n);
+            CHK_CUDA(cudaGetLastError());
+            CHK_CUDA(cudaEventRecord(c->ev_zero[g], sZ));
+            // A tensor can only meet a symbol its table lacks when it borrows another tensor's
+            // table; the reference builds shared tables over the full alphabet, so this is
+            // normally false and the kernel without the escape test runs.
+            bool need_escape = false;
+            for (size_t i = a; i < b && !need_escape; ++i) {
+                if (c->work[i].owns) continue;
+                const FreqTable& ft = c->tables[c->work[i].table];
+                for (int sy = 0; sy < 256 && !need_escape; ++sy) need_escape = ft.norm_freq[sy] == 0;
+            }
+            auto kernel = any_int ? (need_escape ? rans_encode_kernel<true, true> : rans_encode_kernel<true, false>)
+                                  : (need_escape ? rans_encode_kernel<false, true> : rans_encode_kernel<false, false>);
+            const size_t smem = any_int ? sizeof(EncSmem<4>) : sizeof(EncSmem<2>);
+            const uint32_t grid = persistent_grid(c, reinterpret_cast<const void*>(kernel), smem, n,
+                                                  n_seg > 1 ? c->encode_teams_per_sm : 0);
+            CHK_CUDA(cudaEventRecord(c->ev_enc0[g], sB));
+            kernel<<<grid, kTeam, smem, sB>>>(descs_g, enc, static_cast<uint8_t*>(c->d_scratch.p), hdrs_g, lsrc_g,
+                                              static_cast<const uint32_t*>(c->d_order.p) + a,
+                                              static_cast<uint32_t*>(c->d_ticket.p) + g, (uint32_t)n);
+            CHK_CUDA(cudaGetLastError());
+            CHK_CUDA(cudaEventRecord(c->ev_enc1[g], sB));
+            c->launches += 2;
+            // offsets + compaction into the data-section layout; the running payload offset is
+            // handed from one segment's scan to the next through d_poff
+            CHK_CUDA(cudaStreamWaitEvent(sC, c->ev_enc1[g], 0));
+            CHK_CUDA(cudaStreamWaitEvent(sC, c->ev_zero[g], 0));
+            CHK_CUDA(cudaEventRecord(c->ev_cmp0[g], sC));
+            unsigned long long* poff_g = static_cast<unsigned long long*>(c->d_poff.p) + a;
+            lane_scan_kernel<<<(uint32_t)(n < 4096 ? n : 4096), 256, 0, sC>>>(
+                static_cast<TensorDesc*>(c->d_descs.p) + a, hdrs_g, static_cast<unsigned long long*>(c->d_psize.p) + a,
+                loff_g, (uint32_t)n);
+            CHK_CUDA(cudaGetLastError());
+            tensor_scan_kernel<<<1, 1024, 0, sC>>>(static_cast<TensorDesc*>(c->d_descs.p) + a,
+                                                   static_cast<const unsigned long long*>(c->d_psize.p) + a, poff_g,
+                                                   (uint32_t)n, a ? poff_g : nullptr);
+            CHK_CUDA(cudaGetLastError());
+            const unsigned long long blocks = ((unsigned long long)n * 256 + 7) / 8;
+            const uint32_t g3 = (uint32_t)(blocks < 148ull * 16 ? blocks : 148ull * 16);
+            compact_kernel<<<g3, 256, 0, sC>>>(descs_g, hdrs_g, lsrc_g, loff_g, static_cast<const uint8_t*>(c->d_scratch.p),
+                                               static_cast<uint8_t*>(c->d_payload.p), (uint32_t)n);
+            CHK_CUDA(cudaGetLastError());
+            CHK_CUDA(cudaEventRecord(c->ev_cmp1[g], sC));
+            c->launches += 3;
+            launched[g] = true;
+        };
+
+        Error pending{CHK_OK, ""};
+        try {
+            for (size_t g = 0, a = 0; g < n_seg; ++g) {
+                const size_t b = seg_end[g];
+                {
+                    std::unique_lock<std::mutex> lk(mu);
+                    cv.wait(lk, [&] {
+                        return failed.load() || (seg_left[g].load() == 0 && ready.load(std::memory_order_acquire) > g);
+                    });
+                }
+                if (failed.load()) break;
+                if (b > a) launch_segment(g, a, b);
+                a = b;
+            }
+        } catch (const Error& e) {
+            pending = e;
+            {
+                std::lock_guard<std::mutex> lk(mu);
+                failed.store(true);
+            }
+            cv.notify_all();
+        }
+        normaliser.join();
         releaser.join();
+        if (pending.code != CHK_OK) throw pending;
         if (failed.load()) CHK_CUDA(cudaStreamSynchronize(s));  // surfaces the device error
     }
     c->timing["table_ms"] = wall_ms(t_tab);
 
-    // frequencies up (512 B per table); prefix sums and encode entries are derived on the device
-    control_copy(c, c->d_nf16.p, h_nf16, T * 512, s);
-    build_tables_kernel<<<(uint32_t)(T < 4096 ? T : 4096), 256, 0, s>>>(
-        static_cast<const uint16_t*>(c->d_nf16.p), static_cast<EncEntry*>(c->d_enc.p),
-        static_cast<uint32_t*>(c->d_freq.p), static_cast<uint32_t*>(c->d_cum.p), (uint32_t)T);
-    CHK_CUDA(cudaGetLastError());
-    c->launches++;
-    CHK_CUDA(cudaEventRecord(c->ev[2], s));
-
-    // ---- stage 2: encode
-    {
-        // The shared symbol-0 chain of every tensor (one thread each) runs on the side
-        // stream next to the value lanes; both are joined before the offsets are computed.
-        CHK_CUDA(cudaStreamWaitEvent(c->side_stream, c->ev[2], 0));
-        zero_lane_kernel<<<(uint32_t)((W + 127) / 128), 128, 0, c->side_stream>>>(
-            static_cast<const TensorDesc*>(c->d_descs.p), static_cast<const EncEntry*>(c->d_enc.p),
-            static_cast<uint8_t*>(c->d_scratch.p), static_cast<LaneHeader*>(c->d_hdrs.p),
-            static_cast<unsigned long long*>(c->d_lsrc.p), (uint32_t)W);
-        CHK_CUDA(cudaGetLastError());
-        CHK_CUDA(cudaEventRecord(c->ev[7], c->side_stream));
-        bool any_int = false;
-        for (size_t i = 0; i < W && !any_int; ++i) any_int = c->work[i].spe * 2 != c->work[i].es;
-        // A tensor can only meet a symbol its table lacks when it borrows another tensor's
-        // table; the reference builds shared tables over the full alphabet, so this is
-        // normally false and the kernel without the escape test runs.
-        bool need_escape = false;
-        for (size_t i = 0; i < W && !need_escape; ++i) {
-            if (c->work[i].owns) continue;
-            const FreqTable& ft = c->tables[c->work[i].table];
-            for (int sy = 0; sy < 256 && !need_escape; ++sy) need_escape = ft.norm_freq[sy] == 0;
-        }
-        auto kernel = any_int ? (need_escape ? rans_encode_kernel<true, true> : rans_encode_kernel<true, false>)
-                              : (need_escape ? rans_encode_kernel<false, true> : rans_encode_kernel<false, false>);
-        const size_t smem = any_int ? sizeof(EncSmem<4>) : sizeof(EncSmem<2>);
-        const uint32_t grid = persistent_grid(c, reinterpret_cast<const void*>(kernel), smem, W);
-        kernel<<<grid, kTeam, smem, s>>>(
-            static_cast<const TensorDesc*>(c->d_descs.p), static_cast<const EncEntry*>(c->d_enc.p),
-            static_cast<uint8_t*>(c->d_scratch.p), static_cast<LaneHeader*>(c->d_hdrs.p),
-            static_cast<unsigned long long*>(c->d_lsrc.p), static_cast<const uint32_t*>(c->d_order.p),
-            static_cast<uint32_t*>(c->d_ticket.p), (uint32_t)W);
-        CHK_CUDA(cudaGetLastError());
-        c->launches += 2;
-    }
-    CHK_CUDA(cudaEventRecord(c->ev[3], s));
-    CHK_CUDA(cudaStreamWaitEvent(s, c->ev[7], 0));
-
-    // ---- stage 3: offsets + compaction into the data-section layout
-    {
-        const uint32_t g1 = (uint32_t)(W < 4096 ? W : 4096);
-        lane_scan_kernel<<<g1, 256, 0, s>>>(static_cast<TensorDesc*>(c->d_descs.p),
-                                            static_cast<LaneHeader*>(c->d_hdrs.p),
-                                            static_cast<unsigned long long*>(c->d_psize.p),
-                                            static_cast<uint32_t*>(c->d_loff.p), (uint32_t)W);
-        CHK_CUDA(cudaGetLastError());
-        tensor_scan_kernel<<<1, 1024, 0, s>>>(static_cast<TensorDesc*>(c->d_descs.p),
-                                              static_cast<const unsigned long long*>(c->d_psize.p),
-                                              static_cast<unsigned long long*>(c->d_poff.p), (uint32_t)W);
-        CHK_CUDA(cudaGetLastError());
-        const unsigned long long warps = (unsigned long long)W * 256;
-        const unsigned long long blocks = (warps + 7) / 8;
-        const uint32_t g3 = (uint32_t)(blocks < 148ull * 16 ? blocks : 148ull * 16);
-        compact_kernel<<<g3, 256, 0, s>>>(static_cast<const TensorDesc*>(c->d_descs.p),
-                                          static_cast<const LaneHeader*>(c->d_hdrs.p),
-                                          static_cast<const unsigned long long*>(c->d_lsrc.p),
-                                          static_cast<const uint32_t*>(c->d_loff.p),
-                                          static_cast<const uint8_t*>(c->d_scratch.p),
-                                          static_cast<uint8_t*>(c->d_payload.p), (uint32_t)W);
-        CHK_CUDA(cudaGetLastError());
-        c->launches += 3;
-    }
-    CHK_CUDA(cudaEventRecord(c->ev[4], s));
-    control_copy(c, c->h_poff.p, c->d_poff.p, (W + 1) * 8, s);
-    control_copy(c, c->h_descs.p, c->d_descs.p, W * sizeof(TensorDesc), s);
-    if (host_images) control_copy(c, c->h_hdrs.p, c->d_hdrs.p, W * 4096, s);
+    cudaStream_t s_end = c->cmp_stream;
+    control_copy(c, c->h_poff.p, c->d_poff.p, (W + 1) * 8, s_end);
+    control_copy(c, c->h_descs.p, c->d_descs.p, W * sizeof(TensorDesc), s_end);
+    if (host_images) control_copy(c, c->h_hdrs.p, c->d_hdrs.p, W * 4096, s_end);
+    CHK_CUDA(cudaStreamSynchronize(s_end));
     CHK_CUDA(cudaStreamSynchronize(s));
 
+    // encode grids of different segments run side by side: their time is the span from the first
+    // start to the last end; compactions run one after the other and are summed.  The stages
+    // overlap, so the three figures add up to more than device_span_ms.
+    double enc_ms = 0, cmp_ms = 0;
+    size_t first = n_seg, last = n_seg;
+    for (size_t g = 0; g < n_seg; ++g) {
+        if (!launched[g]) continue;
+        if (first == n_seg) first = g;
+        const double e = ms_between(c->ev_enc0[first], c->ev_enc1[g]);
+        if (e > enc_ms) enc_ms = e;
+        cmp_ms += ms_between(c->ev_cmp0[g], c->ev_cmp1[g]);
+        last = g;
+    }
     c->timing["split_hist_ms"] = ms_between(c->ev[0], c->ev[1]);
-    c->timing["encode_ms"] = ms_between(c->ev[2], c->ev[3]);
-    c->timing["compact_ms"] = ms_between(c->ev[3], c->ev[4]);
-    c->timing["table_gap_ms"] = ms_between(c->ev[1], c->ev[2]);  // device idle between counting and encoding
-    c->timing["device_span_ms"] = ms_between(c->ev[0], c->ev[4]);
+    c->timing["encode_ms"] = enc_ms;
+    c->timing["compact_ms"] = cmp_ms;
+    c->timing["device_span_ms"] = last < n_seg ? ms_between(c->ev[0], c->ev_cmp1[last]) : 0.0;
+    c->timing["compress_device_ms"] = c->timing["device_span_ms"];
     c->timing["to_sync_ms"] = wall_ms(t_total);
     c->timing["compress_device_ms"] =
         c->timing["split_hist_ms"] + c->timing["encode_ms"] + c->timing["compact_ms"];
@@ -727,7 +827,7 @@ static void compress_and_save(Context* c, const std::string& dir) {
 // ------------------------------------------------------------------ restore
 static void run_decode(Context* c, size_t W, const uint8_t* d_payload, const uint8_t* d_sidecar,
                        const uint32_t* d_freq, const uint32_t* d_cum, const LaneHeader* d_hdrs,
-                       const std::vector<std::string>& names) {
+                       const std::vector<size_t>& tensor_of) {
     cudaStream_t s = c->stream;
     dev_ensure(c, c->d_status, W * 4 + 256);
     pin_ensure(c->h_status, W * 4 + 256);
@@ -758,7 +858,7 @@ static void run_decode(Context* c, size_t W, const uint8_t* d_payload, const uin
     const uint32_t* st = static_cast<const uint32_t*>(c->h_status.p);
     for (size_t i = 0; i < W; ++i)
         if (st[i])
-            throw Error{CHK_ERR_DECODE, "tensor '" + names[i] + "' failed its stream check (" +
+            throw Error{CHK_ERR_DECODE, "tensor '" + c->tensors[tensor_of[i]].name + "' failed its stream check (" +
                                             ((st[i] & kErrEndState) ? "end state " : "") +
                                             ((st[i] & kErrEndPointer) ? "stream length" : "") + ")"};
     c->restored = W;
@@ -771,7 +871,7 @@ static void decompress_resident(Context* c, void* const* dst) {
     c->restored = 0;
     std::vector<TensorDesc> run;
     std::vector<size_t> src_index;
-    std::vector<std::string> names;
+    std::vector<size_t> tensor_of;
     for (size_t i = 0; i < c->work.size(); ++i) {
         const WorkItem& w = c->work[i];
         void* target = dst ? dst[w.idx] : c->tensors[w.idx].ptr;
@@ -787,7 +887,7 @@ static void decompress_resident(Context* c, void* const* dst) {
         if ((reinterpret_cast<uintptr_t>(target) & 15) == 0 && (d.sidecar_off & 15) == 0) d.flags |= kFlagAligned;
         run.push_back(d);
         src_index.push_back(i);
-        names.push_back(c->tensors[w.idx].name);
+        tensor_of.push_back(w.idx);
     }
     const size_t W = run.size();
     if (W == 0) return;
@@ -800,7 +900,7 @@ static void decompress_resident(Context* c, void* const* dst) {
     control_copy(c, c->d_descs.p, c->h_descs.p, W * sizeof(TensorDesc), c->stream);
     run_decode(c, W, static_cast<const uint8_t*>(c->d_payload.p), static_cast<const uint8_t*>(c->d_sidecar.p),
                static_cast<const uint32_t*>(c->d_freq.p), static_cast<const uint32_t*>(c->d_cum.p),
-               static_cast<const LaneHeader*>(c->d_hdrs.p), names);
+               static_cast<const LaneHeader*>(c->d_hdrs.p), tensor_of);
     c->timing["decompress_total_ms"] = wall_ms(t_total);
 }
 
@@ -831,7 +931,7 @@ static void decompress_images(Context* c, const uint8_t* st, size_t st_n, const 
 
     std::vector<TensorDesc> run;
     std::vector<size_t> entry_of;
-    std::vector<std::string> names;
+    std::vector<size_t> tensor_of;
     for (size_t i = 0; i < n_st; ++i) {
         const uint8_t* e = st + kFileHeader + i * kStatesEntry;
         const std::string name = get_name(e);
@@ -887,7 +987,7 @@ static void decompress_images(Context* c, const uint8_t* st, size_t st_n, const 
         if ((reinterpret_cast<uintptr_t>(d.dst) & 15) == 0 && (d.sidecar_off & 15) == 0) d.flags |= kFlagAligned;
         run.push_back(d);
         entry_of.push_back(i);
-        names.push_back(name);
+        tensor_of.push_back(r->second);
     }
     const size_t W = run.size();
     if (W == 0) return;
@@ -926,7 +1026,7 @@ static void decompress_images(Context* c, const uint8_t* st, size_t st_n, const 
     CHK_CUDA(cudaEventRecord(c->ev[3], s));
     run_decode(c, W, static_cast<const uint8_t*>(c->d_payload.p), static_cast<const uint8_t*>(c->d_sidecar.p),
                static_cast<const uint32_t*>(c->d_freq.p), static_cast<const uint32_t*>(c->d_cum.p),
-               static_cast<const LaneHeader*>(c->d_hdrs.p), names);
+               static_cast<const LaneHeader*>(c->d_hdrs.p), tensor_of);
     c->timing["h2d_ms"] = ms_between(c->ev[0], c->ev[3]);
     c->timing["decode_wait_ms"] = ms_between(c->ev[3], c->ev[1]);
     c->timing["decompress_total_ms"] = wall_ms(t_total);
@@ -1039,8 +1139,15 @@ int chk_context_create(int device, int rank, int local_rank, chk_context** out) 
     c->rank = rank;
     c->local_rank = local_rank;
     try {
-        CHK_CUDA(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
+        // the counting stream gets the highest priority: its blocks go first whenever an SM has room,
+        // so the encode teams of earlier segments do not hold up the tables of later ones
+        int prio_lo = 0, prio_hi = 0;
+        CHK_CUDA(cudaDeviceGetStreamPriorityRange(&prio_lo, &prio_hi));
+        CHK_CUDA(cudaStreamCreateWithPriority(&c->stream, cudaStreamNonBlocking, prio_hi));
         CHK_CUDA(cudaStreamCreateWithFlags(&c->side_stream, cudaStreamNonBlocking));
+        for (auto& e : c->enc_streams) CHK_CUDA(cudaStreamCreateWithFlags(&e, cudaStreamNonBlocking));
+        CHK_CUDA(cudaStreamCreateWithFlags(&c->cmp_stream, cudaStreamNonBlocking));
+        for (auto& z : c->zero_streams) CHK_CUDA(cudaStreamCreateWithFlags(&z, cudaStreamNonBlocking));
         CHK_CUDA(cudaDeviceGetAttribute(&c->sm_count, cudaDevAttrMultiProcessorCount, device));
         cudaMemPoolProps props{};
         props.allocType = cudaMemAllocationTypePinned;
@@ -1076,8 +1183,14 @@ int chk_context_destroy(chk_context* c) {
         if (b->p) cudaFreeHost(b->p);
     for (auto& e : c->ev)
         if (e) cudaEventDestroy(e);
-    for (auto& e : c->seg_events)
-        if (e) cudaEventDestroy(e);
+    for (auto* v : {&c->seg_events, &c->ev_tab, &c->ev_zero, &c->ev_enc0, &c->ev_enc1, &c->ev_cmp0, &c->ev_cmp1})
+        for (auto& e : *v)
+            if (e) cudaEventDestroy(e);
+    for (auto& e : c->enc_streams)
+        if (e) cudaStreamDestroy(e);
+    if (c->cmp_stream) cudaStreamDestroy(c->cmp_stream);
+    for (auto& z : c->zero_streams)
+        if (z) cudaStreamDestroy(z);
     if (c->pool) cudaMemPoolDestroy(c->pool);
     if (c->side_stream) cudaStreamDestroy(c->side_stream);
     if (c->stream) cudaStreamDestroy(c->stream);
@@ -1135,7 +1248,18 @@ int chk_set_option(chk_context* c, const char* key, int64_t value) {
         c->host_threads = (int)value;
     else if (k == "decode_two_level")
         c->decode_two_level = value != 0;
-    else
+    else if (k == "segments") {
+        if (value < 1 || value > 8) throw chk::Error{CHK_ERR_INVALID, "segments must be 1..8"};
+        c->segments = (int)value;
+    } else if (k == "first_segment_pct") {
+        if (value < 0 || value > 90) throw chk::Error{CHK_ERR_INVALID, "first_segment_pct must be 0..90"};
+        c->first_segment_pct = (int)value;
+    } else if (k == "encode_after_count") {
+        c->encode_after_count = value != 0;
+    } else if (k == "encode_teams_per_sm") {
+        if (value < 0 || value > 64) throw chk::Error{CHK_ERR_INVALID, "encode_teams_per_sm must be 0..64 (0 = as many as fit)"};
+        c->encode_teams_per_sm = (int)value;
+    } else
         throw chk::Error{CHK_ERR_INVALID, "unknown option: " + k};
     CHK_API_END
 }
@@ -1461,7 +1585,7 @@ extern "C" int chk_encode_tensor_static(const void* d_src, uint64_t num_elements
     lane_scan_kernel<<<1, 256, 0, s>>>(&dev->desc, static_cast<LaneHeader*>(d_lane_headers), dev->payload_size,
                                        dev->lane_off, 1u);
     CHK_CUDA(cudaGetLastError());
-    tensor_scan_kernel<<<1, 1024, 0, s>>>(&dev->desc, dev->payload_size, dev->payload_off, 1u);
+    tensor_scan_kernel<<<1, 1024, 0, s>>>(&dev->desc, dev->payload_size, dev->payload_off, 1u, nullptr);
     CHK_CUDA(cudaGetLastError());
     compact_kernel<<<32, 256, 0, s>>>(&dev->desc, static_cast<const LaneHeader*>(d_lane_headers), dev->lane_src,
                                       dev->lane_off, base, static_cast<uint8_t*>(d_payload), 1u);

@@ -408,12 +408,16 @@ __global__ void __launch_bounds__(256) lane_scan_kernel(TensorDesc* __restrict__
 }
 
 // Exclusive prefix sum of the per-tensor payload sizes (one CTA); total in out[n].
+// A batch scanned in several launches chains them: `start` points at the total the
+// previous launch left (its out[n], which is this launch's out[0]); null starts at 0.
 __global__ void __launch_bounds__(1024) tensor_scan_kernel(TensorDesc* __restrict__ descs,
                                                            const unsigned long long* __restrict__ payload_size,
                                                            unsigned long long* __restrict__ payload_off,
-                                                           uint32_t n_tensors) {
+                                                           uint32_t n_tensors, const unsigned long long* start) {
     CHK_SHARED unsigned long long part[1024];
     const uint32_t t = threadIdx.x;
+    const unsigned long long first = start ? *start : 0ull;
+    __syncthreads();  // everyone has read the start before out[0] is rewritten
     const uint32_t per = (n_tensors + 1023) / 1024;
     const uint32_t lo = t * per < n_tensors ? t * per : n_tensors;
     const uint32_t hi = lo + per < n_tensors ? lo + per : n_tensors;
@@ -422,7 +426,7 @@ __global__ void __launch_bounds__(1024) tensor_scan_kernel(TensorDesc* __restric
     part[t] = s;
     __syncthreads();
     if (t == 0) {
-        unsigned long long run = 0;
+        unsigned long long run = first;
         for (uint32_t i = 0; i < 1024; ++i) {
             const unsigned long long v = part[i];
             part[i] = run;

@@ -54,22 +54,23 @@ inline void normalize_histogram(const uint32_t hist[256], bool ensure_full_alpha
         int sym;
         double frac;
     };
-    std::vector<Key> keys;
-    keys.reserve(256);
+    Key keys[256];
+    size_t n_keys = 0;
     for (int s = 0; s < 256; ++s) {
         if (!slots[s]) continue;
         const double exact = total ? ((double)std::max(hist[s], 1u) * kM / (double)total) : 1.0;
-        keys.push_back({s, exact - (double)(int)exact});
+        keys[n_keys++] = {s, exact - (double)(int)exact};
     }
-    std::sort(keys.begin(), keys.end(), [](const Key& a, const Key& b) { return a.frac > b.frac; });
+    if (assigned != kM)  // the order is only consulted when slots have to be handed out or taken back
+        std::sort(keys, keys + n_keys, [](const Key& a, const Key& b) { return a.frac > b.frac; });
     if (assigned < kM) {
         uint32_t rem = kM - assigned;
-        for (size_t k = 0; k < keys.size() && rem; ++k, --rem) slots[keys[k].sym]++;
+        for (size_t k = 0; k < n_keys && rem; ++k, --rem) slots[keys[k].sym]++;
     } else if (assigned > kM) {
         uint32_t rem = assigned - kM;
         for (;;) {
             const uint32_t before = rem;
-            for (int k = (int)keys.size() - 1; k >= 0 && rem; --k)
+            for (int k = (int)n_keys - 1; k >= 0 && rem; --k)
                 if (slots[keys[k].sym] > 1) {
                     slots[keys[k].sym]--;
                     --rem;

@@ -71,7 +71,12 @@ int chk_tensor_count(chk_context* ctx, uint64_t* count);
 /* Options: "repair_tables" (0/1; shared tables are renormalised until they sum
  * to 4096 -- a deviation from the reference that keeps them decodable),
  * "verify_zero_lanes" (0/1; decode also checks the lanes that only carry
- * zeroed low bytes), "host_threads" (threads for table normalisation, 0 = all). */
+ * zeroed low bytes), "host_threads" (threads for table normalisation, 0 = all),
+ * "decode_two_level" (0/1; 5 KiB two-level decode table instead of 16 KiB),
+ * "segments" (1..8, default 8: pieces a batch of 64 tensors or more is cut into so
+ * that counting, encoding and compaction of neighbouring pieces overlap on the
+ * device; 1 runs the stages one after the other), "encode_teams_per_sm" (default
+ * 0 = as many as fit: cap on the resident encode teams per SM of one launch). */
 int chk_set_option(chk_context* ctx, const char* key, int64_t value);
 
 /* ---- analysis: checkers::analyze_tensors, src/api.cpp:1033-1253 ----------

@@ -112,7 +112,7 @@ uint32_t emu_encode(size_t n, const uint8_t* const* srcs, const uint64_t* n_byte
                                            &ticket, (uint32_t)n);
         });
     emu::launch(grid, 256, 0, [&] { lane_scan_kernel(b.descs.data(), hdrs.data(), psize.data(), loff.data(), (uint32_t)n); });
-    emu::launch(1, 1024, 0, [&] { tensor_scan_kernel(b.descs.data(), psize.data(), poff.data(), (uint32_t)n); });
+    emu::launch(1, 1024, 0, [&] { tensor_scan_kernel(b.descs.data(), psize.data(), poff.data(), (uint32_t)n, nullptr); });
     emu::launch(grid, 256, 0, [&] {
         compact_kernel(b.descs.data(), hdrs.data(), lsrc.data(), loff.data(), scr, payload_out, (uint32_t)n);
     });
