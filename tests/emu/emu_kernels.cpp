@@ -79,7 +79,7 @@ void emu_split_hist(size_t n, const uint8_t* const* srcs, const uint64_t* n_byte
 uint32_t emu_encode(size_t n, const uint8_t* const* srcs, const uint64_t* n_bytes, const uint32_t* es,
                     const uint32_t* spe, const uint32_t* table_idx, size_t n_tables, const uint32_t* nf,
                     const uint32_t* cf, uint8_t* payload_out, uint64_t* payload_off_out, uint32_t* hdrs_out,
-                    uint8_t* raw_out, uint32_t grid, uint32_t float_only) {
+                    uint8_t* raw_out, uint32_t grid, uint32_t float_only, uint32_t segments) {
     Batch b = make_batch(n, srcs, nullptr, n_bytes, es, spe, table_idx, nullptr);
     std::vector<EncEntry> enc(n_tables * 256);
     for (size_t t = 0; t < n_tables; ++t) {
@@ -94,28 +94,36 @@ uint32_t emu_encode(size_t n, const uint8_t* const* srcs, const uint64_t* n_byte
     std::vector<LaneHeader> hdrs(n * 256);
     std::vector<unsigned long long> lsrc(n * 256);
     std::vector<uint32_t> loff(n * 256);
-    std::vector<uint32_t> order(n);
-    for (size_t i = 0; i < n; ++i) order[i] = (uint32_t)(n - 1 - i);  // any permutation must give the same result
-    uint32_t ticket = 0;
+    // The batch runs as `segments` consecutive ranges, each through its own launches on offset
+    // pointers, the way the library's compress pipeline does; any cut must give the same bytes.
     std::vector<unsigned long long> psize(n), poff(n + 1);
     uint32_t status = 0;
-    emu::launch((unsigned)((n + 127) / 128), 128, 0,
-                [&] { zero_lane_kernel(b.descs.data(), enc.data(), scr, hdrs.data(), lsrc.data(), (uint32_t)n); });
-    if (float_only)  // the variant the pipeline uses for float-only batches without missing symbols
-        emu::launch(grid, kTeam, sizeof(EncSmem<2>), [&] {
-            rans_encode_kernel<false, false>(b.descs.data(), enc.data(), scr, hdrs.data(), lsrc.data(), order.data(),
-                                             &ticket, (uint32_t)n);
+    if (segments < 1) segments = 1;
+    std::vector<uint32_t> order(n);
+    std::vector<uint32_t> tickets(segments, 0);
+    for (uint32_t g = 0; g < segments; ++g) {
+        const size_t a = n * g / segments, e = n * (g + 1) / segments, m = e - a;
+        if (m == 0) continue;
+        for (size_t i = 0; i < m; ++i) order[a + i] = (uint32_t)(m - 1 - i);  // any permutation must give the same result
+        TensorDesc* descs = b.descs.data() + a;
+        LaneHeader* hd = hdrs.data() + a * 256;
+        unsigned long long* ls = lsrc.data() + a * 256;
+        uint32_t* lo = loff.data() + a * 256;
+        emu::launch((unsigned)((m + 127) / 128), 128, 0, [&] { zero_lane_kernel(descs, enc.data(), scr, hd, ls, (uint32_t)m); });
+        if (float_only)  // the variant the pipeline uses for float-only batches without missing symbols
+            emu::launch(grid, kTeam, sizeof(EncSmem<2>), [&] {
+                rans_encode_kernel<false, false>(descs, enc.data(), scr, hd, ls, order.data() + a, &tickets[g], (uint32_t)m);
+            });
+        else
+            emu::launch(grid, kTeam, sizeof(EncSmem<4>), [&] {
+                rans_encode_kernel<true, true>(descs, enc.data(), scr, hd, ls, order.data() + a, &tickets[g], (uint32_t)m);
+            });
+        emu::launch(grid, 256, 0, [&] { lane_scan_kernel(descs, hd, psize.data() + a, lo, (uint32_t)m); });
+        emu::launch(1, 1024, 0, [&] {
+            tensor_scan_kernel(descs, psize.data() + a, poff.data() + a, (uint32_t)m, a ? poff.data() + a : nullptr);
         });
-    else
-        emu::launch(grid, kTeam, sizeof(EncSmem<4>), [&] {
-            rans_encode_kernel<true, true>(b.descs.data(), enc.data(), scr, hdrs.data(), lsrc.data(), order.data(),
-                                           &ticket, (uint32_t)n);
-        });
-    emu::launch(grid, 256, 0, [&] { lane_scan_kernel(b.descs.data(), hdrs.data(), psize.data(), loff.data(), (uint32_t)n); });
-    emu::launch(1, 1024, 0, [&] { tensor_scan_kernel(b.descs.data(), psize.data(), poff.data(), (uint32_t)n, nullptr); });
-    emu::launch(grid, 256, 0, [&] {
-        compact_kernel(b.descs.data(), hdrs.data(), lsrc.data(), loff.data(), scr, payload_out, (uint32_t)n);
-    });
+        emu::launch(grid, 256, 0, [&] { compact_kernel(descs, hd, ls, lo, scr, payload_out, (uint32_t)m); });
+    }
     for (size_t i = 0; i <= n; ++i) payload_off_out[i] = poff[i];
     std::memcpy(hdrs_out, hdrs.data(), n * 4096);
     for (size_t i = 0; i < n; ++i) raw_out[i] = (b.descs[i].flags & kFlagRaw) ? 1 : 0;

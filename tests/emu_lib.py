@@ -83,7 +83,7 @@ class Emu:
                                 None if nh is None else _p(nh), _p(side), _p(hist, u32p), C.c_uint32(grid))
         return side, hist
 
-    def encode(self, tensors, es, spe, table_idx, nf, cf, grid=3, float_only=False):
+    def encode(self, tensors, es, spe, table_idx, nf, cf, grid=3, float_only=False, segments=1):
         n, ptrs = self._arrays(tensors)
         nb = np.array([t.size for t in tensors], np.uint64)
         es_a, spe_a = np.array(es, np.uint32), np.array(spe, np.uint32)
@@ -96,7 +96,7 @@ class Emu:
         raw = np.zeros(n, np.uint8)
         st = self.lib.emu_encode(C.c_size_t(n), ptrs, _p(nb, u64p), _p(es_a, u32p), _p(spe_a, u32p), _p(ti, u32p),
                                  C.c_size_t(nf.shape[0]), _p(nf, u32p), _p(cf, u32p), _p(payload), _p(poff, u64p),
-                                 _p(hdrs, u32p), _p(raw), C.c_uint32(grid), C.c_uint32(int(float_only)))
+                                 _p(hdrs, u32p), _p(raw), C.c_uint32(grid), C.c_uint32(int(float_only)), C.c_uint32(segments))
         return payload, poff, hdrs, raw, st
 
     def decode(self, n_bytes, es, spe, table_idx, nf, cf, hdrs, payload, poff, raw, sidecar, check_zero=0, grid=3,

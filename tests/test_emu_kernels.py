@@ -47,6 +47,12 @@ def test_split_hist_encode_decode(emu, oracle, misalign):
         assert bool(raw[i]) == r, i
         assert np.array_equal(got, p), i
         assert np.array_equal(hdrs[i], hd), i
+    # cut into segments that go through their own launches on offset pointers (the compress
+    # pipeline of the library): same payload, offsets and headers whatever the cut
+    for segments in (2, 3, len(tensors)):
+        p2, o2, h2, r2, st2 = emu.encode(tensors, es, spe, list(range(len(tensors))), nf, cf, segments=segments)
+        assert st2 == 0 and np.array_equal(o2, poff) and np.array_equal(h2, hdrs) and np.array_equal(r2, raw)
+        assert np.array_equal(p2[:int(poff[-1])], payload[:int(poff[-1])]), segments
     for dst_mis in (0, 4):
         outs, status = emu.decode([a.size for a in tensors], es, spe, list(range(len(tensors))), nf, cf, hdrs, payload,
                                   poff, raw, side, check_zero=1, dst_misalign=dst_mis)
