@@ -446,7 +446,8 @@ static void compress(Context* c, bool host_images) {
     // ---- stage 1: low bytes out, histograms.  The batch is cut into a few segments; each
     // segment's histograms are copied back as soon as its launch is done, so the host
     // normalises segment g while the device still counts g+1.
-    const size_t n_seg = W >= 64 ? (size_t)c->segments : 1;
+    // a small batch cannot fill the device whichever way it is cut: one segment, fewest launches
+    const size_t n_seg = W >= 512 ? (size_t)c->segments : 1;
     std::vector<size_t> seg_end(n_seg, W);
     {
         unsigned long long acc = 0;

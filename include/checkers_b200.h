@@ -73,7 +73,7 @@ int chk_tensor_count(chk_context* ctx, uint64_t* count);
  * "verify_zero_lanes" (0/1; decode also checks the lanes that only carry
  * zeroed low bytes), "host_threads" (threads for table normalisation, 0 = all),
  * "decode_two_level" (0/1; 5 KiB two-level decode table instead of 16 KiB),
- * "segments" (1..8, default 8: pieces a batch of 64 tensors or more is cut into so
+ * "segments" (1..8, default 3: pieces a batch of 512 tensors or more is cut into so
  * that counting, encoding and compaction of neighbouring pieces overlap on the
  * device; 1 runs the stages one after the other), "encode_teams_per_sm" (default
  * 0 = as many as fit: cap on the resident encode teams per SM of one launch). */
