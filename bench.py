@@ -120,14 +120,25 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True)
             self.thread.start()
         except OSError:
             self.proc = None
 
-    def stop(self):
+    def wait_first(self, timeout=10.0):
+        """Block until the first sample has arrived (nvidia-smi takes a while to start on a box with many GPUs)."""
+        t0 = time.time()
+        while self.proc and not self.lines and time.time() - t0 < timeout:
+            time.sleep(0.02)
+
+    def mark(self):
+        return len(self.lines)
+
+    def stop(self, first=0, last=None):
+        """Summary of the samples with index in [first, last]; when the window was shorter than the
+        sampling interval, the sample before it and the one after it are used."""
         if not self.proc:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         time.sleep(0.15)
@@ -139,7 +150,9 @@ class ClockSampler:
         self.thread.join(timeout=2)
         sm, mx, reasons = [], [], set()
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for ln in self.lines:
+        lo = max(first - 1, 0)
+        hi = len(self.lines) if last is None else min(last + 1, len(self.lines))
+        for ln in self.lines[lo:max(hi, lo + 1)]:
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 7:
                 continue
@@ -194,7 +207,7 @@ def cpu_arm(args, rank, world):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--world-shards", type=int, default=8, help="flat-index shards of the model; one per rank")
@@ -285,9 +298,11 @@ def main():
     except Exception:
         gpu_id = str(local_rank)
     sampler = ClockSampler(gpu_id)
+    sampler.start()
+    sampler.wait_first()
     barrier()
     launches0 = ctx.kernel_launches()
-    sampler.start()
+    mark0 = sampler.mark()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     enc_ms, dec_ms, split_ms, compact_ms, table_ms, cwall_ms, dwall_ms = [], [], [], [], [], [], []
     e0.record(lib_stream)
@@ -302,7 +317,7 @@ def main():
         dwall_ms.append(ctx.timing("decompress_total_ms"))
     e1.record(lib_stream)
     barrier()
-    clocks = sampler.stop()
+    clocks = sampler.stop(mark0, sampler.mark())
     launches = ctx.kernel_launches() - launches0
     elapsed_ms = e0.elapsed_time(e1)
     if world > 1:

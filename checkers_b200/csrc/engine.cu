@@ -332,10 +332,12 @@ static void upload_order(Context* c, size_t W, SizeFn&& size_of) {
     control_zero(c, c->d_ticket.p, 256, c->stream);
 }
 
-static void ensure_events(std::vector<cudaEvent_t>& v, size_t n, bool timing) {
+// blocking: a host thread that waits for the event sleeps instead of spinning on a core
+static void ensure_events(std::vector<cudaEvent_t>& v, size_t n, bool timing, bool blocking = false) {
     while (v.size() < n) {
         cudaEvent_t e = nullptr;
-        CHK_CUDA(cudaEventCreateWithFlags(&e, timing ? cudaEventDefault : cudaEventDisableTiming));
+        CHK_CUDA(cudaEventCreateWithFlags(&e, (timing ? cudaEventDefault : cudaEventDisableTiming) |
+                                                  (blocking ? cudaEventBlockingSync : 0)));
         v.push_back(e);
     }
 }
@@ -460,7 +462,7 @@ static void compress(Context* c, bool host_images) {
             if (acc * 100 >= bytes_total * cut) seg_end[g++] = i + 1;
         }
     }
-    ensure_events(c->seg_events, n_seg, false);
+    ensure_events(c->seg_events, n_seg, false, true);
     ensure_events(c->ev_tab, n_seg, false);
     ensure_events(c->ev_zero, n_seg, false);
     ensure_events(c->ev_enc0, n_seg, true);

@@ -11,6 +11,7 @@
 #include <algorithm>
 #include <cstdint>
 #include <cstring>
+#include <functional>
 #include <vector>
 
 #include "kernels.cuh"
@@ -22,6 +23,15 @@ struct FreqTable {
     uint32_t cum_freq[257];
     uint32_t sum;  // 4096 for a decodable table
 };
+
+// floor(num / den) for num < 2^44, den < 2^40: a double estimate (off by at most one) put right
+// with one multiplication, instead of a 64-bit division per symbol.
+inline uint32_t floor_div(uint64_t num, uint64_t den, double inv_den) {
+    uint64_t q = (uint64_t)((double)num * inv_den);
+    if (q * den > num) --q;
+    else if ((q + 1) * den <= num) ++q;
+    return (uint32_t)q;
+}
 
 // `repair` = false is the reference behaviour (a single decrement pass when the
 // minimum-one-slot rule over-assigns, which can leave the sum above 4096 for
@@ -44,9 +54,10 @@ inline void normalize_histogram(const uint32_t hist[256], bool ensure_full_alpha
     }
     uint32_t slots[256] = {};
     uint32_t assigned = 0;
+    const double inv_total = total ? 1.0 / (double)total : 0.0;
     for (int s = 0; s < 256; ++s) {
         if (!ensure_full_alphabet && hist[s] == 0) continue;
-        uint32_t v = total ? (uint32_t)((uint64_t)std::max(hist[s], 1u) * kM / total) : 0u;
+        uint32_t v = total ? floor_div((uint64_t)std::max(hist[s], 1u) * kM, total, inv_total) : 0u;
         slots[s] = v ? v : 1u;
         assigned += slots[s];
     }
@@ -61,12 +72,33 @@ inline void normalize_histogram(const uint32_t hist[256], bool ensure_full_alpha
         const double exact = total ? ((double)std::max(hist[s], 1u) * kM / (double)total) : 1.0;
         keys[n_keys++] = {s, exact - (double)(int)exact};
     }
-    if (assigned != kM)  // the order is only consulted when slots have to be handed out or taken back
-        std::sort(keys, keys + n_keys, [](const Key& a, const Key& b) { return a.frac > b.frac; });
+    // The order is only consulted when slots have to be handed out or taken back, and when they
+    // are handed out only the SET of the first `rem` keys matters.  That set is the same for
+    // every correct sort unless equal fractions straddle position `rem`; so it is found by
+    // selection (about a fifth of the sort's cost), and the sort itself -- whose tie order is
+    // part of the format -- only runs when the straddling case occurs.
+    auto by_frac = [](const Key& a, const Key& b) { return a.frac > b.frac; };
     if (assigned < kM) {
         uint32_t rem = kM - assigned;
-        for (size_t k = 0; k < n_keys && rem; ++k, --rem) slots[keys[k].sym]++;
+        if (rem >= n_keys) {
+            for (size_t k = 0; k < n_keys; ++k) slots[keys[k].sym]++;
+        } else {
+            double fr[256];
+            for (size_t k = 0; k < n_keys; ++k) fr[k] = keys[k].frac;
+            std::nth_element(fr, fr + (rem - 1), fr + n_keys, std::greater<double>());
+            const double t = fr[rem - 1];  // the rem-th largest fraction
+            size_t n_ge = 0;
+            for (size_t k = 0; k < n_keys; ++k) n_ge += keys[k].frac >= t;
+            if (n_ge == rem) {
+                for (size_t k = 0; k < n_keys; ++k)
+                    if (keys[k].frac >= t) slots[keys[k].sym]++;
+            } else {
+                std::sort(keys, keys + n_keys, by_frac);
+                for (size_t k = 0; k < n_keys && rem; ++k, --rem) slots[keys[k].sym]++;
+            }
+        }
     } else if (assigned > kM) {
+        std::sort(keys, keys + n_keys, by_frac);
         uint32_t rem = assigned - kM;
         for (;;) {
             const uint32_t before = rem;
