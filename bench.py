@@ -275,9 +275,10 @@ def main():
     def step():
         ctx.compress(host_images=False)
         s = ctx.summary()
-        if world > 1:
-            manifest.gather_summaries(s, device=device)
+        pending = manifest.start_gather(s, device=device) if world > 1 else None   # sizes of all ranks for the manifest
         ctx.decompress_resident(dst)
+        if pending is not None:
+            pending.result()
         return s
 
     def barrier():

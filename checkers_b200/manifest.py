@@ -37,6 +37,35 @@ def gather_summaries(summary, group=None, device=None):
     return [dict(zip(FIELDS, r)) for r in rows]
 
 
+class PendingGather:
+    """An all-gather of summaries that runs in the background (start_gather); result() waits for it."""
+
+    def __init__(self, rows=None, work=None, out=None, world=1):
+        self._rows, self._work, self._out, self._world = rows, work, out, world
+
+    def result(self):
+        if self._rows is None:
+            self._work.wait()
+            self._rows = self._out.view(self._world, len(FIELDS)).cpu().tolist()
+        return [dict(zip(FIELDS, r)) for r in self._rows]
+
+
+def start_gather(summary, group=None, device=None):
+    """gather_summaries without waiting: the collective is queued (NCCL: asynchronously, on the
+    process group's own stream) and the caller goes on, e.g. restores or writes its files, before
+    it asks for result().  A rank is then not held up by the others between the two calls."""
+    import torch
+    import torch.distributed as dist
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_backend(group) != "nccl":
+        return PendingGather(rows=[[int(s[k]) for k in FIELDS] for s in gather_summaries(summary, group, device)])
+    world = dist.get_world_size(group)
+    dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+    mine = torch.tensor([int(summary[k]) for k in FIELDS], dtype=torch.int64, device=dev)
+    out = torch.empty(world * len(FIELDS), dtype=torch.int64, device=dev)
+    work = dist.all_gather_into_tensor(out, mine, group=group, async_op=True)
+    return PendingGather(work=work, out=out, world=world)
+
+
 def build_manifest(summaries):
     """Per-rank sizes plus exclusive running offsets, and the totals."""
     ranks, run = [], {k: 0 for k in FIELDS}

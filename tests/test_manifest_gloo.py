@@ -29,6 +29,7 @@ WORKER = textwrap.dedent("""
                    original_bytes=sum(a.size for a in arrays))
     rows = manifest.gather_summaries(summary)
     assert len(rows) == world and rows[rank] == summary
+    assert manifest.start_gather(summary).result() == rows   # the non-blocking form gives the same rows
     if rank == 0:
         manifest.write_manifest(out, manifest.build_manifest(rows))
     dist.barrier()
