@@ -387,3 +387,77 @@ def test_segmented_pipeline_matches_oracle(chk, oracle, tmp_path):
         for o, h, n in zip(outs, host, names):
             assert np.array_equal(o[:h.view(np.uint8).size].cpu().numpy(), h.view(np.uint8).reshape(-1)), n
         ctx.close()
+
+
+def test_codec_microbenchmark_config_full_size(chk, oracle, tmp_path):
+    """The codec microbenchmark configuration at its full size -- a 1 GiB fp32 tensor ~ N(0, 1e-3) and a 1 GiB
+    bf16 tensor ~ N(0, 0.02), seed 1, in 4 MiB chunks -- checked through size-independent properties: the
+    full pipeline round-trips losslessly, split-only recombines to the source, entropy-coding-only (the same
+    bytes registered as int8, no low-byte split) round-trips, and sampled chunks equal the oracle's files."""
+    g = torch.Generator(device="cuda").manual_seed(1)
+    x32 = torch.randn(256 << 20, generator=g, device="cuda", dtype=torch.float32) * 1e-3
+    xbf = (torch.randn(512 << 20, generator=g, device="cuda", dtype=torch.float32) * 0.02).to(torch.bfloat16)
+    o32, obf = torch.zeros_like(x32), torch.zeros_like(xbf)
+    torch.cuda.synchronize()
+    chunk = 4 << 20
+    ctx = chk.Context(device=0)
+    dst = []
+    for k in range(256):
+        ctx.register_pointer(f"fp32.{k}", x32.data_ptr() + k * chunk, chunk // 4, F32)
+        dst.append(o32.data_ptr() + k * chunk)
+    for k in range(256):
+        ctx.register_pointer(f"bf16.{k}", xbf.data_ptr() + k * chunk, chunk // 2, BF16)
+        dst.append(obf.data_ptr() + k * chunk)
+    ctx.compress()
+    s = ctx.summary()
+    assert s["n_tensors"] == 512 and s["original_bytes"] == 2 << 30
+    compressed = s["states_bytes"] + s["mantissa_bytes"] + s["dict_bytes"]
+    assert compressed < s["original_bytes"]                      # Gaussian data: the exponent bytes compress
+    assert ctx.decompress_resident(dst) == 512
+    torch.cuda.synchronize()
+    assert torch.equal(x32.view(torch.uint8), o32.view(torch.uint8))
+    assert torch.equal(xbf.view(torch.uint8), obf.view(torch.uint8))
+    ctx.close()
+
+    # split only: masked | low bytes is the source again
+    for t, dt, es in ((x32, F32, 4), (xbf, BF16, 2)):
+        n = chunk // es
+        masked = torch.zeros(chunk, dtype=torch.uint8, device="cuda")
+        side = torch.zeros(chunk // 2, dtype=torch.uint8, device="cuda")
+        c2 = chk.Context(device=0)
+        c2.split(t.data_ptr() + 3 * chunk, n, dt, masked.data_ptr(), side.data_ptr())
+        torch.cuda.synchronize()
+        src = t.view(torch.uint8)[3 * chunk:4 * chunk].view(n, es)
+        m, sd = masked.view(n, es), side.view(n, es // 2)
+        assert torch.equal(m[:, es // 2:], src[:, es // 2:]) and int(m[:, :es // 2].max()) == 0
+        assert torch.equal(sd, src[:, :es // 2])
+        c2.close()
+
+    # entropy coding only: the fp32 bytes as int8 tensors (no split), first 64 MiB
+    c3 = chk.Context(device=0)
+    o8 = torch.zeros(64 << 20, dtype=torch.uint8, device="cuda")
+    for k in range(16):
+        c3.register_pointer(f"bytes.{k}", x32.data_ptr() + k * chunk, chunk, I8)
+    c3.compress()
+    assert c3.decompress_resident([o8.data_ptr() + k * chunk for k in range(16)]) == 16
+    torch.cuda.synchronize()
+    assert torch.equal(o8, x32.view(torch.uint8)[:64 << 20])
+    c3.close()
+
+    # sampled chunks against the oracle, file for file
+    names, host, dev, dtypes = [], [], [], []
+    for t, dt, tag in ((x32, F32, "fp32"), (xbf, BF16, "bf16")):
+        for k in (0, 255):
+            piece = t.view(torch.uint8)[k * chunk:(k + 1) * chunk]
+            names.append(f"{tag}.{k}")
+            host.append(piece.cpu().numpy().copy())
+            dev.append(piece)
+            dtypes.append(dt)
+    c4 = chk.Context(device=0)
+    register_all(c4, names, dev, dtypes)
+    out_gpu, out_cpu = str(tmp_path / "gpu"), str(tmp_path / "cpu")
+    c4.compress_and_save(out_gpu)
+    oracle.compress_and_save(names, host, dtypes, out_cpu)
+    for a, b, what in zip(read_files(out_gpu), read_files(out_cpu), ("states", "mantissa", "tables")):
+        assert a == b, f"{what} file differs from the oracle's"
+    c4.close()

@@ -147,3 +147,38 @@ def test_golden_reports_match_reference_cli(tmp_path):
                 os.makedirs(os.path.dirname(gold), exist_ok=True)
                 shutil.copy(os.path.join(d, "prefix_mask_repair", r), gold)
             assert strip_times(os.path.join(d, "prefix_mask_repair", r)) == strip_times(gold), (tag, r)
+
+
+@pytest.mark.gpu
+def test_cli_large_group_matches_reference(tmp_path):
+    """A group at the upper end of the restore configuration's range (2^22 elements) next to a small one."""
+    torch = pytest.importorskip("torch")
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    if not os.path.exists(REF_REPAIR_CLI):
+        pytest.skip("oracle/_ref not built: no reference output for this size")
+    from checkers_b200 import repair
+
+    def export(root):
+        os.makedirs(os.path.join(root, "analysis", "plots"), exist_ok=True)
+        os.makedirs(os.path.join(root, "tensors"), exist_ok=True)
+        manifest = ["tensor_key,layer,category,state_type,numel,dtype,file"]
+        for layer, (n, kind, dtype) in enumerate([(1 << 22, "f32_master", "float32"), (1 << 16, "f32_master", "float32")]):
+            raw, _ = synth(kind, n, 900 + layer)
+            rel = f"tensors/master_mlp.up_{layer}.bin"
+            raw.tofile(os.path.join(root, rel))
+            manifest.append(f"master.mlp.up.{layer},{layer},mlp.up,master,{n},{dtype},{rel}")
+        groups = ["state_type,category,group_id,n_layers,layers,representative_layer,c6,c7,c8,c9",
+                  'master,mlp.up,0,2,"0 1",0,0,0,0,0']
+        open(os.path.join(root, "manifest.csv"), "w").write("\n".join(manifest) + "\n")
+        open(os.path.join(root, "analysis", "plots", "grouping_summary.csv"), "w").write("\n".join(groups) + "\n")
+
+    extra = ["--max-rules", "6"]
+    ours, theirs = str(tmp_path / "ours"), str(tmp_path / "theirs")
+    export(ours)
+    export(theirs)
+    assert repair.main([ours] + extra) == 0
+    subprocess.check_call([REF_REPAIR_CLI, theirs] + extra, stdout=subprocess.DEVNULL)
+    for r in REPORTS:
+        assert strip_times(os.path.join(ours, "prefix_mask_repair", r)) == \
+            strip_times(os.path.join(theirs, "prefix_mask_repair", r)), r
