@@ -597,6 +597,10 @@ static void compress(Context* c, bool host_images) {
                 c->launches++;
             }
             CHK_CUDA(cudaEventRecord(c->ev_tab[g], sB));
+            // a member of a cluster borrows the table of an anchor that may sit in an earlier
+            // segment, whose tables were built on another stream
+            for (size_t p = 0; p < g; ++p)
+                if (launched[p]) CHK_CUDA(cudaStreamWaitEvent(sB, c->ev_tab[p], 0));
             // the shared symbol-0 chain of every tensor (one thread each) runs next to the value lanes
             CHK_CUDA(cudaStreamWaitEvent(sZ, c->ev_tab[g], 0));
             zero_lane_kernel<<<(uint32_t)((n + 127) / 128), 128, 0, sZ>>>(descs_g, enc, static_cast<uint8_t*>(c->d_scratch.p),

@@ -461,3 +461,34 @@ def test_codec_microbenchmark_config_full_size(chk, oracle, tmp_path):
     for a, b, what in zip(read_files(out_gpu), read_files(out_cpu), ("states", "mantissa", "tables")):
         assert a == b, f"{what} file differs from the oracle's"
     c4.close()
+
+
+def test_segmented_pipeline_with_shared_tables(chk, oracle, tmp_path):
+    """Cluster members borrow their anchor's table across pipeline segments (the anchor's table is built
+    on another stream, segments earlier): files equal the oracle's and restore, for 1 and 4 segments."""
+    names, host, dtypes = make_state(n_layers=140, n=3000, seed=21)   # 560 tensors
+    dev = [dev_bytes(h) for h in host]
+    cid, anchors = _cluster_setup(oracle, names, host, dtypes)
+    assert len(anchors) >= 1
+    out_cpu = str(tmp_path / "cpu")
+    oracle.compress_and_save(names, host, dtypes, out_cpu, cluster_id=cid, anchor_names=anchors, repair_tables=True)
+    ref = read_files(out_cpu)
+    for segments in (4, 1):
+        ctx = chk.Context(device=0)
+        register_all(ctx, names, dev, dtypes)
+        ctx.set_cluster_info(names, cid, anchors)
+        ctx.set_option("repair_tables", 1)
+        ctx.set_option("segments", segments)
+        out_gpu = str(tmp_path / f"gpu{segments}")
+        ctx.compress_and_save(out_gpu)
+        for a, b, what in zip(read_files(out_gpu), ref, ("states", "mantissa", "tables")):
+            assert a == b, f"{segments} segments: {what} file differs from the oracle's"
+        ctx.close()
+    outs = [torch.zeros(h.size, dtype=torch.uint8, device="cuda") for h in host]
+    ctx2 = chk.Context(device=0)
+    for n, o, h, dt in zip(names, outs, host, dtypes):
+        ctx2.register_pointer(n, o.data_ptr(), h.size // ELEM_SIZE[dt], dt)
+    assert ctx2.load_and_decompress(out_gpu) == len(names)
+    for o, h, n in zip(outs, host, names):
+        assert np.array_equal(o.cpu().numpy(), h), n
+    ctx2.close()
