@@ -516,14 +516,17 @@ __global__ void __launch_bounds__(256) compact_kernel(const TensorDesc* __restri
 //   two levels: slot -> symbol (1 byte), symbol -> freq[0:16) | cum[16:32)              5 KiB per tensor
 // The second costs one more dependent shared-memory load per symbol but lets about
 // twice as many teams be resident on an SM.
-constexpr uint32_t kRingWords = 20;
+constexpr uint32_t kRingWords = 17;
 template <int NV, bool TL>
 struct DecSmem {
     uint32_t dtab[TL ? 256 : kM];  // two levels: freq | cum<<16 per symbol
     uint8_t slot_sym[TL ? kM : 4];
-    // 64-byte input ring per chain plus one word whose first byte mirrors ring byte 0
-    // (so byte p+1 is always at address p+1); 80 bytes apart keeps 16-byte stores aligned
-    alignas(16) uint32_t ring[NV * kTeam * kRingWords];
+    // 64-byte input ring per chain (two 32-byte blocks) plus a 17th word that repeats word 0,
+    // so the word after any ring word is the next one without a wrap.  The rings of a warp are
+    // interleaved word by word (word w of lane l at [w * 32 + l]): every lane stays in its own
+    // shared-memory bank wherever its read position is, so neither the reads (each lane at a
+    // different, data-dependent position) nor the block stores ever conflict.
+    uint32_t ring[NV * kTeam * kRingWords];
     uint32_t cum[260];
 };
 // shared memory per team: [chains per thread: 2 = float tensors only, 4 = integers present][table shape]
@@ -571,12 +574,19 @@ __device__ __forceinline__ void dec_request(DecChain& c, const uint8_t* __restri
     }
     ++c.loaded;
 }
+// ring_words: this lane's ring word 0; its word w is at ring_words[w * 32]
 __device__ __forceinline__ void dec_commit(DecChain& c, uint32_t* ring_words) {
     if (c.has_pend) {
         const uint32_t r = ((c.loaded - 1) & 1) * 8;
-        *reinterpret_cast<uint4*>(ring_words + r) = c.pend0;
-        *reinterpret_cast<uint4*>(ring_words + r + 4) = c.pend1;
-        if (r == 0) ring_words[16] = c.pend0.x;  // mirror of byte 0 behind byte 63
+        ring_words[(r + 0) * 32] = c.pend0.x;
+        ring_words[(r + 1) * 32] = c.pend0.y;
+        ring_words[(r + 2) * 32] = c.pend0.z;
+        ring_words[(r + 3) * 32] = c.pend0.w;
+        ring_words[(r + 4) * 32] = c.pend1.x;
+        ring_words[(r + 5) * 32] = c.pend1.y;
+        ring_words[(r + 6) * 32] = c.pend1.z;
+        ring_words[(r + 7) * 32] = c.pend1.w;
+        if (r == 0) ring_words[16 * 32] = c.pend0.x;  // word 0 again behind word 15
         c.has_pend = false;
     }
 }
@@ -606,8 +616,11 @@ __device__ __forceinline__ uint32_t dec_step(DecChain& c, const uint32_t* dtab, 
         sym = e;
         x = ((e >> 8) & 0xFFFu) * xs + xs + (e >> 20);
     }
-    const uint8_t* rp = ring_bytes + (c.rel & 63);
-    const uint32_t top = __byte_perm(rp[0], rp[1], 0x0411);  // rp[0] to bits 31..24, rp[1] to bits 23..16
+    // the two stream bytes at the read position: the ring word that holds the first one and its
+    // successor (two conflict-free loads), shifted down by the position inside the word
+    const uint32_t* rw = reinterpret_cast<const uint32_t*>(ring_bytes + ((c.rel << 5) & 0x780u));  // word (rel >> 2) & 15
+    const uint32_t pair = __funnelshift_r(rw[0], rw[32], c.rel << 3);  // shift count is taken mod 32: 8 * (rel & 3)
+    const uint32_t top = __byte_perm(pair, 0u, 0x0144);  // first byte to bits 31..24, second to bits 23..16
     // bytes to pull in: 0 for x >= 2^23, 1 for x >= 2^15, else 2 (a valid state is never below 2^11)
     const uint32_t t = (uint32_t)__clz((int)x) - 1u;
     c.x = __funnelshift_l(top, x, t & 24u);
@@ -661,7 +674,7 @@ __device__ __forceinline__ void decode_tensor(const TensorDesc& d, uint32_t ti,
         ch[k].max_blocks = ((ch[k].rel_end + 31) >> 5) + 1;
         ch[k].loaded = 0;
         ch[k].has_pend = false;
-        ringw[k] = sm->ring + (size_t)(k * kTeam + j) * kRingWords;
+        ringw[k] = sm->ring + (size_t)(k * (kTeam / 32) + (j >> 5)) * (kRingWords * 32) + (j & 31);
         ringb[k] = reinterpret_cast<const uint8_t*>(ringw[k]);
         if (B > t) {  // the lane has symbols: start with both blocks of the ring filled
 #pragma unroll
