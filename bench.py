@@ -17,6 +17,12 @@ A step = compress the shard (low-byte split + histograms, tables, 256-lane rANS
 encode, compaction into the file layout) and restore it (decode + merge) with
 all data resident in HBM.  value = shard bytes / step time, summed over ranks,
 timed with CUDA events on the library's stream, max over ranks.
+
+e2e = the same work for a slice of the shard that starts and ends in pinned host
+memory, through checkers_b200.streaming.ChunkedHostPipeline: every input byte is
+copied host->device, the three file images of every chunk device->host, then the
+images host->device and the restored tensors device->host, all inside the timed
+region (wall clock between device synchronisations, max over ranks).
 """
 import argparse
 import json
