@@ -76,7 +76,10 @@ int chk_tensor_count(chk_context* ctx, uint64_t* count);
  * "segments" (1..8, default 3: pieces a batch of 512 tensors or more is cut into so
  * that counting, encoding and compaction of neighbouring pieces overlap on the
  * device; 1 runs the stages one after the other), "encode_teams_per_sm" (default
- * 0 = as many as fit: cap on the resident encode teams per SM of one launch). */
+ * 0 = as many as fit: cap on the resident encode teams per SM of one launch),
+ * "first_segment_pct" (0..90, default 0 = equal shares: size of the first piece),
+ * "encode_after_count" (0/1: encode grids start only once the whole batch has been
+ * counted).  None of the tuning options changes the bytes that are produced. */
 int chk_set_option(chk_context* ctx, const char* key, int64_t value);
 
 /* ---- analysis: checkers::analyze_tensors, src/api.cpp:1033-1253 ----------

@@ -26,7 +26,7 @@ WORKER = textwrap.dedent("""
     summary = dict(n_tensors=3, n_tables=3, states_bytes=size(f"rank_{{rank}}_states.ansc"),
                    mantissa_bytes=size(f"mantissa/rank_{{rank}}_mantissa.mant"),
                    dict_bytes=size(f"tables/rank_{{rank}}_tables.dict"),
-                   original_bytes=sum(a.size for a in arrays))
+                   original_bytes=sum(a.size for a in arrays), digests=manifest.file_digests(out, rank))
     rows = manifest.gather_summaries(summary)
     assert len(rows) == world and rows[rank] == summary
     assert manifest.start_gather(summary).result() == rows   # the non-blocking form gives the same rows
@@ -55,6 +55,16 @@ def test_two_ranks_write_one_manifest(tmp_path):
         for key, rel in r["files"].items():
             assert os.path.getsize(os.path.join(out, rel)) == r[{"states": "states_bytes", "mantissa": "mantissa_bytes",
                                                                   "tables": "dict_bytes"}[key]]
+    from checkers_b200 import manifest
+    assert manifest.verify_manifest(out) == []
+    assert all(len(r["sha256"][k]) == 64 for r in (r0, r1) for k in ("states", "mantissa", "tables"))
+    victim = os.path.join(out, r1["files"]["mantissa"])
+    blob = bytearray(open(victim, "rb").read())
+    blob[len(blob) // 2] ^= 1
+    open(victim, "wb").write(bytes(blob))
+    problems = manifest.verify_manifest(out)
+    assert len(problems) == 1 and "rank 1" in problems[0] and "SHA-256" in problems[0]
+    assert manifest.verify_manifest(out, ranks=[0]) == []
     t = m["totals"]
     assert t["original_bytes"] == r0["original_bytes"] + r1["original_bytes"]
     assert t["compressed_bytes"] == sum(r[k] for r in (r0, r1) for k in ("states_bytes", "mantissa_bytes", "dict_bytes"))
