@@ -260,9 +260,7 @@ def main():
     tags = (chk.BF16, chk.F32, chk.F32, chk.F32)
 
     ctx = chk.Context(device=local_rank, rank=rank, local_rank=local_rank)
-    # table normalisation runs on host threads: share the cores between the ranks of this node
     local_world = int(os.environ.get("LOCAL_WORLD_SIZE", str(world)))
-    ctx.set_option("host_threads", max(2, (os.cpu_count() or 2) // max(local_world, 1)))
     for kv in args.opt:
         k, v = kv.split("=")
         ctx.set_option(k, int(v))
@@ -349,8 +347,6 @@ def main():
             h_targets.append(ho[off:off + n])
     pipe = ChunkedHostPipeline(h_tensors, device=local_rank, rank=rank, chunk_bytes=args.e2e_chunk_bytes,
                                workers=args.e2e_workers)
-    for ch in pipe.chunks:
-        ch.ctx.set_option("host_threads", max(2, (os.cpu_count() or 2) // max(args.e2e_workers * local_world, 1)))
     e_bytes = sum(h.numel() * h.element_size() for h in h_in)
     img_bytes = 0
 

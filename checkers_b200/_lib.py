@@ -33,6 +33,7 @@ def _load():
     sig = {
         "chk_last_error": (C.c_char_p, []),
         "chk_context_create": (C.c_int, [C.c_int, C.c_int, C.c_int, C.POINTER(vp)]),
+        "chk_context_create_ex": (C.c_int, [C.c_int, C.c_int, C.c_int, u64, C.POINTER(vp)]),
         "chk_context_destroy": (C.c_int, [vp]),
         "chk_reset": (C.c_int, [vp]),
         "chk_set_histogram_bins": (C.c_int, [vp, C.c_uint32]),
@@ -49,6 +50,7 @@ def _load():
         "chk_compress": (C.c_int, [vp, C.c_int]),
         "chk_get_image": (C.c_int, [vp, C.c_int, C.POINTER(vp), C.POINTER(u64)]),
         "chk_get_summary": (C.c_int, [vp, C.POINTER(Summary)]),
+        "chk_get_table_report": (C.c_int, [vp, C.POINTER(u64), C.POINTER(u64)]),
         "chk_load_and_decompress": (C.c_int, [vp, C.c_char_p]),
         "chk_decompress_images": (C.c_int, [vp, vp, u64, vp, u64, vp, u64]),
         "chk_decompress_resident": (C.c_int, [vp, C.POINTER(vp)]),

@@ -43,10 +43,46 @@ def current_context():
     return _ctx
 
 
+def _master_of(optimizer):
+    """Map id(model parameter) -> fp32 master tensor for the usual mixed-precision wrappers.
+
+    The reference reads DeepSpeed ZeRO-3's flat fp32 partitions (src/api.cpp:416-685, submitted as
+    'master_weights::<p>', :614-625).  Without DeepSpeed the same state sits in one of a few shapes:
+    a `master_params` / `master_weights` dict keyed by parameter, parallel lists of low-precision and
+    fp32 parameter groups (apex FP16_Optimizer: fp16_groups + fp32_from_fp16_groups; Megatron:
+    float16_groups + fp32_from_float16_groups; DeepSpeed stages 1-2: bit16_groups +
+    single_partition_of_fp32_groups is flat and is NOT handled here), or a `main_param` attribute on
+    the parameter itself."""
+    out = {}
+    for holder in (optimizer, getattr(optimizer, "optimizer", None)):
+        if holder is None:
+            continue
+        for attr in ("master_params", "master_weights"):
+            d = getattr(holder, attr, None)
+            if isinstance(d, dict):
+                for k, v in d.items():
+                    out[id(k)] = v
+        for lo, hi in (("fp16_groups", "fp32_from_fp16_groups"), ("float16_groups", "fp32_from_float16_groups"),
+                       ("bit16_groups", "fp32_groups")):
+            g_lo, g_hi = getattr(holder, lo, None), getattr(holder, hi, None)
+            if g_lo is None or g_hi is None:
+                continue
+            for grp_lo, grp_hi in zip(g_lo, g_hi):
+                for p_lo, p_hi in zip(grp_lo, grp_hi):
+                    out[id(p_lo)] = p_hi
+    return out
+
+
 def _named_state_tensors(model_engine, optimizer):
-    """(name, tensor) pairs in the reference's naming scheme for a plain module +
-    Adam-style optimizer: '<p>', 'optimizer.exp_avg::<p>', 'optimizer.exp_avg_sq::<p>'
-    (src/api.cpp:583-653 uses the same prefixes for ZeRO-3 flat slices)."""
+    """(name, tensor) pairs in the reference's naming scheme and per-parameter order
+    (src/api.cpp:583-653): '<p>', 'master_weights::<p>', 'optimizer.exp_avg::<p>',
+    'optimizer.exp_avg_sq::<p>', for a plain module (or an engine with .module) and an
+    Adam-style optimizer, with or without fp32 master copies.
+
+    Every parameter the module holds on this rank is tracked.  (The reference's ZeRO-3 walk keeps
+    only the parameters whose index falls into the rank's "territory", :543-573, although every
+    rank holds a slice of every parameter -- so most of each rank's state is never saved.  There
+    is no such filter here: what is local is registered.)"""
     if isinstance(model_engine, dict):
         return list(model_engine.items())
     if isinstance(model_engine, (list, tuple)):
@@ -57,9 +93,21 @@ def _named_state_tensors(model_engine, optimizer):
     opt = optimizer if optimizer is not None else getattr(model_engine, "optimizer", None)
     base = getattr(opt, "optimizer", opt)
     state = getattr(base, "state", None) or {}
+    masters = _master_of(opt) if opt is not None else {}
     for name, p in params:
         out.append((name, p.data))
-        st = state.get(p, None)
+        master = masters.get(id(p), getattr(p, "main_param", None))
+        if master is not None:
+            out.append((f"master_weights::{name}", master.data if hasattr(master, "data") else master))
+        st = None
+        for key in (master, p):  # Adam state is keyed by whichever tensor the optimizer steps
+            if key is not None:
+                try:
+                    st = state.get(key, None)
+                except TypeError:
+                    st = None
+                if st:
+                    break
         if st:
             if "exp_avg" in st:
                 out.append((f"optimizer.exp_avg::{name}", st["exp_avg"]))
@@ -68,20 +116,57 @@ def _named_state_tensors(model_engine, optimizer):
     return out
 
 
-def initialize_context(model_engine, optimizer=None, histogram_bins=256, background_threads=1):
+_log_file = None
+
+
+def _log(line):
+    """One line of the per-rank log, in the reference's place and spelling:
+    ./logs/<run id>/rank_<r>/checkers.log (src/logging.cpp:105-160), '[TIMING] key=value'
+    (src/api.cpp:1017-1020, 1240-1246, 1293; src/ANSCompressor.cpp:1397-1399)."""
+    global _log_file
+    if os.environ.get("CHECKERS_LOG", "1") == "0" or _ctx is None:
+        return
+    try:
+        if _log_file is None:
+            run_id = os.environ.get("CHECKERS_LOG_RUN_ID") or f"run_{os.getpid()}"
+            d = os.path.join(os.environ.get("CHECKERS_LOG_DIR", "logs"), run_id, f"rank_{max(_ctx.rank, 0)}")
+            os.makedirs(d, exist_ok=True)
+            _log_file = open(os.path.join(d, "checkers.log"), "a", buffering=1)
+        _log_file.write(line + "\n")
+    except OSError:
+        pass  # logging never fails a checkpoint
+
+
+def _timing(key, ms):
+    _log(f"[TIMING] {key}={ms:.6f}")
+
+
+def initialize_context(model_engine, optimizer=None, histogram_bins=256, background_threads=1, *,
+                       shared_tables="reference"):
     """Registers the rank's tensors.  `model_engine` may be an engine/module with
     named_parameters(), or a dict / list of (name, CUDA tensor) pairs.
     `background_threads` is accepted for signature compatibility; registration
-    here is a metadata push and needs no worker threads."""
-    global _ctx, _initialized
+    here is a metadata push and needs no worker threads.
+
+    shared_tables (an addition): what to do when analyze_tensors() has grouped tensors into clusters
+    whose shared table the reference's normalisation leaves undecodable (every bf16 cluster):
+    "reference" refuses to write such files (compress_and_save raises), "reference_bytes" writes the
+    reference's exact, unrestorable bytes, "repair" renormalises shared tables so they decode."""
+    global _ctx, _initialized, _log_file
+    import time
+    t0 = time.perf_counter()
     try:
         if histogram_bins == 0:
             raise RuntimeError("histogram_bins must be greater than zero")
         if background_threads == 0:
             raise RuntimeError("background_threads must be greater than zero")
+        if shared_tables not in ("reference", "reference_bytes", "repair"):
+            raise RuntimeError("shared_tables must be 'reference', 'reference_bytes' or 'repair'")
         rank = _env_rank(model_engine, "global_rank", "RANK")
         local_rank = _env_rank(model_engine, "local_rank", "LOCAL_RANK")
+        t1 = time.perf_counter()
         pairs = _named_state_tensors(model_engine, optimizer)
+        t2 = time.perf_counter()
         device = None
         for _, t in pairs:
             if getattr(t, "is_cuda", False):
@@ -92,13 +177,23 @@ def initialize_context(model_engine, optimizer=None, histogram_bins=256, backgro
             device = torch.cuda.current_device()
         if _ctx is not None:
             _ctx.close()
+        if _log_file is not None:
+            _log_file.close()
+            _log_file = None
         _ctx = Context(device=device, rank=rank, local_rank=local_rank)
         _ctx.set_histogram_bins(histogram_bins)
+        _ctx.set_option("repair_tables", int(shared_tables == "repair"))
+        _ctx.set_option("allow_undecodable", int(shared_tables == "reference_bytes"))
         for name, t in pairs:
             if not getattr(t, "is_cuda", False):
                 continue  # no local device storage on this rank
             _ctx.register_tensor(name, t.contiguous() if not t.is_contiguous() else t)
         _initialized = True
+        t3 = time.perf_counter()
+        _timing("setup_ms", (t1 - t0) * 1e3)
+        _timing("discovery_ms", (t2 - t1) * 1e3)
+        _timing("flush_ms", (t3 - t2) * 1e3)
+        _timing("total_ms", (t3 - t0) * 1e3)
     except Exception as e:  # noqa: BLE001 - mirror the reference: report, then re-raise
         _fail("", e)
 
@@ -116,7 +211,12 @@ def analyze_tensors():
             raise RuntimeError("Context not initialized: MemoryManager logger is null.")
         if _ctx.tensor_count() == 0:
             return
+        import time
+        t0 = time.perf_counter()
         _ctx.analyze()
+        _timing("analyze_histograms_ms", _ctx.timing("analyze_stats_ms"))   # statistics, value histograms, fingerprints: one kernel
+        _timing("analyze_knn_clusters_ms", _ctx.timing("analyze_cluster_ms"))
+        _timing("analyze_total_ms", (time.perf_counter() - t0) * 1e3)
     except Exception as e:  # noqa: BLE001
         _fail("", e)
 
@@ -125,7 +225,17 @@ def compress_and_save(output_path):
     try:
         if not _initialized or _ctx is None:
             raise RuntimeError("Context not initialized: call initialize_context first.")
+        import time
+        t0 = time.perf_counter()
         _ctx.compress_and_save(output_path)
+        _timing("compress_and_save_total_ms", _ctx.timing("compress_total_ms") + _ctx.timing("io_ms"))
+        _timing("compress_computation_ms", _ctx.timing("compress_device_ms"))
+        _timing("compress_io_ms", _ctx.timing("io_ms"))
+        _timing("compress_and_save_wall_ms", (time.perf_counter() - t0) * 1e3)
+        s = _ctx.summary()
+        _log(f"[ANS][rank={max(_ctx.rank, 0)}][summary] tensors={s['n_tensors']} tables={s['n_tables']} "
+             f"original_bytes={s['original_bytes']} ans_bytes={s['states_bytes']} sidecar_bytes={s['mantissa_bytes']} "
+             f"disk_ratio={s['original_bytes'] / max(s['states_bytes'] + s['mantissa_bytes'] + s['dict_bytes'], 1):.6f}")
     except Exception as e:  # noqa: BLE001
         _fail("compress_and_save: ", e)
 

@@ -36,10 +36,11 @@ class Context:
     """One rank's registry + compressor.  Tensors are borrowed: keep them alive
     and unchanged until the call that uses them returns."""
 
-    def __init__(self, device=0, rank=0, local_rank=None):
+    def __init__(self, device=0, rank=0, local_rank=None, workspace_bytes=0):
+        """workspace_bytes bounds the encode scratch (0 = one slot per encode team the device can hold)."""
         self._h = C.c_void_p()
-        check(lib.chk_context_create(int(device), int(rank), int(rank if local_rank is None else local_rank),
-                                     C.byref(self._h)))
+        check(lib.chk_context_create_ex(int(device), int(rank), int(rank if local_rank is None else local_rank),
+                                        int(workspace_bytes), C.byref(self._h)))
         self.device, self.rank = int(device), int(rank)
         self._keep = []
         self.names = []
@@ -139,6 +140,12 @@ class Context:
         s = _lib.Summary()
         check(lib.chk_get_summary(self._h, C.byref(s)))
         return {k: getattr(s, k) for k, _ in _lib.Summary._fields_}
+
+    def table_report(self):
+        """(tables of the last compression, how many of them do not sum to 4096 and cannot be decoded)."""
+        n, bad = C.c_uint64(), C.c_uint64()
+        check(lib.chk_get_table_report(self._h, C.byref(n), C.byref(bad)))
+        return n.value, bad.value
 
     def load_and_decompress(self, input_dir):
         check(lib.chk_load_and_decompress(self._h, os.fspath(input_dir).encode()))

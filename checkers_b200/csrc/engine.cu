@@ -17,9 +17,7 @@
 // the file images are filled by three large copies.
 #include <cuda_runtime.h>
 
-#include <atomic>
 #include <chrono>
-#include <condition_variable>
 #include <cstdio>
 #include <cstring>
 #include <filesystem>
@@ -30,7 +28,6 @@
 #include <memory>
 #include <mutex>
 #include <string>
-#include <thread>
 #include <unordered_map>
 #include <vector>
 
@@ -119,29 +116,28 @@ struct Context {
     ClusterMap clusters;
     std::vector<StatsOut> stats;
 
-    bool repair_tables = false, verify_zero_lanes = false;
+    bool repair_tables = false, verify_zero_lanes = false, allow_undecodable = false;
     bool decode_two_level = false;
-    int host_threads = 0;
 
     // device buffers (grow-only, from the context's pool)
-    DevBuf d_descs, d_tiles, d_hist, d_sidecar, d_scratch, d_hdrs, d_lsrc, d_order, d_ticket, d_loff, d_psize, d_poff, d_nf16,
+    DevBuf d_descs, d_tiles, d_hist, d_sidecar, d_scratch, d_hdrs, d_order, d_ticket, d_psize, d_zslots, d_zregions, d_zslot_of, d_jobs, d_sums,
         d_payload, d_enc, d_freq, d_cum, d_status, d_stats_desc, d_stats_out;
     cudaStream_t side_stream = nullptr;
-    // compress pipeline: counting (stream), encoding, compaction and the zero-lane chains each have their own stream
-    cudaStream_t enc_streams[8] = {}, cmp_stream = nullptr, zero_streams[4] = {};
-    std::vector<cudaEvent_t> seg_events, ev_tab, ev_zero, ev_enc0, ev_enc1, ev_cmp0, ev_cmp1;
-    int segments = 3;             // launches the batch is cut into (1 = no overlap between stages)
-    int first_segment_pct = 0;    // share of the batch in the first segment (0 = equal shares)
-    int encode_after_count = 0;   // 1: encode grids start only when the whole batch has been counted
+    std::vector<cudaEvent_t> ev_count, ev_tab;
+    int segments = 4;             // launches the counting of a batch is cut into (tables of a piece are built under the next)
+    uint64_t workspace_bytes = 0; // bound on the encode scratch (0 = one slot for every team the device can hold)
     int encode_teams_per_sm = 0;  // cap on resident encode teams per SM and launch (0 = as many as fit)
+    int decode_teams_per_sm = 0;  // same for the decode grid
     int sm_count = 0;
     // pinned host staging
-    PinBuf h_hist, h_hdrs, h_poff, h_descs, h_status, h_enc, h_stats, h_order, h_tiles;
+    PinBuf h_hdrs, h_poff, h_psize, h_descs, h_status, h_jobs, h_sums, h_freq, h_cum, h_stats, h_order, h_tiles;
     PinBuf img[3];  // states, mantissa, tables
 
     // result of the last compression
     std::vector<WorkItem> work;
-    std::vector<FreqTable> tables;
+    size_t n_tables = 0;
+    std::vector<uint32_t> table_sums;  // per table of the last compression: 4096 when decodable
+    uint64_t undecodable_tables = 0;
     std::vector<TensorDesc> descs;  // host copy, payload_off / flags filled in
     bool have_resident = false, have_images = false;
     chk_summary summary{};
@@ -218,29 +214,6 @@ static void control_zero(Context* c, void* dst, size_t bytes, cudaStream_t s) {
     c->launches++;
 }
 
-template <typename F>
-static void parallel_for(size_t n, int threads, F&& fn) {
-    if (threads <= 0) threads = (int)std::thread::hardware_concurrency();
-    if (threads < 1) threads = 1;
-    if ((size_t)threads > (n + 15) / 16) threads = (int)((n + 15) / 16);  // work is handed out 16 items at a time
-    if (threads <= 1) {
-        for (size_t i = 0; i < n; ++i) fn(i);
-        return;
-    }
-    std::atomic<size_t> next{0};
-    std::vector<std::thread> pool;
-    for (int t = 0; t < threads; ++t)
-        pool.emplace_back([&] {
-            for (;;) {
-                const size_t i0 = next.fetch_add(16);
-                if (i0 >= n) break;
-                const size_t i1 = i0 + 16 < n ? i0 + 16 : n;
-                for (size_t i = i0; i < i1; ++i) fn(i);
-            }
-        });
-    for (auto& th : pool) th.join();
-}
-
 // ------------------------------------------------------------------ work list
 // Order, ownership and sharing rules of compress_and_save_all
 // (src/ANSCompressor.cpp:1056-1078, :1210, :1239-1261, :1352-1371).
@@ -287,7 +260,7 @@ static void build_work(Context* c) {
         c->work.push_back(std::move(w));
     }
     // whether a table is built with the full alphabet: owner that is a cluster anchor
-    c->tables.resize(n_tables);  // every entry is rewritten by normalize_histogram before it is read
+    c->n_tables = (size_t)n_tables;
 }
 
 static bool is_cluster_anchor(const Context* c, const WorkItem& w) {
@@ -353,22 +326,36 @@ static uint32_t persistent_grid(Context* c, const void* kernel, size_t smem, siz
 }
 
 // ------------------------------------------------------------------ compress
+// The whole call is queued in one go -- the host never waits in between:
+//   count stream   split_hist_kernel over the batch, in a few launches ("segments")
+//   table stream   normalize_tables_kernel for each of those pieces as soon as it is counted, so
+//                  only the tables of the last piece are not hidden under the counting
+//   count stream   one persistent rans_encode_fused_kernel for the whole batch: lanes, symbol-0
+//                  chains, lane and tensor offsets, headers and the gather into the data-section
+//                  layout, tensor by tensor inside the teams.  Its scratch is one slot per
+//                  resident team; a workspace bound simply means fewer teams.
+// Counting and encoding contend for the same units of an SM (shared-memory atomics against table
+// lookups): run side by side they only take turns, so they run one after the other, while the
+// memory-bound gather of finished tensors hides under the issue-bound chains of the others.
 static void compress(Context* c, bool host_images) {
     const auto t_total = std::chrono::steady_clock::now();
     CHK_CUDA(cudaSetDevice(c->device));
     c->have_resident = c->have_images = false;
     c->summary = chk_summary{};
+    c->undecodable_tables = 0;
     build_work(c);
     const size_t W = c->work.size();
-    const size_t T = c->tables.size();
+    const size_t T = c->n_tables;
     cudaStream_t s = c->stream;
 
     c->descs.assign(W, TensorDesc{});
     pin_ensure(c->h_tiles, (W + 1) * 4);
     uint32_t* tile_start = static_cast<uint32_t*>(c->h_tiles.p);
     tile_start[0] = 0;
-    unsigned long long sidecar_total = 0, scratch_total = 0, bytes_total = 0;
+    unsigned long long sidecar_total = 0, bytes_total = 0, slot_bytes = 0;
+    uint32_t max_stride = 0;
     size_t n_sidecars = 0;
+    bool any_member = false, any_int = false;
     for (size_t i = 0; i < W; ++i) {
         const WorkItem& w = c->work[i];
         TensorDesc& d = c->descs[i];
@@ -379,27 +366,31 @@ static void compress(Context* c, bool host_images) {
         d.spe = w.spe;
         d.table_idx = (uint32_t)w.table;
         d.sidecar_off = sidecar_total;
-        d.scratch_off = scratch_total;
+        d.scratch_off = 0;  // lanes go to the slot of whichever team encodes the tensor
         const unsigned long long c_max = (w.bytes + 255) / 256;
-        d.chunk_stride = (uint32_t)((2 * c_max + 15) & ~15ull);
+        d.chunk_stride = (uint32_t)((2 * c_max + 31) & ~31ull);
         d.flags = w.owns ? kFlagNeedHist : 0u;
         if ((reinterpret_cast<uintptr_t>(d.src) & 15) == 0 && (sidecar_total & 15) == 0) d.flags |= kFlagAligned;
         sidecar_total += (unsigned long long)c->tensors[w.idx].n_elem * w.spe;
         // value-lane regions, plus one shared region for the lanes that only see zeroed bytes
-        scratch_total += (w.spe * 2 == w.es ? 129ull : 256ull) * d.chunk_stride;
+        const unsigned long long need = (w.spe * 2 == w.es ? 129ull : 256ull) * d.chunk_stride;
+        if (need > slot_bytes) slot_bytes = need;
+        if (d.chunk_stride > max_stride) max_stride = d.chunk_stride;
         bytes_total += w.bytes;
         n_sidecars += w.spe > 0;
+        any_member = any_member || !w.owns;
+        any_int = any_int || w.spe * 2 != w.es;
         tile_start[i + 1] = tile_start[i] + (uint32_t)((w.bytes + kSplitTileBytes - 1) / kSplitTileBytes);
     }
 
     if (W == 0) {
         c->have_resident = true;
+        c->table_sums.clear();
         if (host_images) {
-            const size_t sizes[3] = {kFileHeader, kFileHeader, kFileHeader};
             const uint32_t magic[3] = {kStatesMagic, kMantMagic, kDictMagic};
             const uint32_t ver[3] = {kStatesVersion, kMantVersion, kDictVersion};
             for (int k = 0; k < 3; ++k) {
-                pin_ensure(c->img[k], sizes[k]);
+                pin_ensure(c->img[k], kFileHeader);
                 uint8_t* p = static_cast<uint8_t*>(c->img[k].p);
                 put<uint32_t>(p, magic[k]);
                 put<uint32_t>(p + 4, ver[k]);
@@ -412,307 +403,197 @@ static void compress(Context* c, bool host_images) {
         return;
     }
 
+    // ---- the encode grid and its scratch: one slot (the largest tensor's lane regions) per team
+    slot_bytes = (slot_bytes + 255) & ~255ull;
+    auto kernel = any_int ? rans_encode_fused_kernel<true> : rans_encode_fused_kernel<false>;
+    const size_t smem = any_int ? sizeof(EncSmem<4>) : sizeof(EncSmem<2>);
+    uint32_t teams = persistent_grid(c, reinterpret_cast<const void*>(kernel), smem, W, c->encode_teams_per_sm);
+    if (c->workspace_bytes) {
+        const unsigned long long fit = c->workspace_bytes / slot_bytes;
+        if (fit == 0)
+            throw Error{CHK_ERR_CAPACITY, "workspace of " + std::to_string(c->workspace_bytes) + " bytes is smaller than the " +
+                                              std::to_string(slot_bytes) + " bytes of encode scratch the largest tensor needs"};
+        if (fit < teams) teams = (uint32_t)fit;
+    }
+
+    // ---- pieces the batch is counted in (equal bytes; a small batch is one piece)
+    const size_t n_seg = W >= 512 ? (size_t)c->segments : 1;
+    std::vector<size_t> seg_end;
+    {
+        unsigned long long acc = 0;
+        for (size_t i = 0; i < W; ++i) {
+            acc += c->descs[i].n_bytes;
+            if (seg_end.size() + 1 < n_seg && acc * n_seg >= bytes_total * (seg_end.size() + 1)) seg_end.push_back(i + 1);
+        }
+        seg_end.push_back(W);
+    }
+    const size_t n_win = seg_end.size();
+
     dev_ensure(c, c->d_descs, W * sizeof(TensorDesc));
     dev_ensure(c, c->d_tiles, (W + 1) * 4);
     dev_ensure(c, c->d_hist, W * 1024);
     dev_ensure(c, c->d_sidecar, sidecar_total + 64);
-    dev_ensure(c, c->d_scratch, scratch_total + 64);
+    dev_ensure(c, c->d_scratch, (unsigned long long)teams * slot_bytes + 64);
+    // the batch's distinct symbol-0 chains (a handful: see zero_chain_kernel)
+    const uint32_t z_slots = (uint32_t)(n_sidecars < 64 ? (n_sidecars ? n_sidecars : 1) : 64);
+    dev_ensure(c, c->d_zslots, z_slots * sizeof(ZeroSlot));
+    dev_ensure(c, c->d_zregions, (unsigned long long)z_slots * max_stride + 64);
+    dev_ensure(c, c->d_zslot_of, W * 4);
     dev_ensure(c, c->d_hdrs, W * 4096);
-    dev_ensure(c, c->d_lsrc, W * 2048);
-    dev_ensure(c, c->d_order, W * 4);
     dev_ensure(c, c->d_ticket, 256);
-    pin_ensure(c->h_order, W * 4);
-    dev_ensure(c, c->d_loff, W * 1024);
+    dev_ensure(c, c->d_order, W * 4);
     dev_ensure(c, c->d_psize, W * 8);
-    dev_ensure(c, c->d_poff, (W + 1) * 8);
-    dev_ensure(c, c->d_payload, bytes_total + 64);
+    dev_ensure(c, c->d_payload, bytes_total + (unsigned long long)kPayloadAlign * W + 64);  // a heap: every range starts on a sector
     dev_ensure(c, c->d_enc, T * 256 * sizeof(EncEntry));
     dev_ensure(c, c->d_freq, T * 256 * 4);
     dev_ensure(c, c->d_cum, T * 257 * 4);
-    dev_ensure(c, c->d_status, 256);
-    pin_ensure(c->h_hist, W * 1024);
-    pin_ensure(c->h_hdrs, W * 4096);
+    dev_ensure(c, c->d_jobs, T * sizeof(TableJob));
+    dev_ensure(c, c->d_sums, T * 4);
+    pin_ensure(c->h_hdrs, host_images ? W * 4096 : 0);
     pin_ensure(c->h_poff, (W + 1) * 8);
+    pin_ensure(c->h_psize, W * 8);
+    pin_ensure(c->h_order, W * 4);
     pin_ensure(c->h_descs, W * sizeof(TensorDesc));
-    pin_ensure(c->h_status, 256);
-    pin_ensure(c->h_enc, T * 512);
-    dev_ensure(c, c->d_nf16, T * 512);
+    pin_ensure(c->h_jobs, T * sizeof(TableJob));
+    pin_ensure(c->h_sums, T * 4 + 4);
+    const bool want_tables = host_images || any_member;
+    pin_ensure(c->h_freq, want_tables ? T * 256 * 4 : 0);
+    pin_ensure(c->h_cum, host_images ? T * 257 * 4 : 0);
 
     std::memcpy(c->h_descs.p, c->descs.data(), W * sizeof(TensorDesc));
+    {
+        TableJob* jobs = static_cast<TableJob*>(c->h_jobs.p);
+        for (size_t i = 0; i < W; ++i) {
+            const WorkItem& w = c->work[i];
+            if (!w.owns) continue;
+            const bool full = is_cluster_anchor(c, w);
+            jobs[w.table].owner = (uint32_t)i;
+            jobs[w.table].flags = (full ? kTableFullAlphabet : 0u) | (full && c->repair_tables ? kTableRepair : 0u);
+        }
+        // largest tensors first, so the persistent grid drains the batch without a ragged last wave
+        uint32_t* ord = static_cast<uint32_t*>(c->h_order.p);
+        for (size_t i = 0; i < W; ++i) ord[i] = (uint32_t)i;
+        std::stable_sort(ord, ord + W, [&](uint32_t x, uint32_t y) { return c->descs[x].n_bytes > c->descs[y].n_bytes; });
+    }
+    ensure_events(c->ev_count, n_win, true);
+    ensure_events(c->ev_tab, n_win, true);
+
     c->timing["prepare_ms"] = wall_ms(t_total);
     CHK_CUDA(cudaEventRecord(c->ev[0], s));
     control_copy(c, c->d_descs.p, c->h_descs.p, W * sizeof(TensorDesc), s);
     control_copy(c, c->d_tiles.p, c->h_tiles.p, (W + 1) * 4, s);
+    control_copy(c, c->d_jobs.p, c->h_jobs.p, T * sizeof(TableJob), s);
+    control_copy(c, c->d_order.p, c->h_order.p, W * 4, s);
     control_zero(c, c->d_hist.p, W * 1024, s);
+    control_zero(c, c->d_ticket.p, 256, s);  // word 0: ticket counter; words 2-3: the 64-bit heap cursor
+    control_zero(c, c->d_zslots.p, z_slots * sizeof(ZeroSlot), s);
 
-    // ---- stage 1: low bytes out, histograms.  The batch is cut into a few segments; each
-    // segment's histograms are copied back as soon as its launch is done, so the host
-    // normalises segment g while the device still counts g+1.
-    // a small batch cannot fill the device whichever way it is cut: one segment, fewest launches
-    const size_t n_seg = W >= 512 ? (size_t)c->segments : 1;
-    std::vector<size_t> seg_end(n_seg, W);
-    {
-        unsigned long long acc = 0;
-        size_t g = 0;
-        for (size_t i = 0; i < W && g + 1 < n_seg; ++i) {
-            acc += c->descs[i].n_bytes;
-            // a smaller first segment gets the first encode grid going early; the rest are equal
-            const unsigned first = c->first_segment_pct > 0 ? (unsigned)c->first_segment_pct : (unsigned)(100 / n_seg);
-            const unsigned cut = first + (unsigned)((100 - first) * g / (n_seg - 1));
-            if (acc * 100 >= bytes_total * cut) seg_end[g++] = i + 1;
-        }
-    }
-    ensure_events(c->seg_events, n_seg, false, true);
-    ensure_events(c->ev_tab, n_seg, false);
-    ensure_events(c->ev_zero, n_seg, false);
-    ensure_events(c->ev_enc0, n_seg, true);
-    ensure_events(c->ev_enc1, n_seg, true);
-    ensure_events(c->ev_cmp0, n_seg, true);
-    ensure_events(c->ev_cmp1, n_seg, true);
-    {
-        // every segment has its own largest-first order (indices relative to the segment) and ticket counter
-        uint32_t* ord = static_cast<uint32_t*>(c->h_order.p);
-        for (size_t g = 0, a = 0; g < n_seg; ++g) {
-            const size_t b = seg_end[g];
-            for (size_t i = a; i < b; ++i) ord[i] = (uint32_t)(i - a);
-            std::stable_sort(ord + a, ord + b, [&](uint32_t x, uint32_t y) {
-                return c->descs[a + x].n_bytes > c->descs[a + y].n_bytes;
-            });
-            a = b;
-        }
-        control_copy(c, c->d_order.p, c->h_order.p, W * 4, s);
-        control_zero(c, c->d_ticket.p, 256, s);
-    }
-    for (size_t g = 0, a = 0; g < n_seg; ++g) {
-        const size_t b = seg_end[g];
-        if (b > a) {
-            const uint32_t tiles = tile_start[b] - tile_start[a];
-            const uint32_t grid = tiles < 148u * 8u ? tiles : 148u * 8u;
-            split_hist_kernel<<<grid, 256, 0, s>>>(static_cast<const TensorDesc*>(c->d_descs.p) + a,
-                                                   static_cast<const uint32_t*>(c->d_tiles.p) + a, (uint32_t)(b - a),
-                                                   tile_start[a], tiles, static_cast<uint8_t*>(c->d_sidecar.p),
-                                                   static_cast<uint32_t*>(c->d_hist.p) + a * 256);
+    const uint32_t sms = (uint32_t)(c->sm_count > 0 ? c->sm_count : 1);
+    size_t tab_done = 0;
+    for (size_t g = 0, a = 0; g < n_win; ++g) {
+        const size_t b = seg_end[g], n = b - a;
+        const uint32_t tiles = tile_start[b] - tile_start[a];
+        const uint32_t grid1 = tiles < sms * 8u ? tiles : sms * 8u;
+        split_hist_kernel<<<grid1, 256, 0, s>>>(static_cast<const TensorDesc*>(c->d_descs.p) + a,
+                                                static_cast<const uint32_t*>(c->d_tiles.p) + a, (uint32_t)n, tile_start[a],
+                                                tiles, static_cast<uint8_t*>(c->d_sidecar.p),
+                                                static_cast<uint32_t*>(c->d_hist.p) + a * 256);
+        CHK_CUDA(cudaGetLastError());
+        c->launches++;
+        CHK_CUDA(cudaEventRecord(c->ev_count[g], s));
+        // tables owned inside this piece: table numbers follow the work order, so they are a range
+        size_t tab_hi = tab_done;
+        for (size_t i = a; i < b; ++i)
+            if (c->work[i].owns) tab_hi = (size_t)c->work[i].table + 1;
+        CHK_CUDA(cudaStreamWaitEvent(c->side_stream, c->ev_count[g], 0));
+        if (tab_hi > tab_done) {
+            const size_t t0 = tab_done, nt = tab_hi - tab_done;
+            // a job's owner index counts from the start of the batch: whole-batch descriptor and histogram arrays
+            normalize_tables_kernel<<<(uint32_t)(nt < sms * 8u ? nt : sms * 8u), 256, 0, c->side_stream>>>(
+                static_cast<const TableJob*>(c->d_jobs.p) + t0, static_cast<const TensorDesc*>(c->d_descs.p),
+                static_cast<const uint32_t*>(c->d_hist.p), static_cast<EncEntry*>(c->d_enc.p) + t0 * 256,
+                static_cast<uint32_t*>(c->d_freq.p) + t0 * 256, static_cast<uint32_t*>(c->d_cum.p) + t0 * 257,
+                static_cast<uint32_t*>(c->d_sums.p) + t0, (uint32_t)nt);
             CHK_CUDA(cudaGetLastError());
             c->launches++;
-            control_copy(c, static_cast<uint8_t*>(c->h_hist.p) + a * 1024,
-                         static_cast<const uint8_t*>(c->d_hist.p) + a * 1024, (b - a) * 1024, s);
+            tab_done = tab_hi;
         }
-        CHK_CUDA(cudaEventRecord(c->seg_events[g], s));
+        // the symbol-0 chains this piece needs and the batch does not have yet
+        zero_chain_kernel<<<(uint32_t)n, 32, 0, c->side_stream>>>(
+            static_cast<const TensorDesc*>(c->d_descs.p) + a, static_cast<const EncEntry*>(c->d_enc.p),
+            static_cast<ZeroSlot*>(c->d_zslots.p), z_slots, static_cast<uint8_t*>(c->d_zregions.p), max_stride,
+            static_cast<int32_t*>(c->d_zslot_of.p) + a, (uint32_t)n);
+        CHK_CUDA(cudaGetLastError());
+        c->launches++;
+        CHK_CUDA(cudaEventRecord(c->ev_tab[g], c->side_stream));
         a = b;
     }
+    CHK_CUDA(cudaStreamWaitEvent(s, c->ev_tab[n_win - 1], 0));  // the table stream is in order: all tables are complete
     CHK_CUDA(cudaEventRecord(c->ev[1], s));
+    uint32_t* const ticket = static_cast<uint32_t*>(c->d_ticket.p);
+    FusedParams fp{};
+    fp.descs = static_cast<TensorDesc*>(c->d_descs.p);
+    fp.tables = static_cast<const EncEntry*>(c->d_enc.p);
+    fp.scratch = static_cast<uint8_t*>(c->d_scratch.p);
+    fp.slot_bytes = slot_bytes;
+    fp.zero_slots = static_cast<const ZeroSlot*>(c->d_zslots.p);
+    fp.zero_regions = static_cast<const uint8_t*>(c->d_zregions.p);
+    fp.zero_slot_of = static_cast<const int32_t*>(c->d_zslot_of.p);
+    fp.zero_region_stride = max_stride;
+    fp.n_tensors = (uint32_t)W;
+    fp.hdrs = static_cast<LaneHeader*>(c->d_hdrs.p);
+    fp.payload = static_cast<uint8_t*>(c->d_payload.p);
+    fp.payload_size = static_cast<unsigned long long*>(c->d_psize.p);
+    fp.heap_cursor = reinterpret_cast<unsigned long long*>(ticket + 2);
+    fp.order = static_cast<const uint32_t*>(c->d_order.p);
+    fp.ticket = ticket;
+    kernel<<<teams, kTeam, smem, s>>>(fp);
+    CHK_CUDA(cudaGetLastError());
+    c->launches++;
+    CHK_CUDA(cudaEventRecord(c->ev[2], s));
+    c->timing["enqueue_ms"] = wall_ms(t_total);
 
-    // ---- tables on the host, and everything after them, segment by segment.
-    // Worker threads normalise tensors in order, waiting for the segment a tensor belongs to;
-    // a releaser thread marks segments whose histograms have landed.  The calling thread
-    // launches, for each segment in turn as soon as its tables are done: table upload and
-    // build_tables_kernel, the encode grid (a stream per segment, so the grids of several
-    // segments share the device: one segment alone has too few tensors to fill it), the shared
-    // zero-lane chains (their own streams), then offsets and compaction (compaction stream).
-    // The device thus counts later segments and compacts earlier ones (memory-bound work)
-    // while it encodes (issue-bound work).
-    const auto t_tab = std::chrono::steady_clock::now();
-    uint16_t* h_nf16 = static_cast<uint16_t*>(c->h_enc.p);
-    bool any_int = false;
-    for (size_t i = 0; i < W && !any_int; ++i) any_int = c->work[i].spe * 2 != c->work[i].es;
-    std::vector<bool> launched(n_seg, false);
-    {
-        std::vector<size_t> owners;
-        std::vector<uint32_t> owner_seg;
-        std::vector<size_t> tab_lo(n_seg, 0), tab_hi(n_seg, 0);  // tables owned inside each segment: [lo, hi)
-        std::unique_ptr<std::atomic<uint32_t>[]> seg_left(new std::atomic<uint32_t>[n_seg]);
-        for (size_t g = 0; g < n_seg; ++g) seg_left[g].store(0);
-        for (size_t i = 0, g = 0; i < W; ++i) {
-            while (i >= seg_end[g]) ++g;
-            if (c->work[i].owns) {
-                const size_t t = (size_t)c->work[i].table;
-                if (tab_hi[g] == tab_lo[g]) tab_lo[g] = t;
-                tab_hi[g] = t + 1;
-                owners.push_back(i);
-                owner_seg.push_back((uint32_t)g);
-                seg_left[g].fetch_add(1);
-            }
-        }
-        std::atomic<uint32_t> ready{0};  // segments whose histograms are on the host
-        std::atomic<bool> failed{false};
-        std::mutex mu;
-        std::condition_variable cv;
-        const uint32_t* hist_all = static_cast<const uint32_t*>(c->h_hist.p);
-        auto work_fn = [&](size_t k) {
-            const uint32_t g = owner_seg[k];
-            if (ready.load(std::memory_order_acquire) <= g) {
-                std::unique_lock<std::mutex> lk(mu);
-                cv.wait(lk, [&] { return ready.load(std::memory_order_acquire) > g || failed.load(); });
-            }
-            if (!failed.load()) {
-                const size_t i = owners[k];
-                const WorkItem& w = c->work[i];
-                uint32_t h[256];
-                std::memcpy(h, hist_all + i * 256, 1024);
-                // the zeroed low bytes of every element are part of the codec input
-                h[0] += (uint32_t)((uint64_t)c->tensors[w.idx].n_elem * w.spe);
-                const bool full = is_cluster_anchor(c, w);
-                FreqTable& ft = c->tables[w.table];
-                normalize_histogram(h, full, full && c->repair_tables, ft);
-                uint16_t* o = h_nf16 + (size_t)w.table * 256;
-                for (int sy = 0; sy < 256; ++sy) o[sy] = (uint16_t)ft.norm_freq[sy];
-            }
-            if (seg_left[g].fetch_sub(1) == 1) {  // last table of its segment: wake the launcher
-                std::lock_guard<std::mutex> lk(mu);
-                cv.notify_all();
-            }
-        };
-        std::thread releaser([&] {
-            cudaSetDevice(c->device);
-            for (size_t g = 0; g < n_seg; ++g) {
-                const bool ok = cudaEventSynchronize(c->seg_events[g]) == cudaSuccess;
-                {
-                    std::lock_guard<std::mutex> lk(mu);
-                    if (ok) ready.store((uint32_t)g + 1, std::memory_order_release); else failed.store(true);
-                }
-                cv.notify_all();
-                if (!ok) return;
-            }
-        });
-        std::thread normaliser([&] { parallel_for(owners.size(), c->host_threads, work_fn); });
-
-        auto launch_segment = [&](size_t g, size_t a, size_t b) {
-            const size_t n = b - a;
-            cudaStream_t sB = c->enc_streams[g % 8], sC = c->cmp_stream, sZ = c->zero_streams[g % 4];
-            const TensorDesc* descs_g = static_cast<const TensorDesc*>(c->d_descs.p) + a;
-            LaneHeader* hdrs_g = static_cast<LaneHeader*>(c->d_hdrs.p) + a * 256;
-            unsigned long long* lsrc_g = static_cast<unsigned long long*>(c->d_lsrc.p) + a * 256;
-            uint32_t* loff_g = static_cast<uint32_t*>(c->d_loff.p) + a * 256;
-            const EncEntry* enc = static_cast<const EncEntry*>(c->d_enc.p);
-            CHK_CUDA(cudaStreamWaitEvent(sB, c->encode_after_count ? c->ev[1] : c->seg_events[g], 0));
-            // frequencies up (512 B per table); prefix sums and encode entries are derived on the device
-            if (tab_hi[g] > tab_lo[g]) {
-                const size_t t0 = tab_lo[g], nt = tab_hi[g] - tab_lo[g];
-                control_copy(c, static_cast<uint16_t*>(c->d_nf16.p) + t0 * 256, h_nf16 + t0 * 256, nt * 512, sB);
-                build_tables_kernel<<<(uint32_t)(nt < 4096 ? nt : 4096), 256, 0, sB>>>(
-                    static_cast<const uint16_t*>(c->d_nf16.p) + t0 * 256, static_cast<EncEntry*>(c->d_enc.p) + t0 * 256,
-                    static_cast<uint32_t*>(c->d_freq.p) + t0 * 256, static_cast<uint32_t*>(c->d_cum.p) + t0 * 257,
-                    (uint32_t)nt);
-                CHK_CUDA(cudaGetLastError());
-                c->launches++;
-            }
-            CHK_CUDA(cudaEventRecord(c->ev_tab[g], sB));
-            // a member of a cluster borrows the table of an anchor that may sit in an earlier
-            // segment, whose tables were built on another stream
-            for (size_t p = 0; p < g; ++p)
-                if (launched[p]) CHK_CUDA(cudaStreamWaitEvent(sB, c->ev_tab[p], 0));
-            // the shared symbol-0 chain of every tensor (one thread each) runs next to the value lanes
-            CHK_CUDA(cudaStreamWaitEvent(sZ, c->ev_tab[g], 0));
-            zero_lane_kernel<<<(uint32_t)((n + 127) / 128), 128, 0, sZ>>>(descs_g, enc, static_cast<uint8_t*>(c->d_scratch.p),
-                                                                          hdrs_g, lsrc_g, (uint32_t)n);
-            CHK_CUDA(cudaGetLastError());
-            CHK_CUDA(cudaEventRecord(c->ev_zero[g], sZ));
-            // A tensor can only meet a symbol its table lacks when it borrows another tensor's
-            // table; the reference builds shared tables over the full alphabet, so this is
-            // normally false and the kernel without the escape test runs.
-            bool need_escape = false;
-            for (size_t i = a; i < b && !need_escape; ++i) {
-                if (c->work[i].owns) continue;
-                const FreqTable& ft = c->tables[c->work[i].table];
-                for (int sy = 0; sy < 256 && !need_escape; ++sy) need_escape = ft.norm_freq[sy] == 0;
-            }
-            auto kernel = any_int ? (need_escape ? rans_encode_kernel<true, true> : rans_encode_kernel<true, false>)
-                                  : (need_escape ? rans_encode_kernel<false, true> : rans_encode_kernel<false, false>);
-            const size_t smem = any_int ? sizeof(EncSmem<4>) : sizeof(EncSmem<2>);
-            const uint32_t grid = persistent_grid(c, reinterpret_cast<const void*>(kernel), smem, n,
-                                                  n_seg > 1 ? c->encode_teams_per_sm : 0);
-            CHK_CUDA(cudaEventRecord(c->ev_enc0[g], sB));
-            kernel<<<grid, kTeam, smem, sB>>>(descs_g, enc, static_cast<uint8_t*>(c->d_scratch.p), hdrs_g, lsrc_g,
-                                              static_cast<const uint32_t*>(c->d_order.p) + a,
-                                              static_cast<uint32_t*>(c->d_ticket.p) + g, (uint32_t)n);
-            CHK_CUDA(cudaGetLastError());
-            CHK_CUDA(cudaEventRecord(c->ev_enc1[g], sB));
-            c->launches += 2;
-            // offsets + compaction into the data-section layout; the running payload offset is
-            // handed from one segment's scan to the next through d_poff
-            CHK_CUDA(cudaStreamWaitEvent(sC, c->ev_enc1[g], 0));
-            CHK_CUDA(cudaStreamWaitEvent(sC, c->ev_zero[g], 0));
-            CHK_CUDA(cudaEventRecord(c->ev_cmp0[g], sC));
-            unsigned long long* poff_g = static_cast<unsigned long long*>(c->d_poff.p) + a;
-            lane_scan_kernel<<<(uint32_t)(n < 4096 ? n : 4096), 256, 0, sC>>>(
-                static_cast<TensorDesc*>(c->d_descs.p) + a, hdrs_g, static_cast<unsigned long long*>(c->d_psize.p) + a,
-                loff_g, (uint32_t)n);
-            CHK_CUDA(cudaGetLastError());
-            tensor_scan_kernel<<<1, 1024, 0, sC>>>(static_cast<TensorDesc*>(c->d_descs.p) + a,
-                                                   static_cast<const unsigned long long*>(c->d_psize.p) + a, poff_g,
-                                                   (uint32_t)n, a ? poff_g : nullptr);
-            CHK_CUDA(cudaGetLastError());
-            const unsigned long long blocks = ((unsigned long long)n * 256 + 7) / 8;
-            const uint32_t g3 = (uint32_t)(blocks < 148ull * 16 ? blocks : 148ull * 16);
-            compact_kernel<<<g3, 256, 0, sC>>>(descs_g, hdrs_g, lsrc_g, loff_g, static_cast<const uint8_t*>(c->d_scratch.p),
-                                               static_cast<uint8_t*>(c->d_payload.p), (uint32_t)n);
-            CHK_CUDA(cudaGetLastError());
-            CHK_CUDA(cudaEventRecord(c->ev_cmp1[g], sC));
-            c->launches += 3;
-            launched[g] = true;
-        };
-
-        Error pending{CHK_OK, ""};
-        try {
-            for (size_t g = 0, a = 0; g < n_seg; ++g) {
-                const size_t b = seg_end[g];
-                {
-                    std::unique_lock<std::mutex> lk(mu);
-                    cv.wait(lk, [&] {
-                        return failed.load() || (seg_left[g].load() == 0 && ready.load(std::memory_order_acquire) > g);
-                    });
-                }
-                if (failed.load()) break;
-                if (b > a) launch_segment(g, a, b);
-                a = b;
-            }
-        } catch (const Error& e) {
-            pending = e;
-            {
-                std::lock_guard<std::mutex> lk(mu);
-                failed.store(true);
-            }
-            cv.notify_all();
-        }
-        normaliser.join();
-        releaser.join();
-        if (pending.code != CHK_OK) throw pending;
-        if (failed.load()) CHK_CUDA(cudaStreamSynchronize(s));  // surfaces the device error
-    }
-    c->timing["table_ms"] = wall_ms(t_tab);
-
-    cudaStream_t s_end = c->cmp_stream;
-    control_copy(c, c->h_poff.p, c->d_poff.p, (W + 1) * 8, s_end);
-    control_copy(c, c->h_descs.p, c->d_descs.p, W * sizeof(TensorDesc), s_end);
-    if (host_images) control_copy(c, c->h_hdrs.p, c->d_hdrs.p, W * 4096, s_end);
-    CHK_CUDA(cudaStreamSynchronize(s_end));
+    control_copy(c, c->h_psize.p, c->d_psize.p, W * 8, s);
+    control_copy(c, c->h_descs.p, c->d_descs.p, W * sizeof(TensorDesc), s);
+    control_copy(c, c->h_sums.p, c->d_sums.p, T * 4, s);
+    if (host_images) control_copy(c, c->h_hdrs.p, c->d_hdrs.p, W * 4096, s);
+    if (want_tables) control_copy(c, c->h_freq.p, c->d_freq.p, T * 256 * 4, s);
+    if (host_images) control_copy(c, c->h_cum.p, c->d_cum.p, T * 257 * 4, s);
     CHK_CUDA(cudaStreamSynchronize(s));
 
-    // encode grids of different segments run side by side: their time is the span from the first
-    // start to the last end; compactions run one after the other and are summed.  The stages
-    // overlap, so the three figures add up to more than device_span_ms.
-    double enc_ms = 0, cmp_ms = 0;
-    size_t first = n_seg, last = n_seg;
-    for (size_t g = 0; g < n_seg; ++g) {
-        if (!launched[g]) continue;
-        if (first == n_seg) first = g;
-        const double e = ms_between(c->ev_enc0[first], c->ev_enc1[g]);
-        if (e > enc_ms) enc_ms = e;
-        cmp_ms += ms_between(c->ev_cmp0[g], c->ev_cmp1[g]);
-        last = g;
-    }
-    c->timing["split_hist_ms"] = ms_between(c->ev[0], c->ev[1]);
-    c->timing["encode_ms"] = enc_ms;
-    c->timing["compact_ms"] = cmp_ms;
-    c->timing["device_span_ms"] = last < n_seg ? ms_between(c->ev[0], c->ev_cmp1[last]) : 0.0;
+    c->timing["split_hist_ms"] = ms_between(c->ev[0], c->ev_count[n_win - 1]);
+    c->timing["table_ms"] = ms_between(c->ev_count[n_win - 1], c->ev[1]);  // what the counting did not hide
+    c->timing["encode_ms"] = ms_between(c->ev[1], c->ev[2]);                // lanes, offsets and gather
+    c->timing["compact_ms"] = 0.0;                                          // part of the encode kernel
+    c->timing["device_span_ms"] = ms_between(c->ev[0], c->ev[2]);
     c->timing["compress_device_ms"] = c->timing["device_span_ms"];
+    c->timing["encode_teams"] = (double)teams;
+    c->timing["workspace_mb"] = (double)((unsigned long long)teams * slot_bytes) / 1048576.0;
     c->timing["to_sync_ms"] = wall_ms(t_total);
-    c->timing["compress_device_ms"] =
-        c->timing["split_hist_ms"] + c->timing["encode_ms"] + c->timing["compact_ms"];
 
+    // descriptors come back with each tensor's place in the payload heap and its raw flag; the file wants
+    // the payloads in index order, so the offsets written there are the running sum of the sizes
     std::memcpy(c->descs.data(), c->h_descs.p, W * sizeof(TensorDesc));
-    const unsigned long long* poff = static_cast<const unsigned long long*>(c->h_poff.p);
+    const unsigned long long* psize = static_cast<const unsigned long long*>(c->h_psize.p);
+    unsigned long long* poff = static_cast<unsigned long long*>(c->h_poff.p);
+    poff[0] = 0;
+    for (size_t i = 0; i < W; ++i) poff[i + 1] = poff[i] + psize[i];
     const unsigned long long payload_total = poff[W];
+    const uint32_t* sums = static_cast<const uint32_t*>(c->h_sums.p);
+    c->table_sums.assign(sums, sums + T);
+    for (size_t t = 0; t < T; ++t) c->undecodable_tables += sums[t] != kM;
+    if (any_member) {
+        // the encode grids ran without the test for symbols missing from a borrowed table
+        const uint32_t* fq = static_cast<const uint32_t*>(c->h_freq.p);
+        for (size_t i = 0; i < W; ++i) {
+            if (c->work[i].owns) continue;
+            const uint32_t* f = fq + (size_t)c->work[i].table * 256;
+            for (int sy = 0; sy < 256; ++sy)
+                if (f[sy] == 0)
+                    throw Error{CHK_ERR_INVALID, "internal: shared table of '" + c->tensors[c->work[i].idx].name +
+                                                     "' lacks a symbol; shared tables must cover the full alphabet"};
+        }
+    }
     c->have_resident = true;
 
     c->summary.n_tensors = W;
@@ -729,8 +610,11 @@ static void compress(Context* c, bool host_images) {
         pin_ensure(c->img[0], c->summary.states_bytes);
         uint8_t* st = static_cast<uint8_t*>(c->img[0].p);
         const size_t st_data = kFileHeader + W * kStatesEntry;
-        if (payload_total)
-            CHK_CUDA(cudaMemcpyAsync(st + st_data, c->d_payload.p, payload_total, cudaMemcpyDeviceToHost, s));
+        // heap order -> file order: each tensor's payload goes to its place in the data section
+        for (size_t i = 0; i < W; ++i)
+            if (psize[i])
+                CHK_CUDA(cudaMemcpyAsync(st + st_data + poff[i], static_cast<const uint8_t*>(c->d_payload.p) + c->descs[i].payload_off,
+                                         psize[i], cudaMemcpyDeviceToHost, s));
         // mantissa image (write_rank_mantissa_file, :839-887)
         pin_ensure(c->img[1], c->summary.mantissa_bytes);
         uint8_t* mt = static_cast<uint8_t*>(c->img[1].p);
@@ -755,6 +639,8 @@ static void compress(Context* c, bool host_images) {
         put<uint32_t>(dc + 12, (uint32_t)T);
 
         const LaneHeader* hdrs = static_cast<const LaneHeader*>(c->h_hdrs.p);
+        const uint32_t* h_freq = static_cast<const uint32_t*>(c->h_freq.p);
+        const uint32_t* h_cum = static_cast<const uint32_t*>(c->h_cum.p);
         size_t m_i = 0;
         for (size_t i = 0; i < W; ++i) {
             const WorkItem& w = c->work[i];
@@ -788,8 +674,8 @@ static void compress(Context* c, bool host_images) {
             if (w.owns) {
                 uint8_t* d = dc + kFileHeader + (size_t)w.table * kDictEntry;
                 put_name(d, t.name);
-                std::memcpy(d + 256, c->tables[w.table].norm_freq, 1024);
-                std::memcpy(d + 1280, c->tables[w.table].cum_freq, 1028);
+                std::memcpy(d + 256, h_freq + (size_t)w.table * 256, 1024);
+                std::memcpy(d + 1280, h_cum + (size_t)w.table * 257, 1028);
             }
         }
         CHK_CUDA(cudaEventRecord(c->ev[6], s));
@@ -824,6 +710,12 @@ static void compress_and_save(Context* c, const std::string& dir) {
     if (ec) throw Error{CHK_ERR_IO, "cannot create output directories under " + dir};
     if (c->tensors.empty()) return;  // nothing registered: directories only (src/ANSCompressor.cpp:1026-1029)
     compress(c, true);
+    if (c->undecodable_tables && !c->allow_undecodable)
+        throw Error{CHK_ERR_UNDECODABLE,
+                    std::to_string(c->undecodable_tables) + " of " + std::to_string(c->n_tables) +
+                        " tables do not sum to 4096 (the reference's single take-back pass on a shared full-alphabet "
+                        "table): the files could not be restored and were not written.  Set \"repair_tables\" for decodable "
+                        "shared tables, \"allow_undecodable\" for the reference's bytes, or compress without clusters."};
     const auto t0 = std::chrono::steady_clock::now();
     std::string paths[3];
     rank_paths(c, dir, paths);
@@ -848,7 +740,7 @@ static void run_decode(Context* c, size_t W, const uint8_t* d_payload, const uin
     upload_order(c, W, [&](size_t i) { return hd[i].n_bytes; });
     auto kernel = any_int ? (tl ? rans_decode_kernel<true, true> : rans_decode_kernel<true, false>)
                           : (tl ? rans_decode_kernel<false, true> : rans_decode_kernel<false, false>);
-    const uint32_t grid = persistent_grid(c, reinterpret_cast<const void*>(kernel), smem, W);
+    const uint32_t grid = persistent_grid(c, reinterpret_cast<const void*>(kernel), smem, W, c->decode_teams_per_sm);
     CHK_CUDA(cudaEventRecord(c->ev[1], s));
     kernel<<<grid, kTeam, smem, s>>>(static_cast<const TensorDesc*>(c->d_descs.p), d_freq, d_cum, d_hdrs, d_payload,
                                      d_sidecar, static_cast<const uint32_t*>(c->d_order.p),
@@ -884,9 +776,9 @@ static void decompress_resident(Context* c, void* const* dst) {
         void* target = dst ? dst[w.idx] : c->tensors[w.idx].ptr;
         if (!target) continue;
         TensorDesc d = c->descs[i];
-        if (!(d.flags & kFlagRaw) && c->tables[w.table].sum != kM)
+        if (!(d.flags & kFlagRaw) && c->table_sums[w.table] != kM)
             throw Error{CHK_ERR_FORMAT, "table of '" + c->tensors[w.idx].name + "' sums to " +
-                                            std::to_string(c->tables[w.table].sum) +
+                                            std::to_string(c->table_sums[w.table]) +
                                             ", not 4096: the stream cannot be decoded"};
         d.dst = static_cast<uint8_t*>(target);
         d.src = nullptr;
@@ -951,10 +843,12 @@ static void decompress_images(Context* c, const uint8_t* st, size_t st_n, const 
         const uint64_t bytes = get<uint64_t>(e + 264), n_elem = get<uint64_t>(e + 272);
         const uint64_t off = get<uint64_t>(e + 280), size = get<uint64_t>(e + 288);
         const uint32_t es = elem_size(dtype), spe = sidecar_per_elem(dtype);
-        if (es == 0 || bytes != n_elem * es) throw Error{CHK_ERR_FORMAT, "entry '" + name + "': inconsistent sizes"};
+        if (es == 0 || n_elem > UINT64_MAX / es || bytes != n_elem * es || bytes >= (1ull << 32))
+            throw Error{CHK_ERR_FORMAT, "entry '" + name + "': inconsistent sizes"};
         if (t.dtype != dtype || t.n_elem != n_elem)
             throw Error{CHK_ERR_INVALID, "tensor '" + name + "': registered dtype/size differs from the checkpoint"};
-        if (off + size > payload_total) throw Error{CHK_ERR_FORMAT, "entry '" + name + "': payload out of range"};
+        if (size > payload_total || off > payload_total - size)
+            throw Error{CHK_ERR_FORMAT, "entry '" + name + "': payload out of range"};
         if (is_raw && size != bytes) throw Error{CHK_ERR_FORMAT, "entry '" + name + "': raw payload size mismatch"};
         TensorDesc d{};
         d.dst = static_cast<uint8_t*>(t.ptr);
@@ -987,7 +881,7 @@ static void decompress_images(Context* c, const uint8_t* st, size_t st_n, const 
             if (sd == side.end()) throw Error{CHK_ERR_FORMAT, "entry '" + name + "': no sidecar in mantissa file"};
             const uint8_t* m = mt + kFileHeader + sd->second * kMantEntry;
             const uint64_t moff = get<uint64_t>(m + 272), msz = get<uint64_t>(m + 280);
-            if (msz != n_elem * spe || moff + msz > sidecar_total)
+            if (msz != n_elem * spe || msz > sidecar_total || moff > sidecar_total - msz)
                 throw Error{CHK_ERR_FORMAT, "entry '" + name + "': sidecar out of range"};
             d.sidecar_off = moff;
         }
@@ -1135,6 +1029,10 @@ extern "C" {
 const char* chk_last_error(void) { return chk::g_last_error.c_str(); }
 
 int chk_context_create(int device, int rank, int local_rank, chk_context** out) {
+    return chk_context_create_ex(device, rank, local_rank, 0, out);
+}
+
+int chk_context_create_ex(int device, int rank, int local_rank, uint64_t workspace_bytes, chk_context** out) {
     CHK_API_BEGIN
     CHK_REQUIRE(out, "out is NULL");
     int n = 0;
@@ -1145,6 +1043,7 @@ int chk_context_create(int device, int rank, int local_rank, chk_context** out) 
     c->device = device;
     c->rank = rank;
     c->local_rank = local_rank;
+    c->workspace_bytes = workspace_bytes;
     try {
         // the counting stream gets the highest priority: its blocks go first whenever an SM has room,
         // so the encode teams of earlier segments do not hold up the tables of later ones
@@ -1152,9 +1051,6 @@ int chk_context_create(int device, int rank, int local_rank, chk_context** out) 
         CHK_CUDA(cudaDeviceGetStreamPriorityRange(&prio_lo, &prio_hi));
         CHK_CUDA(cudaStreamCreateWithPriority(&c->stream, cudaStreamNonBlocking, prio_hi));
         CHK_CUDA(cudaStreamCreateWithFlags(&c->side_stream, cudaStreamNonBlocking));
-        for (auto& e : c->enc_streams) CHK_CUDA(cudaStreamCreateWithFlags(&e, cudaStreamNonBlocking));
-        CHK_CUDA(cudaStreamCreateWithFlags(&c->cmp_stream, cudaStreamNonBlocking));
-        for (auto& z : c->zero_streams) CHK_CUDA(cudaStreamCreateWithFlags(&z, cudaStreamNonBlocking));
         CHK_CUDA(cudaDeviceGetAttribute(&c->sm_count, cudaDevAttrMultiProcessorCount, device));
         cudaMemPoolProps props{};
         props.allocType = cudaMemAllocationTypePinned;
@@ -1179,25 +1075,20 @@ int chk_context_destroy(chk_context* c) {
     cudaSetDevice(c->device);
     if (c->stream) cudaStreamSynchronize(c->stream);
     DevBuf* bufs[] = {&c->d_descs, &c->d_tiles, &c->d_hist, &c->d_sidecar, &c->d_scratch, &c->d_hdrs,
-                      &c->d_lsrc, &c->d_order, &c->d_ticket, &c->d_nf16, &c->d_loff, &c->d_psize, &c->d_poff, &c->d_payload, &c->d_enc,
+                      &c->d_order, &c->d_ticket, &c->d_psize, &c->d_zslots, &c->d_zregions, &c->d_zslot_of, &c->d_jobs, &c->d_sums, &c->d_payload, &c->d_enc,
                       &c->d_freq, &c->d_cum, &c->d_status, &c->d_stats_desc, &c->d_stats_out};
     for (DevBuf* b : bufs)
         if (b->p) cudaFreeAsync(b->p, c->stream);
     if (c->stream) cudaStreamSynchronize(c->stream);
-    PinBuf* pins[] = {&c->h_hist, &c->h_hdrs, &c->h_poff, &c->h_descs, &c->h_status, &c->h_enc, &c->h_stats, &c->h_order, &c->h_tiles,
+    PinBuf* pins[] = {&c->h_hdrs, &c->h_poff, &c->h_psize, &c->h_descs, &c->h_status, &c->h_jobs, &c->h_sums, &c->h_freq, &c->h_cum, &c->h_stats, &c->h_order, &c->h_tiles,
                       &c->img[0], &c->img[1], &c->img[2]};
     for (PinBuf* b : pins)
         if (b->p) cudaFreeHost(b->p);
     for (auto& e : c->ev)
         if (e) cudaEventDestroy(e);
-    for (auto* v : {&c->seg_events, &c->ev_tab, &c->ev_zero, &c->ev_enc0, &c->ev_enc1, &c->ev_cmp0, &c->ev_cmp1})
+    for (auto* v : {&c->ev_count, &c->ev_tab})
         for (auto& e : *v)
             if (e) cudaEventDestroy(e);
-    for (auto& e : c->enc_streams)
-        if (e) cudaStreamDestroy(e);
-    if (c->cmp_stream) cudaStreamDestroy(c->cmp_stream);
-    for (auto& z : c->zero_streams)
-        if (z) cudaStreamDestroy(z);
     if (c->pool) cudaMemPoolDestroy(c->pool);
     if (c->side_stream) cudaStreamDestroy(c->side_stream);
     if (c->stream) cudaStreamDestroy(c->stream);
@@ -1213,7 +1104,9 @@ int chk_reset(chk_context* c) {
     c->have_clusters = false;
     c->stats.clear();
     c->work.clear();
-    c->tables.clear();
+    c->n_tables = 0;
+    c->table_sums.clear();
+    c->undecodable_tables = 0;
     c->descs.clear();
     c->have_resident = c->have_images = false;
     c->summary = chk_summary{};
@@ -1251,21 +1144,24 @@ int chk_set_option(chk_context* c, const char* key, int64_t value) {
         c->repair_tables = value != 0;
     else if (k == "verify_zero_lanes")
         c->verify_zero_lanes = value != 0;
-    else if (k == "host_threads")
-        c->host_threads = (int)value;
+    else if (k == "allow_undecodable")
+        c->allow_undecodable = value != 0;
+
+    else if (k == "workspace_bytes") {
+        if (value < 0) throw chk::Error{CHK_ERR_INVALID, "workspace_bytes must not be negative (0 = no bound)"};
+        c->workspace_bytes = (uint64_t)value;
+    }
     else if (k == "decode_two_level")
         c->decode_two_level = value != 0;
     else if (k == "segments") {
         if (value < 1 || value > 8) throw chk::Error{CHK_ERR_INVALID, "segments must be 1..8"};
         c->segments = (int)value;
-    } else if (k == "first_segment_pct") {
-        if (value < 0 || value > 90) throw chk::Error{CHK_ERR_INVALID, "first_segment_pct must be 0..90"};
-        c->first_segment_pct = (int)value;
-    } else if (k == "encode_after_count") {
-        c->encode_after_count = value != 0;
     } else if (k == "encode_teams_per_sm") {
         if (value < 0 || value > 64) throw chk::Error{CHK_ERR_INVALID, "encode_teams_per_sm must be 0..64 (0 = as many as fit)"};
         c->encode_teams_per_sm = (int)value;
+    } else if (k == "decode_teams_per_sm") {
+        if (value < 0 || value > 64) throw chk::Error{CHK_ERR_INVALID, "decode_teams_per_sm must be 0..64 (0 = as many as fit)"};
+        c->decode_teams_per_sm = (int)value;
     } else
         throw chk::Error{CHK_ERR_INVALID, "unknown option: " + k};
     CHK_API_END
@@ -1350,6 +1246,14 @@ int chk_get_image(chk_context* c, int which, const void** data, uint64_t* size) 
     CHK_REQUIRE(c->have_images, "no host images: call chk_compress(ctx, 1) first");
     *data = c->img[which].p;
     *size = c->img[which].size;
+    CHK_API_END
+}
+
+int chk_get_table_report(chk_context* c, uint64_t* n_tables, uint64_t* n_undecodable) {
+    CHK_API_BEGIN
+    CHK_REQUIRE(c, "context is NULL");
+    if (n_tables) *n_tables = c->n_tables;
+    if (n_undecodable) *n_undecodable = c->undecodable_tables;
     CHK_API_END
 }
 
@@ -1569,7 +1473,12 @@ extern "C" int chk_encode_tensor_static(const void* d_src, uint64_t num_elements
     head.desc.spe = spe;
     head.desc.table_idx = 0;
     head.desc.scratch_off = offsetof(StaticScratch, lanes);
-    head.desc.chunk_stride = (uint32_t)((2 * c_max + 15) & ~15ull);
+    head.desc.chunk_stride = (uint32_t)((2 * c_max + 31) & ~31ull);
+    CHK_REQUIRE(cum_freq[0] == 0, "cum_freq[0] must be 0");
+    for (int i = 0; i < 256; ++i) {
+        CHK_REQUIRE(norm_freq[i] <= kM, "norm_freq above 4096");
+        CHK_REQUIRE(cum_freq[i + 1] == cum_freq[i] + norm_freq[i], "cum_freq is not the running sum of norm_freq");
+    }
     FreqTable ft;
     std::memcpy(ft.norm_freq, norm_freq, 1024);
     std::memcpy(ft.cum_freq, cum_freq, 1028);
@@ -1581,8 +1490,8 @@ extern "C" int chk_encode_tensor_static(const void* d_src, uint64_t num_elements
     // pageable source: the runtime stages it before returning, so the stack frame may go away
     CHK_CUDA(cudaMemcpyAsync(base, &head, sizeof(head), cudaMemcpyHostToDevice, s));
     const bool ints = spe * 2 != es;
-    zero_lane_kernel<<<1, 128, 0, s>>>(&dev->desc, dev->enc, base, static_cast<LaneHeader*>(d_lane_headers), dev->lane_src,
-                                       1u);
+    zero_lane_kernel<<<1, 32, 0, s>>>(&dev->desc, dev->enc, base, static_cast<LaneHeader*>(d_lane_headers), dev->lane_src,
+                                      1u);
     CHK_CUDA(cudaGetLastError());
     auto kernel = ints ? (escape ? rans_encode_kernel<true, true> : rans_encode_kernel<true, false>)
                        : (escape ? rans_encode_kernel<false, true> : rans_encode_kernel<false, false>);

@@ -31,7 +31,6 @@ enum : uint32_t {
 };
 
 enum : uint32_t {
-    kErrBarrierTimeout = 1u,   // an asynchronous tile copy did not complete in time
     kErrEndState = 2u,         // a decoded lane did not end in state 2^23
     kErrEndPointer = 4u,       // a decoded lane did not consume exactly byte_count bytes
 };
@@ -47,7 +46,7 @@ struct TensorDesc {
     uint32_t es;                    // element size in bytes
     uint32_t spe;                   // low bytes per element that bypass the codec
     uint32_t table_idx;             // which frequency table encodes/decodes it
-    uint32_t chunk_stride;          // bytes of scratch per lane (multiple of 16)
+    uint32_t chunk_stride;          // bytes of scratch per lane (multiple of 32)
     uint32_t flags;
     uint32_t pad_;
 };
@@ -116,16 +115,19 @@ __device__ __forceinline__ void split_one_byte(const TensorDesc& d, unsigned lon
                                                uint32_t* wh, bool count) {
     const uint8_t v = d.src[off];
     const uint32_t j = (uint32_t)(off % d.es);
-    if (j < d.spe)
-        sidecar[d.sidecar_off + (off / d.es) * d.spe + j] = v;
-    else if (count)
+    if (j < d.spe) {
+        if (sidecar) sidecar[d.sidecar_off + (off / d.es) * d.spe + j] = v;
+    } else if (count) {
         bin_add(wh, v);
+    }
 }
 
 // Fused row-1 + row-2 pass over all tensors of a batch: writes each tensor's
 // packed low bytes straight into its slice of the sidecar section and counts
-// the bytes the codec will see, except the zeroed ones (the host adds
-// num_elements*spe to bin 0).  The masked copy is never materialised.
+// the bytes the codec will see, except the zeroed ones (num_elements*spe are
+// added to bin 0 where the tables are built).  The masked copy is never
+// materialised.  With sidecar == nullptr the pass only counts (the compress
+// pipeline lets the encoder, which reads every byte anyway, write the low bytes).
 // Tiles are handed to CTAs in contiguous ranges so a CTA mostly stays inside
 // one tensor and merges its bins into global memory once per tensor.
 __global__ void __launch_bounds__(256) split_hist_kernel(const TensorDesc* __restrict__ descs,
@@ -181,6 +183,7 @@ __global__ void __launch_bounds__(256) split_hist_kernel(const TensorDesc* __res
         const unsigned long long base = (unsigned long long)(tile - tile_start[cur]) * kSplitTileBytes;
         const uint32_t nb = (uint32_t)((d.n_bytes - base) < kSplitTileBytes ? (d.n_bytes - base) : kSplitTileBytes);
         const bool count = (d.flags & kFlagNeedHist) != 0;
+        if (!count && !sidecar) continue;  // nothing to do for a tensor that borrows its table
         uint32_t* mine = wh[warp];
         uint32_t* mine_hot = hot[warp] + (lane % kHotCopies) * kHotStride;
 
@@ -211,7 +214,7 @@ __global__ void __launch_bounds__(256) split_hist_kernel(const TensorDesc* __res
                         s2.x = __byte_perm(w[0], w[1], 0x6420);
                         s2.y = __byte_perm(w[2], w[3], 0x6420);
                     }
-                    *reinterpret_cast<uint2*>(sidecar + d.sidecar_off + ((base + (size_t)v * 16) >> 1)) = s2;
+                    if (sidecar) *reinterpret_cast<uint2*>(sidecar + d.sidecar_off + ((base + (size_t)v * 16) >> 1)) = s2;
                     if (count) {
 #pragma unroll
                         for (int k = 0; k < 4; ++k) {
@@ -325,6 +328,7 @@ __global__ void __launch_bounds__(256) byte_histogram_kernel(const uint8_t* __re
 }  // namespace chk
 
 #include "rans_kernels.cuh"
+#include "table_kernels.cuh"
 
 namespace chk {
 

@@ -28,127 +28,121 @@ __device__ __forceinline__ constexpr uint32_t chain_byte(int k) {
     return NV == 4 ? (uint32_t)k : (k == 0 ? (uint32_t)B0 : 3u);
 }
 
-// Device copy of every table of a batch from its 256 normalised frequencies
-// (16-bit, one block of 256 threads per table): the prefix sums, and the encode
-// entry of each symbol exactly as tables.hpp:build_enc_entries computes it.
-__global__ void __launch_bounds__(256) build_tables_kernel(const uint16_t* __restrict__ norm_freq16,
-                                                           EncEntry* __restrict__ enc, uint32_t* __restrict__ freq,
-                                                           uint32_t* __restrict__ cum, uint32_t n_tables) {
-    CHK_SHARED uint32_t warp_tot[8];
-    const uint32_t s = threadIdx.x, lane = s & 31, warp = s >> 5;
-    for (uint32_t t = blockIdx.x; t < n_tables; t += gridDim.x) {
-        const uint32_t f = norm_freq16[(size_t)t * 256 + s];
-        uint32_t v = f;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const uint32_t n = __shfl_up_sync(0xffffffffu, v, o);
-            if (lane >= (uint32_t)o) v += n;
-        }
-        if (lane == 31) warp_tot[warp] = v;
-        __syncthreads();
-        uint32_t before = 0;
-#pragma unroll
-        for (int w = 0; w < 8; ++w)
-            if ((uint32_t)w < warp) before += warp_tot[w];
-        const uint32_t c = before + v - f;  // exclusive prefix
-        freq[(size_t)t * 256 + s] = f;
-        cum[(size_t)t * 257 + s] = c;
-        if (s == 255) cum[(size_t)t * 257 + 256] = c + f;
-        EncEntry e;
-        e.rcp = e.freq_shift = e.bias = e.cmpl = 0;
-        if (f == 1) {
-            e.rcp = 0xFFFFFFFFu;
-            e.freq_shift = 1u;
-            e.bias = c + (kM - 1);
-            e.cmpl = kM - 1;
-        } else if (f > 1) {
-            uint32_t sh = 0;
-            while ((1u << sh) < f) ++sh;
-            const unsigned long long num = 1ull << (31 + sh);
-            e.rcp = (uint32_t)((num + f - 1) / f);
-            e.freq_shift = f | ((sh - 1) << 16);
-            e.bias = c;
-            e.cmpl = kM - f;
-        }
-        enc[(size_t)t * 256 + s] = e;
-        __syncthreads();
-    }
-}
-
-// Shared memory of one encode team: table (256 x 16 B) + a 32-byte output ring
-// per chain.  Ring words are interleaved across the team (word w of thread j's
-// chain k sits at ring[(k*8 + w) * 64 + j]), so a warp never has a bank conflict
-// on it whatever the lanes' positions are.
+// Shared memory of one encode team: table (256 x 8 B) + a 64-byte output ring
+// per chain (two 32-byte blocks).  Ring words are interleaved across the team
+// (word slot s of thread j's chain k sits at byte k*4096 + s*256 + j*4 of the
+// ring area), so a warp never has a bank conflict on it whatever the lanes'
+// positions are.
+constexpr uint32_t kEncRingSlots = 16;                          // words per chain
+constexpr uint32_t kEncRingBytes = kEncRingSlots * kTeam * 4;   // ring area of one chain index
+constexpr uint32_t kEncSlotMask = (kEncRingSlots - 1) * 256u;   // the slot bits of a ring offset
 template <int NV>
 struct EncSmem {
-    uint4 tab[256];
-    uint32_t ring[NV * 8 * kTeam];
+    uint2 tab[256];  // per symbol: rcp | freq << 19 + bias << 5 + shift
+    uint32_t ring[NV * kEncRingSlots * kTeam];
 };
 
 // Output side of one chain.  Emitted bytes are first collected in a 64-bit
 // register pair (newest byte lowest); every two steps a completed 4-byte word
-// moves to the shared-memory ring, and every eight steps a completed 16-byte
-// block moves from the ring to the lane's scratch region.  Streams grow
-// downward in memory, so the oldest byte of a word is its most significant one.
+// moves to the shared-memory ring, and every eight steps a completed 32-byte
+// block -- one whole DRAM sector, so the L2 never has to merge or fill a
+// partly written one -- moves from the ring to the lane's scratch region.
+// Streams grow downward in memory, so the oldest byte of a word is its most
+// significant one and ring slots are filled from the top of a block (slot 7 or
+// 15) downward.  Everything is kept as running offsets so that a step costs no
+// address arithmetic beyond one add.
 struct EncOut {
-    uint32_t lo, hi;    // pending bytes, newest in lo[7:0]
-    uint32_t cnt;       // pending bytes (< 4 after a word check)
-    uint32_t wpos;      // lowest byte position already in the ring (multiple of 4)
-    uint32_t flushed;   // lowest 16-byte block already in global memory
+    uint32_t lo, hi;   // pending bytes, newest in lo[7:0]
+    uint32_t cnt8;     // pending bits (8 per byte; below 32 after a word check)
+    uint32_t soff;     // byte offset in the ring area of the slot the next word goes to
+    uint32_t foff;     // byte offset in the ring area of the block (8 slots) that is flushed next
+    uint32_t wleft;    // words in the ring that are not in global memory yet
+    uint32_t gpos;     // byte position in the lane region the next 32-byte block goes to
 };
 
 __device__ __forceinline__ void enc_emit(EncOut& o, uint32_t v) {  // append byte v[7:0]
     o.hi = __byte_perm(o.hi, o.lo, 0x2107);
     o.lo = __byte_perm(o.lo, v, 0x2104);
-    ++o.cnt;
+    o.cnt8 += 8;
 }
 
 // One encode step of one chain: renormalise (at most two bytes, low byte first)
-// and advance the state.  kEscape = false drops the test for symbols that are
-// missing from the table (the host proves there are none).
+// and advance the state.  The two conditional byte emissions are written as
+// predicated instructions, not branches: in a warp some lane nearly always
+// emits, so a branch would only add its own overhead and a divergent re-issue.
+// kEscape = true adds the test for symbols that are missing from the table
+// (raw escape byte, state untouched); the host proves when there are none.
+// Table entry: 8 bytes, so a warp's random lookups cost half the shared-memory wavefronts of a
+// 16-byte entry (the lookups are what the kernel is bound by).  e.x = reciprocal, e.y = freq in bits
+// 19..31 (so e.y with its low 19 bits cleared is freq * 2^19, the renormalisation bound), bias in bits
+// 5..17, the shift count in bits 0..3 (bit 4 is zero: a funnel shift by e.y shifts by just that count).
 template <bool kEscape>
-__device__ __forceinline__ void enc_step(uint32_t sym, const uint4* tab, uint32_t& x, EncOut& o) {
-    const uint4 e = tab[sym];
-    if (kEscape && e.y == 0) {  // symbol not in the table: raw escape byte, state untouched
+__device__ __forceinline__ void enc_step(uint32_t sym, const uint2* tab, uint32_t& x, EncOut& o) {
+    const uint2 e = tab[sym];
+    if (kEscape && e.y == 0) {
         enc_emit(o, sym);
         return;
     }
-    const uint32_t xmax = e.y << 19;  // freq * 2^19 (the shift field falls off the top)
+    const uint32_t xmax = e.y & 0xFFF80000u;  // freq * 2^19
+#ifdef CHK_CPU_EMULATION
     if (x >= xmax) {
         enc_emit(o, x);
         x >>= 8;
-        if (x >= xmax) {  // a second byte needs freq < 16: rare, so most warps skip this as a whole
-            enc_emit(o, x);
-            x >>= 8;
-        }
     }
-    const uint32_t q = __umulhi(x, e.x) >> (e.y >> 16);
-    x = x + q * e.w + e.z;
+    if (x >= xmax) {  // a second byte needs freq < 16
+        enc_emit(o, x);
+        x >>= 8;
+    }
+#else
+    asm("{\n\t.reg .pred p;\n\t"
+        "setp.hs.u32 p, %0, %4;\n\t"
+        "@p prmt.b32 %1, %1, %2, 0x2107;\n\t"
+        "@p prmt.b32 %2, %2, %0, 0x2104;\n\t"
+        "@p add.u32 %3, %3, 8;\n\t"
+        "@p shr.u32 %0, %0, 8;\n\t"
+        "setp.hs.u32 p, %0, %4;\n\t"
+        "@p prmt.b32 %1, %1, %2, 0x2107;\n\t"
+        "@p prmt.b32 %2, %2, %0, 0x2104;\n\t"
+        "@p add.u32 %3, %3, 8;\n\t"
+        "@p shr.u32 %0, %0, 8;\n\t}"
+        : "+r"(x), "+r"(o.hi), "+r"(o.lo), "+r"(o.cnt8)
+        : "r"(xmax));
+#endif
+    const uint32_t q = __funnelshift_r(__umulhi(x, e.x), 0u, e.y);  // shift count: the low 5 bits of e.y
+    x = x + q * (kM - (e.y >> 19)) + ((e.y >> 5) & 0x1FFFu);
 }
 
 // After at most two steps (4 new bytes, fewer than 8 pending): move one word to the ring.
-__device__ __forceinline__ void enc_word(EncOut& o, uint32_t* ring_col) {
-    if (o.cnt >= 4) {
-        const uint32_t w = __funnelshift_r(o.lo, o.hi, (o.cnt - 4) * 8);
-        o.wpos -= 4;
-        ring_col[((o.wpos >> 2) & 7) * kTeam] = w;
-        o.cnt -= 4;
+__device__ __forceinline__ void enc_word(EncOut& o, uint8_t* ring) {
+    // the oldest four pending bytes; the funnel shift takes its count modulo 32 = cnt8 - 32
+    const uint32_t w = __funnelshift_r(o.lo, o.hi, o.cnt8);
+    if (o.cnt8 >= 32) {
+        *reinterpret_cast<uint32_t*>(ring + o.soff) = w;
+        o.soff = (o.soff & ~kEncSlotMask) | ((o.soff - 256u) & kEncSlotMask);  // next slot down, wrapping inside the ring
+        ++o.wleft;
     }
+    o.cnt8 &= 31u;
 }
 
-// After at most eight steps (16 new bytes in the ring): move the one 16-byte block
-// that may have completed to the lane's scratch region.
-__device__ __forceinline__ void enc_block(EncOut& o, const uint32_t* ring_col, uint8_t* region) {
-    const uint32_t done_to = (o.wpos + 15) >> 4;
-    if (done_to < o.flushed) {
-        const uint32_t b = o.flushed - 1;
-        uint4 v;
-        v.x = ring_col[((b * 4 + 0) & 7) * kTeam];
-        v.y = ring_col[((b * 4 + 1) & 7) * kTeam];
-        v.z = ring_col[((b * 4 + 2) & 7) * kTeam];
-        v.w = ring_col[((b * 4 + 3) & 7) * kTeam];
-        *reinterpret_cast<uint4*>(region + (size_t)b * 16) = v;
-        o.flushed = b;
+// After at most eight steps (16 new bytes in the ring, at most 28 + 16 unflushed): move the
+// one 32-byte block that may have completed to the lane's scratch region.
+__device__ __forceinline__ void enc_block(EncOut& o, const uint8_t* ring, uint8_t* region) {
+    if (o.wleft >= 8) {
+        const uint8_t* b = ring + o.foff;
+        uint4 v0, v1;
+        v0.x = *reinterpret_cast<const uint32_t*>(b);
+        v0.y = *reinterpret_cast<const uint32_t*>(b + 256);
+        v0.z = *reinterpret_cast<const uint32_t*>(b + 512);
+        v0.w = *reinterpret_cast<const uint32_t*>(b + 768);
+        v1.x = *reinterpret_cast<const uint32_t*>(b + 1024);
+        v1.y = *reinterpret_cast<const uint32_t*>(b + 1280);
+        v1.z = *reinterpret_cast<const uint32_t*>(b + 1536);
+        v1.w = *reinterpret_cast<const uint32_t*>(b + 1792);
+        *reinterpret_cast<uint4*>(region + o.gpos) = v0;
+        *reinterpret_cast<uint4*>(region + o.gpos + 16) = v1;
+        o.gpos -= 32;
+        o.foff ^= 2048u;
+        o.wleft -= 8;
     }
 }
 
@@ -157,46 +151,52 @@ __device__ __forceinline__ uint32_t load_row_word(const uint8_t* p, bool aligned
     return (uint32_t)p[0] | ((uint32_t)p[1] << 8) | ((uint32_t)p[2] << 16) | ((uint32_t)p[3] << 24);
 }
 
+// The value lanes of one tensor, encoded by the team into lane regions of d.chunk_stride bytes
+// each starting at `regions` (chain k of thread j uses region j*NV + k).  Returns each chain's
+// final state and the lowest byte position of its stream inside its region.  Ends without a
+// barrier: the caller synchronises before the table and ring are reused.
 template <int NV, int B0, bool kEscape>
-__device__ __forceinline__ void encode_tensor(const TensorDesc& d, uint32_t ti, const EncEntry* __restrict__ tables,
-                                              uint8_t* __restrict__ scratch, LaneHeader* __restrict__ hdrs,
-                                              unsigned long long* __restrict__ lane_src, unsigned char* smem_raw) {
+__device__ __forceinline__ void encode_lanes(const TensorDesc& d, const EncEntry* __restrict__ tables,
+                                             uint8_t* __restrict__ regions, unsigned char* smem_raw,
+                                             uint32_t (&x_out)[NV], uint32_t (&low_out)[NV]) {
     EncSmem<NV>* sm = reinterpret_cast<EncSmem<NV>*>(smem_raw);
+    uint8_t* const ring = reinterpret_cast<uint8_t*>(sm->ring);
     const uint32_t j = threadIdx.x;
     const unsigned long long B = d.n_bytes;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const EncEntry e = tables[(size_t)d.table_idx * 256 + j * 4 + i];
-        sm->tab[j * 4 + i] = make_uint4(e.rcp, e.freq_shift, e.bias, e.cmpl);
+        sm->tab[j * 4 + i] = make_uint2(e.rcp, ((e.freq_shift & 0xFFFFu) << 19) | (e.bias << 5) | (e.freq_shift >> 16));
     }
     __syncthreads();
 
+    const uint32_t S = d.chunk_stride;  // multiple of 32
     uint32_t x[NV];
     EncOut out[NV];
     uint8_t* region[NV];
-    uint32_t* ring[NV];
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
         x[k] = kL;
         out[k].lo = out[k].hi = 0;
-        out[k].cnt = 0;
-        out[k].wpos = d.chunk_stride;
-        out[k].flushed = d.chunk_stride >> 4;
-        region[k] = scratch + d.scratch_off + (size_t)(j * NV + k) * d.chunk_stride;
-        ring[k] = sm->ring + (size_t)k * 8 * kTeam + j;
+        out[k].cnt8 = 0;
+        const uint32_t s0 = ((S >> 2) - 1u) & (kEncRingSlots - 1);  // slot of the first word: the top of its block
+        out[k].soff = (uint32_t)k * kEncRingBytes + s0 * 256u + j * 4u;
+        out[k].foff = (uint32_t)k * kEncRingBytes + (s0 >> 3) * 2048u + j * 4u;
+        out[k].wleft = 0;
+        out[k].gpos = S - 32u;
+        region[k] = regions + (size_t)(j * NV + k) * S;
     }
 
     const unsigned long long full_rows = B >> 8;
     const uint32_t tail = (uint32_t)(B & 255);
     const bool aligned4 = (reinterpret_cast<uintptr_t>(d.src) & 3) == 0;
     const uint8_t* col = d.src + 4 * j;
-
     // One row for all chains of the thread, then (every second row) the word check.
     auto row = [&](uint32_t w, bool word_check) {
 #pragma unroll
         for (int k = 0; k < NV; ++k) {
             enc_step<kEscape>((w >> (8 * chain_byte<NV, B0>(k))) & 0xFF, sm->tab, x[k], out[k]);
-            if (word_check) enc_word(out[k], ring[k]);
+            if (word_check) enc_word(out[k], ring);
         }
     };
 
@@ -206,7 +206,7 @@ __device__ __forceinline__ void encode_tensor(const TensorDesc& d, uint32_t ti, 
         for (int k = 0; k < NV; ++k) {
             const uint32_t t = 4 * j + chain_byte<NV, B0>(k);
             if (t < tail) enc_step<kEscape>(d.src[(full_rows << 8) + t], sm->tab, x[k], out[k]);
-            enc_word(out[k], ring[k]);
+            enc_word(out[k], ring);
         }
     }
     // rows above the last multiple of 8, one at a time: with the partial row at most 8 steps
@@ -217,7 +217,7 @@ __device__ __forceinline__ void encode_tensor(const TensorDesc& d, uint32_t ti, 
         row(load_row_word(col + (r << 8), aligned4), true);
     }
 #pragma unroll
-    for (int k = 0; k < NV; ++k) enc_block(out[k], ring[k], region[k]);
+    for (int k = 0; k < NV; ++k) enc_block(out[k], ring, region[k]);
 
     // full groups of 8 rows, highest first.  The words of the NEXT group are
     // requested before the current group's dependent chains run, so the memory
@@ -239,28 +239,47 @@ __device__ __forceinline__ void encode_tensor(const TensorDesc& d, uint32_t ti, 
 #pragma unroll
         for (int u = 7; u >= 0; --u) row(w[u], (u & 1) == 0);
 #pragma unroll
-        for (int k = 0; k < NV; ++k) enc_block(out[k], ring[k], region[k]);
+        for (int k = 0; k < NV; ++k) enc_block(out[k], ring, region[k]);
     }
 
-    // what is still pending: up to 3 bytes in registers, up to 15 in the ring
+    // what is still pending: up to 3 bytes in registers, up to 7 words in the ring
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
         EncOut& o = out[k];
-        const uint32_t low = o.wpos - o.cnt;  // final lowest byte position of the stream
-        for (uint32_t i = 0; i < o.cnt; ++i)  // oldest pending byte sits highest in memory
-            region[k][o.wpos - 1 - i] = (uint8_t)(o.lo >> ((o.cnt - 1 - i) * 8));
-        for (uint32_t p = o.wpos; p < (o.flushed << 4); p += 4) {
-            const uint32_t w = ring[k][((p >> 2) & 7) * kTeam];
-            *reinterpret_cast<uint32_t*>(region[k] + p) = w;
+        // word i of the unfinished block (oldest first) sits in slot 7 - i of it and belongs at gpos + 4 * (7 - i)
+        for (uint32_t i = 0; i < o.wleft; ++i) {
+            const uint32_t sl = 7u - i;
+            *reinterpret_cast<uint32_t*>(region[k] + o.gpos + 4u * sl) =
+                *reinterpret_cast<const uint32_t*>(ring + o.foff + 256u * sl);
         }
+        const uint32_t top = o.gpos + 32u - 4u * o.wleft;  // lowest byte position written as a whole word
+        const uint32_t cnt = o.cnt8 >> 3;
+        for (uint32_t i = 0; i < cnt; ++i)  // oldest pending byte sits highest in memory
+            region[k][top - 1 - i] = (uint8_t)(o.lo >> ((cnt - 1 - i) * 8));
+        x_out[k] = x[k];
+        low_out[k] = top - cnt;  // final lowest byte position of the stream
+    }
+}
+
+// Stand-alone stage: lanes to scratch, provisional headers and byte locations to global memory
+// (offsets and the gather follow in lane_scan_kernel / tensor_scan_kernel / compact_kernel).
+template <int NV, int B0, bool kEscape>
+__device__ __forceinline__ void encode_tensor(const TensorDesc& d, uint32_t ti, const EncEntry* __restrict__ tables,
+                                              uint8_t* __restrict__ scratch, LaneHeader* __restrict__ hdrs,
+                                              unsigned long long* __restrict__ lane_src, unsigned char* smem_raw) {
+    uint32_t x[NV], low[NV];
+    encode_lanes<NV, B0, kEscape>(d, tables, scratch + d.scratch_off, smem_raw, x, low);
+    const uint32_t j = threadIdx.x;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
         const uint32_t t = 4 * j + chain_byte<NV, B0>(k);
         LaneHeader h;
         h.final_state = x[k];
-        h.byte_count = d.chunk_stride - low;
+        h.byte_count = d.chunk_stride - low[k];
         h.buf_offset = 0;
         h.pad = 0;
         hdrs[(size_t)ti * kLanes + t] = h;
-        lane_src[(size_t)ti * kLanes + t] = d.scratch_off + (unsigned long long)(j * NV + k) * d.chunk_stride + low;
+        lane_src[(size_t)ti * kLanes + t] = d.scratch_off + (unsigned long long)(j * NV + k) * d.chunk_stride + low[k];
     }
     __syncthreads();  // table and ring are reused by the next tensor
 }
@@ -309,7 +328,88 @@ __global__ void __launch_bounds__(kTeam) rans_encode_kernel(const TensorDesc* __
 // in the header and byte location of each of the tensor's zero lanes: a lane
 // with c_max symbols owns the whole string, one with c_max-1 owns its suffix.
 // Runs next to the value-lane kernel (it touches different lanes and regions).
-__global__ void __launch_bounds__(128) zero_lane_kernel(const TensorDesc* __restrict__ descs,
+struct ZeroChain {
+    uint32_t state0, nbytes0;  // after c_max symbols
+    uint32_t state1, nbytes1;  // after c_max - 1 symbols (a suffix of the same byte string)
+};
+// Encodes c_max zeros with table entry e, bytes written downward from region + stride
+// (a multiple of 4; region 4-byte aligned).  One thread, one dependent chain: emitted bytes are
+// collected four at a time so that the chain is not held up by a store per byte.
+__device__ __forceinline__ ZeroChain zero_chain(const EncEntry e, uint8_t* __restrict__ region, uint32_t stride,
+                                                unsigned long long c_max) {
+    const uint32_t f = e.freq_shift & 0xFFFFu, sh = e.freq_shift >> 16, xmax = e.freq_shift << 19;
+    ZeroChain z;
+    if (f == 0) {  // symbol 0 is not in the table: every zero is a raw escape byte and the state never moves
+        for (unsigned long long i = 0; i < c_max; ++i) region[stride - 1 - i] = 0;
+        z.state0 = z.state1 = kL;
+        z.nbytes0 = (uint32_t)c_max;
+        z.nbytes1 = c_max ? (uint32_t)c_max - 1u : 0u;
+        return z;
+    }
+    uint32_t x = kL, acc = 0, nacc = 0, emitted = 0;
+    uint8_t* wp = region + stride;  // the next word goes below this
+    // One step.  This thread's time is one chain of dependent operations (compare, shift, multiply-high,
+    // shift, multiply-add), so nothing in it may branch: with freq >= 16 a symbol emits at most one byte
+    // and everything conditional is a predicated instruction.
+    auto step = [&]() {
+#ifndef CHK_CPU_EMULATION
+        if (f >= 16) {
+            asm volatile(
+                "{\n\t.reg .pred p, q;\n\t.reg .u32 t;\n\t"
+                "setp.hs.u32 p, %0, %5;\n\t"
+                "@p prmt.b32 %1, %0, %1, 0x6540;\n\t"  // acc = acc << 8 | low byte of x: the newest byte is the lowest in memory
+                "@p shr.u32 %0, %0, 8;\n\t"
+                "@p add.u32 %2, %2, 1;\n\t"
+                "@p add.u32 %3, %3, 1;\n\t"
+                "setp.eq.u32 q, %3, 4;\n\t"
+                "@q sub.u64 %4, %4, 4;\n\t"
+                "@q st.global.u32 [%4], %1;\n\t"
+                "@q mov.u32 %3, 0;\n\t"
+                "mul.hi.u32 t, %0, %6;\n\t"
+                "shr.u32 t, t, %7;\n\t"
+                "mad.lo.u32 %0, t, %8, %0;\n\t"
+                "add.u32 %0, %0, %9;\n\t}"
+                : "+r"(x), "+r"(acc), "+r"(emitted), "+r"(nacc), "+l"(wp)
+                : "r"(xmax), "r"(e.rcp), "r"(sh), "r"(e.cmpl), "r"(e.bias)
+                : "memory");
+            return;
+        }
+#endif
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {  // at most two bytes per symbol
+            if (x >= xmax) {
+                acc = (acc << 8) | (x & 0xFFu);  // the newest byte is the lowest in memory
+                x >>= 8;
+                ++emitted;
+                if (++nacc == 4) {
+                    wp -= 4;
+                    *reinterpret_cast<uint32_t*>(wp) = acc;
+                    nacc = 0;
+                }
+            }
+        }
+        const uint32_t q = __umulhi(x, e.rcp) >> sh;
+        x = x + q * e.cmpl + e.bias;
+    };
+    const uint32_t n1 = c_max ? (uint32_t)(c_max - 1) : 0u;  // c_max < 2^24: a tensor is smaller than 4 GiB
+    uint32_t i = 0;
+    for (; i + 4 <= n1; i += 4) {
+        step();
+        step();
+        step();
+        step();
+    }
+    for (; i < n1; ++i) step();
+    z.state1 = c_max ? x : kL;
+    z.nbytes1 = emitted;
+    if (c_max) step();
+    z.state0 = x;
+    z.nbytes0 = emitted;
+    for (uint32_t k = 0; k < nacc; ++k) (wp - nacc)[k] = (uint8_t)(acc >> (8 * k));  // up to three bytes left
+    return z;
+}
+
+__global__ void __launch_bounds__(32) zero_lane_kernel(const TensorDesc* __restrict__ descs,
                                                         const EncEntry* __restrict__ tables,
                                                         uint8_t* __restrict__ scratch,
                                                         LaneHeader* __restrict__ hdrs,
@@ -319,42 +419,17 @@ __global__ void __launch_bounds__(128) zero_lane_kernel(const TensorDesc* __rest
     if (ti >= n_tensors) return;
     const TensorDesc d = descs[ti];
     if (d.spe * 2 != d.es) return;  // integer tensors have no zeroed bytes
-    const EncEntry e = tables[(size_t)d.table_idx * 256];
-    const uint32_t f = e.freq_shift & 0xFFFFu, sh = e.freq_shift >> 16, xmax = e.freq_shift << 19;
     const unsigned long long zbase = d.scratch_off + (unsigned long long)kTeam * 2 * d.chunk_stride;
-    uint8_t* const region = scratch + zbase;
-    uint32_t wpos = d.chunk_stride, x = kL;
-    uint32_t state1 = kL, nbytes1 = 0;  // after c_max - 1 symbols
     const unsigned long long c_max = (d.n_bytes + kLanes - 1) / kLanes;
-    for (unsigned long long i = 1; i <= c_max; ++i) {
-        if (f == 0) {
-            region[--wpos] = 0;
-        } else {
-            if (x >= xmax) {
-                region[--wpos] = (uint8_t)x;
-                x >>= 8;
-                if (x >= xmax) {
-                    region[--wpos] = (uint8_t)x;
-                    x >>= 8;
-                }
-            }
-            const uint32_t q = __umulhi(x, e.rcp) >> sh;
-            x = x + q * e.cmpl + e.bias;
-        }
-        if (i + 1 == c_max) {
-            state1 = x;
-            nbytes1 = d.chunk_stride - wpos;
-        }
-    }
-    const uint32_t state0 = x, nbytes0 = d.chunk_stride - wpos;
+    const ZeroChain z = zero_chain(tables[(size_t)d.table_idx * 256], scratch + zbase, d.chunk_stride, c_max);
     for (uint32_t t = 0; t < kLanes; ++t) {
         if ((t % d.es) >= d.spe) continue;
         const unsigned long long cnt = d.n_bytes > t ? (d.n_bytes - t + kLanes - 1) / kLanes : 0;
         LaneHeader h;
         h.buf_offset = 0;
         h.pad = 0;
-        h.final_state = cnt == 0 ? kL : (cnt == c_max ? state0 : state1);
-        h.byte_count = cnt == 0 ? 0u : (cnt == c_max ? nbytes0 : nbytes1);
+        h.final_state = cnt == 0 ? kL : (cnt == c_max ? z.state0 : z.state1);
+        h.byte_count = cnt == 0 ? 0u : (cnt == c_max ? z.nbytes0 : z.nbytes1);
         hdrs[(size_t)ti * kLanes + t] = h;
         lane_src[(size_t)ti * kLanes + t] = zbase + d.chunk_stride - h.byte_count;
     }
@@ -443,6 +518,47 @@ __global__ void __launch_bounds__(1024) tensor_scan_kernel(TensorDesc* __restric
     }
 }
 
+// One warp copies cnt bytes from s to o (neither aligned): 16 bytes per thread per step once the
+// destination is aligned (funnel-shifted source words), kPieces pieces per thread in flight so a
+// warp keeps kPieces x 512 bytes on their way.
+template <int kPieces>
+__device__ __forceinline__ void warp_copy(uint8_t* __restrict__ o, const uint8_t* __restrict__ s, uint32_t cnt,
+                                          uint32_t lane) {
+    uint32_t head = (uint32_t)((16 - (reinterpret_cast<uintptr_t>(o) & 15)) & 15);
+    if (head > cnt) head = cnt;
+    if (lane < head) o[lane] = s[lane];
+    const uint32_t nvec = (cnt - head) >> 4;
+    const uint8_t* sv = s + head;
+    uint8_t* ov = o + head;
+    const uint32_t mis = (uint32_t)(reinterpret_cast<uintptr_t>(sv) & 3);
+    const uint32_t* sw = reinterpret_cast<const uint32_t*>(sv - mis);
+    for (uint32_t v0 = lane; v0 < nvec; v0 += 32 * kPieces) {
+        uint32_t a[kPieces][5];
+#pragma unroll
+        for (int u = 0; u < kPieces; ++u) {
+            const uint32_t v = v0 + 32 * u;
+            if (v < nvec) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) a[u][i] = sw[v * 4 + i];
+                a[u][4] = mis ? sw[v * 4 + 4] : 0u;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kPieces; ++u) {
+            const uint32_t v = v0 + 32 * u;
+            if (v < nvec) {
+                uint4 r;
+                r.x = __funnelshift_r(a[u][0], a[u][1], mis * 8);
+                r.y = __funnelshift_r(a[u][1], a[u][2], mis * 8);
+                r.z = __funnelshift_r(a[u][2], a[u][3], mis * 8);
+                r.w = __funnelshift_r(a[u][3], a[u][4], mis * 8);
+                *reinterpret_cast<uint4*>(ov + (size_t)v * 16) = r;
+            }
+        }
+    }
+    for (uint32_t i = head + (nvec << 4) + lane; i < cnt; i += 32) o[i] = s[i];
+}
+
 // Gather (src/ANSCompressor.cpp:225-238): one warp per (tensor, lane) moves that
 // lane's bytes from scratch to their place in the data section, 16 bytes per
 // thread per step once the destination is aligned.  A passthrough tensor instead
@@ -469,44 +585,266 @@ __global__ void __launch_bounds__(256) compact_kernel(const TensorDesc* __restri
                 out[i] = (i % d.es) < d.spe ? (uint8_t)0 : d.src[i];
             continue;
         }
-        const uint32_t cnt = hdrs[(size_t)ti * kLanes + t].byte_count;
-        const uint8_t* s = scratch + lane_src[(size_t)ti * kLanes + t];
-        uint8_t* o = out + lane_off[(size_t)ti * kLanes + t];
-        uint32_t head = (uint32_t)((16 - (reinterpret_cast<uintptr_t>(o) & 15)) & 15);
-        if (head > cnt) head = cnt;
-        if (lane < head) o[lane] = s[lane];
-        const uint32_t nvec = (cnt - head) >> 4;
-        const uint8_t* sv = s + head;
-        uint8_t* ov = o + head;
-        const uint32_t mis = (uint32_t)(reinterpret_cast<uintptr_t>(sv) & 3);
-        const uint32_t* sw = reinterpret_cast<const uint32_t*>(sv - mis);
-        // four 16-byte pieces per thread and step: all their loads are issued before the first
-        // is used, so a warp keeps 2 KiB in flight instead of 512 bytes
-        for (uint32_t v0 = lane; v0 < nvec; v0 += 128) {
-            uint32_t a[4][5];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const uint32_t v = v0 + 32 * u;
-                if (v < nvec) {
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) a[u][i] = sw[v * 4 + i];
-                    a[u][4] = mis ? sw[v * 4 + 4] : 0u;
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const uint32_t v = v0 + 32 * u;
-                if (v < nvec) {
-                    uint4 r;
-                    r.x = __funnelshift_r(a[u][0], a[u][1], mis * 8);
-                    r.y = __funnelshift_r(a[u][1], a[u][2], mis * 8);
-                    r.z = __funnelshift_r(a[u][2], a[u][3], mis * 8);
-                    r.w = __funnelshift_r(a[u][3], a[u][4], mis * 8);
-                    *reinterpret_cast<uint4*>(ov + (size_t)v * 16) = r;
-                }
-            }
+        warp_copy<4>(out + lane_off[(size_t)ti * kLanes + t], scratch + lane_src[(size_t)ti * kLanes + t],
+                  hdrs[(size_t)ti * kLanes + t].byte_count, lane);
+    }
+}
+
+// ------------------------------------------------------------------ shared symbol-0 chains of a batch
+// The symbol-0 chain of a tensor depends on nothing but the table entry of symbol 0 and the
+// number of symbols per lane.  Half of a float tensor's codec input is zeroed bytes, so that
+// entry is the same (frequency 2048, give or take one) for nearly every tensor of a checkpoint,
+// and a batch of thousands of tensors has a handful of distinct chains.  zero_chain_kernel
+// computes each distinct chain once: one warp per tensor, lane 0 looks its key up in a small
+// open-addressing table (an atomicCAS on the key claims a free slot), the first to claim a slot
+// computes the chain into the slot's region, every tensor records its slot; nothing waits.  A chain is
+// 16384 dependent steps for a 4 MiB tensor -- about a millisecond for one thread however it is
+// written -- which is why it is taken out of the encode teams' path.  Tensors that find the
+// table full get slot -1 and their team computes the chain itself.
+struct ZeroSlot {
+    // c_max << 32 | frequency and shift of symbol 0 (top bit set; 0 = free).  Symbol 0 is the first symbol, so
+    // its cumulative frequency is 0 and the rest of its table entry follows from the frequency.
+    unsigned long long key;
+    ZeroChain chain;
+};
+
+__global__ void __launch_bounds__(32) zero_chain_kernel(const TensorDesc* __restrict__ descs,
+                                                        const EncEntry* __restrict__ tables,
+                                                        ZeroSlot* __restrict__ slots, uint32_t n_slots,
+                                                        uint8_t* __restrict__ regions, uint32_t region_stride,
+                                                        int32_t* __restrict__ slot_of, uint32_t n_tensors) {
+    const uint32_t ti = blockIdx.x;
+    if (ti >= n_tensors || threadIdx.x != 0) return;
+    const TensorDesc d = descs[ti];
+    if (d.spe * 2 != d.es) {  // integer tensors have no zeroed bytes
+        slot_of[ti] = -1;
+        return;
+    }
+    const EncEntry e = tables[(size_t)d.table_idx * 256];
+    const unsigned long long c_max = (d.n_bytes + kLanes - 1) / kLanes;
+    const unsigned long long key = (c_max << 32) | e.freq_shift | (1ull << 63);  // never 0
+    uint32_t h = (uint32_t)((key * 0x9E3779B97F4A7C15ull) >> 40) % n_slots;
+    int32_t found = -1;
+    for (uint32_t probe = 0; probe < n_slots && found < 0; ++probe, h = h + 1 == n_slots ? 0 : h + 1) {
+        const unsigned long long prev = atomicCAS(&slots[h].key, 0ull, key);
+        if (prev == 0ull) {  // claimed: this thread computes the chain (nobody reads it before the kernel has ended)
+            slots[h].chain = zero_chain(e, regions + (size_t)h * region_stride, d.chunk_stride, c_max);
+            found = (int32_t)h;
+        } else if (prev == key) {
+            found = (int32_t)h;
         }
-        for (uint32_t i = head + (nvec << 4) + lane; i < cnt; i += 32) o[i] = s[i];
+    }
+    slot_of[ti] = found;
+}
+
+// ------------------------------------------------------------------ encode + offsets + gather in one kernel
+// rans_encode_fused_kernel does for each tensor what rans_encode_kernel, zero_lane_kernel,
+// lane_scan_kernel and compact_kernel do for a batch, inside the team that encodes it: value
+// lanes into the team's OWN scratch slot (one slot per resident team, reused from tensor to
+// tensor, so the scratch a batch needs is teams x largest tensor instead of the whole batch),
+// the shared symbol-0 chain, the prefix sum of the 256 lane lengths
+// (src/ANSCompressor.cpp:647-651), the passthrough rule and final headers (:686-713), and the
+// gather of the lanes into one contiguous payload (:225-238).
+//
+// Where that payload goes: the data section of the file wants the tensors in index order, so
+// the place of tensor i depends on the sizes of all tensors before it -- which other teams are
+// still producing.  Waiting for them would make the teams march in step (every team of a wave
+// waiting for the slowest one before any gathers).  Instead the device payload is a heap: a team
+// takes the next free range with one atomic add, records it in the descriptor, and gathers at
+// once, while the other teams of its SM keep the issue slots busy with their chains -- which is
+// how the memory-bound gather hides under the issue-bound encoding.  The decoder follows the
+// descriptors, so it does not care about the order; the file order is restored where the
+// payloads leave the device (one copy per tensor into its place in the file image).
+constexpr uint32_t kPayloadAlign = 32;  // heap ranges start on a DRAM sector
+
+struct FusedInfo {  // per tensor, overlaid on the ring area once the lanes are encoded
+    uint32_t cnt[kLanes];   // bytes of lane t
+    uint32_t src[kLanes];   // where they start: offset in the team's scratch slot, or (top bit set) in the shared zero chain
+    uint32_t dst[kLanes];   // where they go, relative to the tensor's payload
+    uint32_t fin[kLanes];   // final state of lane t
+    uint32_t warp_tot[2];
+    unsigned long long payload_off;
+    ZeroChain zero;
+};
+
+constexpr uint32_t kSrcSharedChain = 0x80000000u;
+
+#ifdef CHK_CPU_EMULATION
+#define CHK_NOINLINE
+#else
+#define CHK_NOINLINE __noinline__
+#endif
+
+// Everything after the value lanes of a tensor are in the team's slot (their lengths, positions and final
+// states already in `info`).  Kept out of line so that its registers do not add to those of the encode loop.
+// Everything the one-kernel path needs, passed as one kernel parameter: it stays in the constant
+// bank and is read where it is used instead of being carried in registers through the encode loop.
+struct FusedParams {
+    TensorDesc* descs;
+    const EncEntry* tables;
+    uint8_t* scratch;                  // one slot of slot_bytes per team
+    unsigned long long slot_bytes;
+    const ZeroSlot* zero_slots;        // the batch's shared symbol-0 chains (zero_chain_kernel)
+    const uint8_t* zero_regions;
+    const int32_t* zero_slot_of;       // may be null: every team then computes its own chain
+    uint32_t zero_region_stride;
+    uint32_t n_tensors;
+    LaneHeader* hdrs;
+    uint8_t* payload;                  // the payload heap
+    unsigned long long* payload_size;  // per tensor
+    unsigned long long* heap_cursor;
+    const uint32_t* order;
+    uint32_t* ticket;
+};
+
+// Everything after the value lanes of a tensor are in the team's slot (their lengths, positions and final
+// states already in `info`).  Kept out of line so that its registers do not add to those of the encode loop.
+__device__ CHK_NOINLINE void finish_tensor(const FusedParams& P, uint32_t ti, bool floats, uint8_t* __restrict__ slot,
+                                           FusedInfo* info) {
+    const TensorDesc d = P.descs[ti];
+    const uint32_t j = threadIdx.x, lane = j & 31, warp = j >> 5;
+    const uint32_t S = d.chunk_stride;
+    const unsigned long long B = d.n_bytes;
+    const uint8_t* shared_chain = nullptr;
+    if (floats) {
+        // the symbol-0 chain that all lanes of zeroed low bytes share: from the batch's cache, or (cache full)
+        // computed here by one thread into the region after the value lanes
+        uint32_t zbase = 2u * kTeam * S;
+        const unsigned long long c_max = (B + kLanes - 1) / kLanes;
+        const int32_t zs = P.zero_slot_of ? P.zero_slot_of[ti] : -1;
+        if (zs >= 0) {
+            if (j == 0) info->zero = P.zero_slots[zs].chain;
+            shared_chain = P.zero_regions + (size_t)zs * P.zero_region_stride;
+            zbase = kSrcSharedChain;
+        } else if (j == 0) {
+            info->zero = zero_chain(P.tables[(size_t)d.table_idx * 256], slot + zbase, S, c_max);
+        }
+        __syncthreads();
+        const ZeroChain z = info->zero;
+#pragma unroll
+        for (uint32_t b = 0; b < 4; ++b) {
+            const uint32_t t = 4 * j + b;
+            if ((t % d.es) >= d.spe) continue;  // a value lane
+            const unsigned long long n = B > t ? (B - t + kLanes - 1) / kLanes : 0;
+            const uint32_t c = n == 0 ? 0u : (n == c_max ? z.nbytes0 : z.nbytes1);
+            info->cnt[t] = c;
+            info->fin[t] = n == 0 ? kL : (n == c_max ? z.state0 : z.state1);
+            info->src[t] = zbase + S - c;
+        }
+    }
+
+    // ---- the prefix sum of the lane lengths, the passthrough decision, the final headers
+    uint32_t cnt[4];
+#pragma unroll
+    for (uint32_t b = 0; b < 4; ++b) cnt[b] = info->cnt[4 * j + b];
+    const uint32_t mine = cnt[0] + cnt[1] + cnt[2] + cnt[3];
+    uint32_t inc = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t n = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= (uint32_t)o) inc += n;
+    }
+    if (lane == 31) info->warp_tot[warp] = inc;
+    __syncthreads();
+    const uint32_t total = info->warp_tot[0] + info->warp_tot[1];
+    uint32_t off = (warp ? info->warp_tot[0] : 0u) + inc - mine;
+    const bool raw = (unsigned long long)total >= B;
+    const unsigned long long size = raw ? B : (unsigned long long)total;
+    if (j == 0) {  // the tensor's range of the payload heap
+        const unsigned long long at = atomicAdd(P.heap_cursor, (size + kPayloadAlign - 1) & ~(unsigned long long)(kPayloadAlign - 1));
+        info->payload_off = at;
+        P.payload_size[ti] = size;
+        P.descs[ti].payload_off = at;
+        P.descs[ti].flags = raw ? (d.flags | kFlagRaw) : (d.flags & ~kFlagRaw);
+    }
+#pragma unroll
+    for (uint32_t b = 0; b < 4; ++b) {
+        const uint32_t t = 4 * j + b;
+        LaneHeader h;
+        h.pad = 0;
+        if (raw) {
+            h.final_state = 0;
+            h.byte_count = t == 0 ? (uint32_t)B : 0u;
+            h.buf_offset = 0;
+        } else {
+            h.final_state = info->fin[t];
+            h.byte_count = cnt[b];
+            h.buf_offset = off;
+        }
+        P.hdrs[(size_t)ti * kLanes + t] = h;
+        info->dst[t] = off;
+        off += cnt[b];
+    }
+    __syncthreads();
+
+    // ---- gather: lanes side by side in lane order, or the masked tensor itself
+    uint8_t* out = P.payload + info->payload_off;
+    if (raw) {
+        for (unsigned long long i = j; i < B; i += kTeam) out[i] = (i % d.es) < d.spe ? (uint8_t)0 : d.src[i];
+    } else {
+        for (uint32_t t = warp; t < kLanes; t += 2) {
+            const uint32_t sr = info->src[t];
+            warp_copy<4>(out + info->dst[t], (sr & kSrcSharedChain) ? shared_chain + (sr & ~kSrcSharedChain) : slot + sr,
+                         info->cnt[t], lane);
+        }
+    }
+    __syncthreads();  // table and lane table are reused by the next tensor
+}
+
+template <int NV, int B0>
+__device__ __forceinline__ void encode_tensor_fused(const FusedParams& P, uint32_t ti, uint8_t* __restrict__ slot,
+                                                    unsigned char* smem_raw) {
+    const uint32_t j = threadIdx.x;
+    uint32_t x[NV], low[NV];
+    uint32_t S;
+    {
+        const TensorDesc d = P.descs[ti];
+        S = d.chunk_stride;
+        encode_lanes<NV, B0, false>(d, P.tables, slot, smem_raw, x, low);
+    }
+    __syncthreads();  // the ring is free: its area now holds the per-tensor lane table
+    FusedInfo* info = reinterpret_cast<FusedInfo*>(reinterpret_cast<EncSmem<NV>*>(smem_raw)->ring);
+    static_assert(sizeof(FusedInfo) <= sizeof(uint32_t) * 2 * kEncRingSlots * kTeam, "lane table must fit the ring area");
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const uint32_t t = 4 * j + chain_byte<NV, B0>(k);
+        info->cnt[t] = S - low[k];
+        info->fin[t] = x[k];
+        info->src[t] = (j * NV + (uint32_t)k) * S + low[k];
+    }
+    __syncthreads();
+    finish_tensor(P, ti, NV == 2, slot, info);
+}
+
+// One team per tensor.  Tensors are handed out through a ticket counter in the order given by
+// P.order (largest first), so the persistent grid drains the batch without a ragged last wave.
+#ifndef CHK_ENC_MINBLOCKS
+#define CHK_ENC_MINBLOCKS 12
+#endif
+#ifdef CHK_CPU_EMULATION
+#define CHK_GRID_CONSTANT
+#else
+#define CHK_GRID_CONSTANT __grid_constant__
+#endif
+template <bool kInts>
+__global__ void __launch_bounds__(kTeam, kInts ? 1 : CHK_ENC_MINBLOCKS) rans_encode_fused_kernel(
+    const CHK_GRID_CONSTANT FusedParams P) {
+    CHK_DYN_SMEM(smem);
+    CHK_SHARED uint32_t s_ticket;
+    uint8_t* const slot = P.scratch + (unsigned long long)blockIdx.x * P.slot_bytes;
+    for (;;) {
+        const uint32_t tk = next_ticket(P.ticket, &s_ticket);
+        if (tk >= P.n_tensors) break;
+        const uint32_t ti = P.order[tk];
+        const uint32_t es = P.descs[ti].es, spe = P.descs[ti].spe;
+        if (es == 4 && spe == 2)
+            encode_tensor_fused<2, 2>(P, ti, slot, smem);
+        else if (es == 2 && spe == 1)
+            encode_tensor_fused<2, 1>(P, ti, slot, smem);
+        else if (kInts)
+            encode_tensor_fused<4, 0>(P, ti, slot, smem);
+        else
+            __syncthreads();  // keep the barrier count uniform
     }
 }
 
@@ -809,8 +1147,11 @@ __device__ __forceinline__ void decode_tensor(const TensorDesc& d, uint32_t ti,
 // One team (CTA of 64 threads) per tensor.  Each thread rebuilds one 32-bit word
 // of every row from its decoded bytes and the sidecar and stores it directly.
 // kInts as for the encoder; TL selects the table shape.
+#ifndef CHK_DEC_MINBLOCKS
+#define CHK_DEC_MINBLOCKS 1
+#endif
 template <bool kInts, bool TL>
-__global__ void __launch_bounds__(kTeam) rans_decode_kernel(const TensorDesc* __restrict__ descs,
+__global__ void __launch_bounds__(kTeam, CHK_DEC_MINBLOCKS) rans_decode_kernel(const TensorDesc* __restrict__ descs,
                                                             const uint32_t* __restrict__ freq_tables,  // [T][256]
                                                             const uint32_t* __restrict__ cum_tables,   // [T][257]
                                                             const LaneHeader* __restrict__ hdrs,

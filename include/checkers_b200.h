@@ -31,7 +31,7 @@ extern "C" {
 #define CHK_ERR_IO (-3)       /* file could not be read or written */
 #define CHK_ERR_FORMAT (-4)   /* file contents are not a valid checkpoint */
 #define CHK_ERR_DECODE (-5)   /* a stream failed its end-state / length check */
-#define CHK_ERR_TIMEOUT (-6)  /* a bounded device-side wait ran out */
+#define CHK_ERR_UNDECODABLE (-6) /* shared tables that do not sum to 4096: the files could not be restored */
 #define CHK_ERR_CAPACITY (-7) /* a size exceeds a stated fixed limit */
 
 /* DataType tags, include/checkers/TensorResource.hpp:30-37 */
@@ -62,6 +62,15 @@ const char* chk_last_error(void);
  * MemoryManager::submit_tensor src/MemoryManager.cpp:218-250).  Records keep
  * submission order, which is the order of every output file. */
 int chk_context_create(int device, int rank, int local_rank, chk_context** out);
+/* The same with a bound on the context's encode workspace (the reference sizes its buffers per tensor,
+ * src/ANSCompressor.cpp:348-388, and its statistics slabs per batch, src/MemoryManager.cpp:692-707; here the
+ * one pool that grows with the work is the encoder's scratch).  Compression keeps one scratch slot -- twice
+ * the largest tensor's codec input, the worst case of its 256 lanes -- per resident encode team; with
+ * workspace_bytes > 0 fewer teams run so that their slots fit (slower, same bytes); a bound smaller than
+ * one slot makes chk_compress return CHK_ERR_CAPACITY.  0 = no bound: one slot for every team the device
+ * can hold (about 7.5 GB on a B200 for tensors of 4 MiB).  The compressed outputs -- the sidecar section
+ * and the payload heap, sized for the worst case of one byte per input byte -- are not workspace. */
+int chk_context_create_ex(int device, int rank, int local_rank, uint64_t workspace_bytes, chk_context** out);
 int chk_context_destroy(chk_context* ctx);
 int chk_reset(chk_context* ctx); /* MemoryManager::reset: forget tensors, clusters, results */
 int chk_set_histogram_bins(chk_context* ctx, uint32_t bins); /* initialize_context(histogram_bins=) */
@@ -70,16 +79,15 @@ int chk_register_tensor(chk_context* ctx, const char* name, const void* device_p
 int chk_tensor_count(chk_context* ctx, uint64_t* count);
 /* Options: "repair_tables" (0/1; shared tables are renormalised until they sum
  * to 4096 -- a deviation from the reference that keeps them decodable),
- * "verify_zero_lanes" (0/1; decode also checks the lanes that only carry
- * zeroed low bytes), "host_threads" (threads for table normalisation, 0 = all),
- * "decode_two_level" (0/1; 5 KiB two-level decode table instead of 16 KiB),
- * "segments" (1..8, default 3: pieces a batch of 512 tensors or more is cut into so
- * that counting, encoding and compaction of neighbouring pieces overlap on the
- * device; 1 runs the stages one after the other), "encode_teams_per_sm" (default
- * 0 = as many as fit: cap on the resident encode teams per SM of one launch),
- * "first_segment_pct" (0..90, default 0 = equal shares: size of the first piece),
- * "encode_after_count" (0/1: encode grids start only once the whole batch has been
- * counted).  None of the tuning options changes the bytes that are produced. */
+ * "allow_undecodable" (0/1; see chk_compress_and_save), "verify_zero_lanes" (0/1;
+ * decode also checks the lanes that only carry zeroed low bytes),
+ * "workspace_bytes" (bound on the encode scratch, as in chk_context_create_ex),
+ * "segments" (1..8, default 4: launches the counting of a batch of 512 tensors or
+ * more is cut into, so that the tables of one piece are built while the next is
+ * counted), "encode_teams_per_sm" / "decode_teams_per_sm" (default 0 = as many as
+ * fit: cap on the resident teams per SM), "decode_two_level" (0/1; 5 KiB two-level
+ * decode table instead of 16 KiB).  None of the tuning options changes the bytes
+ * that are produced. */
 int chk_set_option(chk_context* ctx, const char* key, int64_t value);
 
 /* ---- analysis: checkers::analyze_tensors, src/api.cpp:1033-1253 ----------
@@ -101,6 +109,15 @@ int chk_set_cluster_info(chk_context* ctx, uint64_t n, const char* const* names,
  * writes <dir>/rank_<r>_states.ansc, <dir>/mantissa/rank_<r>_mantissa.mant and
  * <dir>/tables/rank_<r>_tables.dict in the reference's layout (:751-931). */
 int chk_compress_and_save(chk_context* ctx, const char* output_dir);
+/* Tables of the last compression and how many of them do not sum to 4096.  The reference builds the
+ * table a cluster shares over the full alphabet and takes the surplus back in a single pass
+ * (src/ANSCompressor.cpp:477-482); for low-entropy data (every bf16 tensor) the sum stays above 4096,
+ * the streams are not decodable, and the reference itself writes past its decode arrays (:495-499).
+ * Such files are reproduced bit for bit on request, but never silently: chk_compress_and_save returns
+ * CHK_ERR_UNDECODABLE before writing anything unless "allow_undecodable" is set (reference-exact bytes) --
+ * or "repair_tables" makes the tables valid.  Without clusters (no chk_analyze / chk_set_cluster_info)
+ * every tensor owns its table and the case cannot arise. */
+int chk_get_table_report(chk_context* ctx, uint64_t* n_tables, uint64_t* n_undecodable);
 /* Same pipeline, results kept in memory.  host_images != 0 also builds the
  * three file images in pinned host memory (fetch with chk_get_image);
  * otherwise the compressed state stays on the device for chk_decompress_resident. */
@@ -134,7 +151,8 @@ int chk_normalize_histogram(const uint32_t hist[256], int ensure_full_alphabet, 
                             uint32_t cum_freq[257], uint32_t x_max[256], uint32_t* sum_out);
 
 /* ---- timing: the reference's [TIMING] / per-tensor ms fields -------------
- * Keys: split_hist_ms, table_ms, encode_ms, compact_ms, compress_device_ms,
+ * Keys: split_hist_ms (counting), table_ms (what of the table building the counting did not hide),
+ * encode_ms (lanes, offsets and gather: one kernel), compress_device_ms, encode_teams, workspace_mb,
  * d2h_ms, io_ms, compress_total_ms, h2d_ms, decode_ms, decompress_total_ms,
  * analyze_stats_ms, analyze_cluster_ms.  Device spans are CUDA-event times. */
 int chk_get_timing(chk_context* ctx, const char* key, double* ms);

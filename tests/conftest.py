@@ -10,6 +10,12 @@ for p in (ROOT, HERE):
         sys.path.insert(0, p)
 
 
+# the front end writes the reference's per-rank log (./logs/<run id>/rank_<r>/checkers.log): keep it out of the tree
+import tempfile  # noqa: E402
+
+os.environ.setdefault("CHECKERS_LOG_DIR", tempfile.mkdtemp(prefix="checkers_logs_"))
+
+
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run on the B200 box)")
 

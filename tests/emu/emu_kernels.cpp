@@ -35,7 +35,7 @@ Batch make_batch(size_t n, const uint8_t* const* srcs, uint8_t* const* dsts, con
         d.sidecar_off = b.sidecar_total;
         d.scratch_off = b.scratch_total;
         const unsigned long long c_max = (d.n_bytes + 255) / 256;
-        d.chunk_stride = (uint32_t)((2 * c_max + 15) & ~15ull);
+        d.chunk_stride = (uint32_t)((2 * c_max + 31) & ~31ull);
         d.flags = 0;
         if (!need_hist || need_hist[i]) d.flags |= kFlagNeedHist;
         const uintptr_t p = (uintptr_t)(srcs ? (const void*)srcs[i] : (const void*)dsts[i]);
@@ -109,7 +109,7 @@ uint32_t emu_encode(size_t n, const uint8_t* const* srcs, const uint64_t* n_byte
         LaneHeader* hd = hdrs.data() + a * 256;
         unsigned long long* ls = lsrc.data() + a * 256;
         uint32_t* lo = loff.data() + a * 256;
-        emu::launch((unsigned)((m + 127) / 128), 128, 0, [&] { zero_lane_kernel(descs, enc.data(), scr, hd, ls, (uint32_t)m); });
+        emu::launch((unsigned)((m + 31) / 32), 32, 0, [&] { zero_lane_kernel(descs, enc.data(), scr, hd, ls, (uint32_t)m); });
         if (float_only)  // the variant the pipeline uses for float-only batches without missing symbols
             emu::launch(grid, kTeam, sizeof(EncSmem<2>), [&] {
                 rans_encode_kernel<false, false>(descs, enc.data(), scr, hd, ls, order.data() + a, &tickets[g], (uint32_t)m);
@@ -128,6 +128,75 @@ uint32_t emu_encode(size_t n, const uint8_t* const* srcs, const uint64_t* n_byte
     std::memcpy(hdrs_out, hdrs.data(), n * 4096);
     for (size_t i = 0; i < n; ++i) raw_out[i] = (b.descs[i].flags & kFlagRaw) ? 1 : 0;
     return status;
+}
+
+// The same through rans_encode_fused_kernel (one launch: lanes, zero chain, offsets, gather).
+// The device payload is a heap: heap_off_out[i] / size_out[i] say where tensor i's payload is.
+void emu_encode_fused(size_t n, const uint8_t* const* srcs, const uint64_t* n_bytes, const uint32_t* es,
+                      const uint32_t* spe, const uint32_t* table_idx, size_t n_tables, const uint32_t* nf,
+                      const uint32_t* cf, uint8_t* heap_out, uint64_t* heap_off_out, uint64_t* size_out,
+                      uint32_t* hdrs_out, uint8_t* raw_out, uint32_t grid, uint32_t float_only) {
+    Batch b = make_batch(n, srcs, nullptr, n_bytes, es, spe, table_idx, nullptr);
+    std::vector<EncEntry> enc(n_tables * 256);
+    for (size_t t = 0; t < n_tables; ++t) {
+        FreqTable ft;
+        std::memcpy(ft.norm_freq, nf + t * 256, 1024);
+        std::memcpy(ft.cum_freq, cf + t * 257, 1028);
+        build_enc_entries(ft, &enc[t * 256]);
+    }
+    unsigned long long slot_bytes = 0;
+    for (size_t i = 0; i < n; ++i) {
+        const unsigned long long need = (b.descs[i].spe * 2 == b.descs[i].es ? 129ull : 256ull) * b.descs[i].chunk_stride;
+        if (need > slot_bytes) slot_bytes = need;
+    }
+    slot_bytes = (slot_bytes + 255) & ~255ull;
+    std::vector<uint8_t> scratch(slot_bytes * grid + 64, 0xAA);
+    uint8_t* scr = (uint8_t*)(((uintptr_t)scratch.data() + 31) & ~(uintptr_t)31);
+    std::vector<LaneHeader> hdrs(n * 256);
+    std::vector<unsigned long long> psize(n, 0);
+    std::vector<uint32_t> order(n);
+    for (size_t i = 0; i < n; ++i) order[i] = (uint32_t)((i * 7 + 3) % n);  // any permutation must give the same result
+    if (n % 7 == 0) for (size_t i = 0; i < n; ++i) order[i] = (uint32_t)(n - 1 - i);
+    unsigned long long cursor = 0;
+    uint32_t ticket = 0;
+    // shared symbol-0 chains: deliberately few slots, so that some tensors fall back to computing their own
+    uint32_t max_stride = 0;
+    for (size_t i = 0; i < n; ++i) max_stride = std::max(max_stride, b.descs[i].chunk_stride);
+    const uint32_t z_slots = 2;
+    std::vector<ZeroSlot> zslots(z_slots);
+    std::memset(zslots.data(), 0, z_slots * sizeof(ZeroSlot));
+    std::vector<uint8_t> zregions((size_t)z_slots * max_stride + 64, 0xBB);
+    std::vector<int32_t> zslot_of(n, -7);
+    emu::launch((unsigned)n, 32, 0, [&] {
+        zero_chain_kernel(b.descs.data(), enc.data(), zslots.data(), z_slots, zregions.data(), max_stride, zslot_of.data(),
+                          (uint32_t)n);
+    });
+    FusedParams fp{};
+    fp.descs = b.descs.data();
+    fp.tables = enc.data();
+    fp.scratch = scr;
+    fp.slot_bytes = slot_bytes;
+    fp.zero_slots = zslots.data();
+    fp.zero_regions = zregions.data();
+    fp.zero_slot_of = zslot_of.data();
+    fp.zero_region_stride = max_stride;
+    fp.n_tensors = (uint32_t)n;
+    fp.hdrs = hdrs.data();
+    fp.payload = heap_out;
+    fp.payload_size = psize.data();
+    fp.heap_cursor = &cursor;
+    fp.order = order.data();
+    fp.ticket = &ticket;
+    if (float_only)
+        emu::launch(grid, kTeam, sizeof(EncSmem<2>), [&] { rans_encode_fused_kernel<false>(fp); });
+    else
+        emu::launch(grid, kTeam, sizeof(EncSmem<4>), [&] { rans_encode_fused_kernel<true>(fp); });
+    for (size_t i = 0; i < n; ++i) {
+        heap_off_out[i] = b.descs[i].payload_off;
+        size_out[i] = psize[i];
+        raw_out[i] = (b.descs[i].flags & kFlagRaw) ? 1 : 0;
+    }
+    std::memcpy(hdrs_out, hdrs.data(), n * 4096);
 }
 
 // payload must be readable 64 bytes past its end and 16-byte aligned.
@@ -165,18 +234,75 @@ void emu_stats(size_t n, const void* const* ptrs, const uint64_t* n_elem, const 
     emu::launch(grid, 256, 0, [&] { tensor_stats_kernel(d.data(), (StatsOut*)outs, (uint32_t)n); });
 }
 
-// enc_out: n_tables*256 entries of 4 words; freq_out n*256; cum_out n*257
-void emu_build_tables(size_t n_tables, const uint16_t* nf16, uint32_t* enc_out, uint32_t* freq_out, uint32_t* cum_out,
-                      uint32_t grid) {
-    emu::launch(grid, 256, 0, [&] { build_tables_kernel(nf16, (EncEntry*)enc_out, freq_out, cum_out, (uint32_t)n_tables); });
-}
-
 // the host routine the device kernel must agree with
 void emu_host_enc_entries(const uint32_t* nf, const uint32_t* cf, uint32_t* enc_out) {
     FreqTable ft;
     std::memcpy(ft.norm_freq, nf, 1024);
     std::memcpy(ft.cum_freq, cf, 1028);
     build_enc_entries(ft, (EncEntry*)enc_out);
+}
+
+// normalize_tables_kernel over n histograms (taken as they are: the descriptors carry no low bytes).
+// enc_out n*256*4 words, freq_out n*256, cum_out n*257, sums_out n.
+void emu_normalize_tables(size_t n, const uint32_t* hist, const uint32_t* flags, uint32_t* enc_out, uint32_t* freq_out,
+                          uint32_t* cum_out, uint32_t* sums_out, uint32_t grid) {
+    std::vector<TensorDesc> descs(n);
+    std::vector<TableJob> jobs(n);
+    for (size_t i = 0; i < n; ++i) {
+        std::memset(&descs[i], 0, sizeof(TensorDesc));
+        descs[i].es = 1;
+        jobs[i].owner = (uint32_t)i;
+        jobs[i].flags = flags[i];
+    }
+    emu::launch(grid, 256, 0, [&] {
+        normalize_tables_kernel(jobs.data(), descs.data(), hist, (EncEntry*)enc_out, freq_out, cum_out, sums_out, (uint32_t)n);
+    });
+}
+
+// sort_replica and the library routine it reproduces, on the same keys (symbols 0..n-1 in input order).
+void emu_sort_replica(size_t n, const double* frac, int32_t* sym_out) {
+    std::vector<FracKey> k(n);
+    for (size_t i = 0; i < n; ++i) k[i] = FracKey{frac[i], (int32_t)i, 0};
+    sort_replica(k.data(), (int)n);
+    for (size_t i = 0; i < n; ++i) sym_out[i] = k[i].sym;
+}
+void emu_std_sort(size_t n, const double* frac, int32_t* sym_out) {
+    std::vector<FracKey> k(n);
+    for (size_t i = 0; i < n; ++i) k[i] = FracKey{frac[i], (int32_t)i, 0};
+    std::sort(k.begin(), k.end(), [](const FracKey& a, const FracKey& b) { return a.frac > b.frac; });
+    for (size_t i = 0; i < n; ++i) sym_out[i] = k[i].sym;
+}
+void emu_heap_sort_pair(size_t n, const double* frac, int32_t* replica_out, int32_t* std_out) {
+    std::vector<FracKey> a(n), b;
+    for (size_t i = 0; i < n; ++i) a[i] = FracKey{frac[i], (int32_t)i, 0};
+    b = a;
+    sr_heap_sort(a.data(), a.data() + n);
+    std::partial_sort(b.begin(), b.end(), b.end(), [](const FracKey& x, const FracKey& y) { return x.frac > y.frac; });
+    for (size_t i = 0; i < n; ++i) {
+        replica_out[i] = a[i].sym;
+        std_out[i] = b[i].sym;
+    }
+}
+// An input on which the library's quicksort degenerates (M. D. McIlroy's adversary: the
+// comparator fixes values while std::sort runs), so the depth limit and the heap sort are reached.
+void emu_sort_killer(size_t n, double* frac_out) {
+    std::vector<double> val(n);
+    const double gas = 1e18;
+    int nsolid = 0, candidate = 0;
+    std::vector<int> idx(n);
+    for (size_t i = 0; i < n; ++i) {
+        idx[i] = (int)i;
+        val[i] = gas;
+    }
+    auto cmp = [&](int x, int y) {
+        if (val[x] == gas && val[y] == gas) {
+            if (x == candidate) val[x] = nsolid++; else val[y] = nsolid++;
+        }
+        if (val[x] == gas) candidate = x; else if (val[y] == gas) candidate = y;
+        return val[x] > val[y];
+    };
+    std::sort(idx.begin(), idx.end(), cmp);
+    for (size_t i = 0; i < n; ++i) frac_out[i] = val[i] == gas ? (double)nsolid : val[i];
 }
 
 uint32_t emu_stats_out_bytes() { return (uint32_t)sizeof(StatsOut); }

@@ -99,6 +99,31 @@ class Emu:
                                  _p(hdrs, u32p), _p(raw), C.c_uint32(grid), C.c_uint32(int(float_only)), C.c_uint32(segments))
         return payload, poff, hdrs, raw, st
 
+    def encode_fused(self, tensors, es, spe, table_idx, nf, cf, grid=3, float_only=False):
+        """The one-kernel path (lanes, zero chain, offsets, gather into a payload heap).  Returns the
+        payloads re-packed in tensor order, their offsets, headers and raw flags like encode()."""
+        n, ptrs = self._arrays(tensors)
+        nb = np.array([t.size for t in tensors], np.uint64)
+        es_a, spe_a = np.array(es, np.uint32), np.array(spe, np.uint32)
+        ti = np.array(table_idx, np.uint32)
+        nf = np.ascontiguousarray(nf, np.uint32).reshape(-1, 256)
+        cf = np.ascontiguousarray(cf, np.uint32).reshape(-1, 257)
+        heap = aligned(int(nb.sum()) + 32 * n + 64)
+        hoff, size = np.zeros(n, np.uint64), np.zeros(n, np.uint64)
+        hdrs = np.zeros((n, 256, 4), np.uint32)
+        raw = np.zeros(n, np.uint8)
+        self.lib.emu_encode_fused(C.c_size_t(n), ptrs, _p(nb, u64p), _p(es_a, u32p), _p(spe_a, u32p), _p(ti, u32p),
+                                  C.c_size_t(nf.shape[0]), _p(nf, u32p), _p(cf, u32p), _p(heap), _p(hoff, u64p),
+                                  _p(size, u64p), _p(hdrs, u32p), _p(raw), C.c_uint32(grid),
+                                  C.c_uint32(int(float_only)))
+        assert all(int(o) % 32 == 0 for o in hoff)
+        spans = sorted((int(o), int(o) + int(z)) for o, z in zip(hoff, size))
+        assert all(a[1] <= b[0] for a, b in zip(spans, spans[1:])), "heap ranges overlap"
+        poff = np.zeros(n + 1, np.uint64)
+        poff[1:] = np.cumsum(size)
+        payload = np.concatenate([heap[int(o):int(o) + int(z)] for o, z in zip(hoff, size)] + [np.zeros(0, np.uint8)])
+        return payload, poff, hdrs, raw
+
     def decode(self, n_bytes, es, spe, table_idx, nf, cf, hdrs, payload, poff, raw, sidecar, check_zero=0, grid=3,
                dst_misalign=0, float_only=False):
         n = len(n_bytes)

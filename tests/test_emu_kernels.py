@@ -53,6 +53,11 @@ def test_split_hist_encode_decode(emu, oracle, misalign):
         p2, o2, h2, r2, st2 = emu.encode(tensors, es, spe, list(range(len(tensors))), nf, cf, segments=segments)
         assert st2 == 0 and np.array_equal(o2, poff) and np.array_equal(h2, hdrs) and np.array_equal(r2, raw)
         assert np.array_equal(p2[:int(poff[-1])], payload[:int(poff[-1])]), segments
+    # the one-kernel path (lanes, zero chain, offsets and gather inside the team) gives the same bytes
+    for grid in (1, 4):
+        p3, o3, h3, r3 = emu.encode_fused(tensors, es, spe, list(range(len(tensors))), nf, cf, grid=grid)
+        assert np.array_equal(o3, poff) and np.array_equal(h3, hdrs) and np.array_equal(r3, raw)
+        assert np.array_equal(p3[:int(poff[-1])], payload[:int(poff[-1])]), grid
     for dst_mis in (0, 4):
         outs, status = emu.decode([a.size for a in tensors], es, spe, list(range(len(tensors))), nf, cf, hdrs, payload,
                                   poff, raw, side, check_zero=1, dst_misalign=dst_mis)
@@ -78,6 +83,9 @@ def test_float_only_kernel_variants(emu, oracle):
         p, hd, r = oracle.compress_tensor(masked[i], *tabs[i][:3])
         assert bool(raw[i]) == r and np.array_equal(payload[int(poff[i]):int(poff[i + 1])], p), i
         assert np.array_equal(hdrs[i], hd), i
+    p3, o3, h3, r3 = emu.encode_fused(tensors, es, spe, list(range(len(tensors))), nf, cf, float_only=True)
+    assert np.array_equal(o3, poff) and np.array_equal(h3, hdrs) and np.array_equal(r3, raw)
+    assert np.array_equal(p3[:int(poff[-1])], payload[:int(poff[-1])])
     outs, status = emu.decode([a.size for a in tensors], es, spe, list(range(len(tensors))), nf, cf, hdrs, payload,
                               poff, raw, side, check_zero=1, float_only=True)
     assert not status.any()
@@ -136,29 +144,3 @@ def test_stats_kernel(emu, oracle):
             assert np.array_equal(res[i][1].view(np.uint32), mom.view(np.uint32)), i
             assert np.array_equal(res[i][2].view(np.uint32), mm.view(np.uint32)), i
             assert res[i][3][4] == np.float32(mm[1] - mm[0])
-
-
-def test_device_table_builder(emu, oracle):
-    """build_tables_kernel must give the prefix sums and encode entries the host routine gives."""
-    import ctypes as C
-    rng = np.random.default_rng(8)
-    tabs = []
-    for i in range(9):
-        h = np.zeros(256, np.uint32)
-        k = [1, 2, 256, 20, 100, 256, 7, 3, 50][i]
-        h[rng.choice(256, k, replace=False)] = rng.integers(1, 10 ** (1 + i % 6), k)
-        tabs.append(oracle.normalize(h, full=(i % 3 == 0)))
-    nf = np.stack([t[0] for t in tabs])
-    cf = np.stack([t[1] for t in tabs])
-    nf16 = nf.astype(np.uint16)
-    n = len(tabs)
-    enc = np.zeros((n, 256, 4), np.uint32)
-    freq, cum = np.zeros((n, 256), np.uint32), np.zeros((n, 257), np.uint32)
-    u32p = C.POINTER(C.c_uint32)
-    emu.lib.emu_build_tables(C.c_size_t(n), nf16.ctypes.data_as(C.POINTER(C.c_uint16)), enc.ctypes.data_as(u32p),
-                             freq.ctypes.data_as(u32p), cum.ctypes.data_as(u32p), C.c_uint32(3))
-    assert np.array_equal(freq, nf) and np.array_equal(cum, cf)
-    for i in range(n):
-        want = np.zeros((256, 4), np.uint32)
-        emu.lib.emu_host_enc_entries(nf[i].ctypes.data_as(u32p), cf[i].ctypes.data_as(u32p), want.ctypes.data_as(u32p))
-        assert np.array_equal(enc[i], want), i

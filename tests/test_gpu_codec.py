@@ -199,7 +199,17 @@ def test_files_identical_with_clusters(chk, oracle, tmp_path, repair):
     ctx.set_cluster_info(names, cid, anchors)
     ctx.set_option("repair_tables", int(repair))
     out_gpu, out_cpu = str(tmp_path / "gpu"), str(tmp_path / "cpu")
+    if not repair:
+        # reference-exact shared tables for bf16 data do not sum to 4096: nothing is written unless asked for
+        with pytest.raises(chk.CheckersError) as ei:
+            ctx.compress_and_save(out_gpu)
+        assert ei.value.code == -6 and not os.path.exists(os.path.join(out_gpu, "rank_1_states.ansc"))
+        n_tab, n_bad = ctx.table_report()
+        assert 0 < n_bad <= n_tab
+        ctx.set_option("allow_undecodable", 1)
     ctx.compress_and_save(out_gpu)
+    if repair:
+        assert ctx.table_report()[1] == 0
     oracle.compress_and_save(names, host, dtypes, out_cpu, rank=1, cluster_id=cid, anchor_names=anchors,
                              repair_tables=repair)
     for a, b, what in zip(read_files(out_gpu, 1), read_files(out_cpu, 1), ("states", "mantissa", "tables")):
@@ -342,7 +352,8 @@ def test_front_end_api(chk, oracle, tmp_path):
         tensors[n] = t.view(torch.bfloat16) if dt == BF16 else t.view(torch.float32)
     with pytest.raises(RuntimeError):
         chk.initialize_context(tensors, histogram_bins=0)
-    chk.initialize_context(tensors, None, 256, 1)
+    # reference-exact bytes even where a cluster's shared table is not decodable (compared with the oracle below)
+    chk.initialize_context(tensors, None, 256, 1, shared_tables="reference_bytes")
     chk.analyze_tensors()
     out = str(tmp_path / "out")
     chk.compress_and_save(out)

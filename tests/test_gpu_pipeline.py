@@ -1,0 +1,236 @@
+"""GPU tests of what surrounds the kernels: the benchmark's own tensor shapes against the oracle, the
+workspace bound, raw-passthrough float tensors through a borrowed table, parameter discovery on a
+module + optimizer, the `checkers_py` module name with the reference example's call sequence, the
+[TIMING] log.  All through the C ABI; files bit-exact."""
+import os
+import types
+
+import numpy as np
+import pytest
+
+from oracle_lib import BF16, ELEM_SIZE, F32, I8, Oracle, synth
+from test_gpu_codec import chk, dev_bytes, read_files, register_all  # noqa: F401  (chk is a fixture)
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+
+
+def _bench_slice(shard, world_shards, chunk_elems, seed):
+    """A flat-index slice of the benchmark's Llama-3-8B state, built like bench.py builds its CPU sample."""
+    import bench
+    pieces, n_elems, _ = bench.shard_pieces(bench.LLAMA3_8B, shard, world_shards, chunk_elems)
+    bufs = bench.make_shard_on_host(pieces, n_elems, seed)
+    names, host, dtypes = [], [], []
+    for name, off, n, _ in pieces:
+        for (prefix, _), b, dt in zip(bench.STATE_KINDS, bufs, (BF16, F32, F32, F32)):
+            names.append(prefix + name)
+            host.append(np.ascontiguousarray(b[off:off + n]).view(np.uint8).reshape(-1).copy())
+            dtypes.append(dt)
+    return pieces, names, host, dtypes
+
+
+def test_benchmark_slice_matches_oracle(chk, oracle, tmp_path):
+    """Pieces of 1 Mi elements at shard position: the end of a down_proj, both RMSNorm gains of the layer
+    (1 + N(0, 1e-3): every bf16 value is 1.0) and the start of the next q_proj, with the lognormal
+    exp_avg_sq the benchmark uses."""
+    pieces, names, host, dtypes = _bench_slice(189, 2048, 1 << 20, 7)
+    assert any(p[3] for p in pieces) and len({p[0].split("@")[0] for p in pieces}) >= 3
+    assert max(p[2] for p in pieces) == 1 << 20
+    dev = [dev_bytes(h) for h in host]
+    ctx = chk.Context(device=0, rank=3)
+    register_all(ctx, names, dev, dtypes)
+    out_gpu, out_cpu = str(tmp_path / "gpu"), str(tmp_path / "cpu")
+    ctx.compress_and_save(out_gpu)
+    oracle.compress_and_save(names, host, dtypes, out_cpu, rank=3)
+    for a, b, what in zip(read_files(out_gpu, 3), read_files(out_cpu, 3), ("states", "mantissa", "tables")):
+        assert a == b, f"{what} file differs from the oracle's"
+    outs = [torch.zeros(h.size, dtype=torch.uint8, device="cuda") for h in host]
+    assert ctx.decompress_resident([o.data_ptr() for o in outs]) == len(names)
+    torch.cuda.synchronize()
+    for o, h, n in zip(outs, host, names):
+        assert np.array_equal(o.cpu().numpy(), h), n
+    ctx.close()
+
+
+def test_workspace_bound(chk, oracle, tmp_path):
+    """A deliberately small workspace: fewer encode teams, the same files; below one slot: refused."""
+    rng = np.random.default_rng(3)
+    kinds = ["bf16_weight", "f32_master", "f32_exp_avg", "f32_exp_avg_sq_lognormal", "i8"]
+    names, host, dev, dtypes = [], [], [], []
+    for i in range(600):
+        raw, dt = synth(kinds[i % len(kinds)], int(rng.integers(1, 30000)), 900 + i)
+        names.append(f"t{i}")
+        host.append(raw.copy())
+        dev.append(dev_bytes(raw))
+        dtypes.append(dt)
+    out_cpu = str(tmp_path / "cpu")
+    oracle.compress_and_save(names, host, dtypes, out_cpu)
+    ref = read_files(out_cpu)
+    slot = 256 * 2 * ((30000 * 4 + 255) // 256 + 16)      # an upper estimate of one team's scratch slot
+    teams_seen = []
+    for ws in (0, 3 * slot):
+        ctx = chk.Context(device=0, workspace_bytes=ws)
+        register_all(ctx, names, dev, dtypes)
+        out_gpu = str(tmp_path / f"gpu{ws}")
+        ctx.compress_and_save(out_gpu)
+        for a, b, what in zip(read_files(out_gpu), ref, ("states", "mantissa", "tables")):
+            assert a == b, f"workspace {ws}: {what} file differs from the oracle's"
+        teams_seen.append(ctx.timing("encode_teams"))
+        if ws:
+            assert ctx.timing("workspace_mb") * 2 ** 20 <= ws
+        ctx.close()
+    assert 1 <= teams_seen[1] < teams_seen[0] and teams_seen[1] <= 8   # my slot estimate is generous
+    ctx = chk.Context(device=0, workspace_bytes=4096)
+    register_all(ctx, names, dev, dtypes)
+    with pytest.raises(chk.CheckersError) as ei:
+        ctx.compress(host_images=False)
+    assert ei.value.code == -7
+    ctx.set_option("workspace_bytes", 0)     # the option lifts the bound again
+    ctx.compress(host_images=False)
+    ctx.close()
+
+
+def test_raw_passthrough_float_through_borrowed_table(chk, oracle, tmp_path):
+    """Float tensors that borrow the table of an anchor whose bytes are nearly all one value: every other byte,
+    the zeroed low bytes included, costs 12 bits, the streams come out larger than the tensor, and the passthrough
+    rule stores the masked bytes raw; restoring such a tensor merges them with its sidecar."""
+    specs = [("a.w", None, 50000), ("b.w", "f32_uniform_bits", 40000), ("c.w", "bf16_weight", 777),
+             ("d.w", "f32_uniform_bits", 255), ("e.w", "f32_master", 30000)]
+    names, host, dtypes = [], [], []
+    for i, (n, kind, cnt) in enumerate(specs):
+        if kind is None:
+            raw, dt = np.full(cnt, 0x55, np.uint8), I8
+            raw[::97] = 0x56
+        else:
+            raw, dt = synth(kind, cnt, 70 + i)
+        names.append(n)
+        host.append(raw.copy())
+        dtypes.append(dt)
+    dev = [dev_bytes(h) for h in host]
+    cid, anchors = [0, 0, 0, 0, -1], ["a.w"]
+    ctx = chk.Context(device=0)
+    register_all(ctx, names, dev, dtypes)
+    ctx.set_cluster_info(names, cid, anchors)
+    ctx.set_option("repair_tables", 1)
+    out_gpu, out_cpu = str(tmp_path / "gpu"), str(tmp_path / "cpu")
+    ctx.compress_and_save(out_gpu)
+    oracle.compress_and_save(names, host, dtypes, out_cpu, cluster_id=cid, anchor_names=anchors, repair_tables=True)
+    st = read_files(out_gpu)[0]
+    for a, b, what in zip(read_files(out_gpu), read_files(out_cpu), ("states", "mantissa", "tables")):
+        assert a == b, f"{what} file differs from the oracle's"
+    assert all(st[16 + k * 4648 + 257] == 1 for k in (1, 2, 3)), "the float members must be stored raw"
+    for source in ("resident", "files"):
+        outs = [torch.zeros(h.size + 8, dtype=torch.uint8, device="cuda") for h in host]
+        if source == "resident":
+            assert ctx.decompress_resident([o.data_ptr() for o in outs]) == len(names)
+        else:
+            ctx2 = chk.Context(device=0)
+            for n, o, h, dt in zip(names, outs, host, dtypes):
+                ctx2.register_pointer(n, o.data_ptr(), h.size // ELEM_SIZE[dt], dt)
+            assert ctx2.load_and_decompress(out_gpu) == len(names)
+            ctx2.close()
+        torch.cuda.synchronize()
+        for o, h, n in zip(outs, host, names):
+            got = o.cpu().numpy()
+            assert np.array_equal(got[:h.size], h) and not got[h.size:].any(), (source, n)
+    ctx.close()
+
+
+class _MasterAdam(torch.optim.Adam):
+    """Adam over fp32 master copies of bf16 parameters, apex FP16_Optimizer style."""
+
+    def __init__(self, params):
+        self.fp16_groups = [list(params)]
+        self.fp32_from_fp16_groups = [[p.detach().clone().float().requires_grad_(True) for p in self.fp16_groups[0]]]
+        super().__init__(self.fp32_from_fp16_groups[0], lr=1e-2)
+
+    def step_from(self):
+        for lo, hi in zip(self.fp16_groups[0], self.fp32_from_fp16_groups[0]):
+            hi.grad = lo.grad.float()
+        self.step()
+        for lo, hi in zip(self.fp16_groups[0], self.fp32_from_fp16_groups[0]):
+            lo.data.copy_(hi.data)
+
+
+def _train_one_step(module, opt, master):
+    x = torch.randn(16, 64, device="cuda", dtype=next(module.parameters()).dtype)
+    module(x).float().pow(2).mean().backward()
+    if master:
+        opt.step_from()
+    else:
+        opt.step()
+
+
+@pytest.mark.parametrize("master", [False, True])
+def test_discovery_on_module_and_optimizer(chk, oracle, tmp_path, master):
+    """initialize_context(module, optimizer): weight, (master copy,) exp_avg, exp_avg_sq per parameter, in the
+    reference's order and names; files equal the oracle's over the same tensors; restore brings them back."""
+    torch.manual_seed(5)
+    module = torch.nn.Sequential(torch.nn.Linear(64, 128), torch.nn.LayerNorm(128), torch.nn.Linear(128, 64)).cuda()
+    if master:
+        module = module.bfloat16()
+        opt = _MasterAdam(module.parameters())
+    else:
+        opt = torch.optim.Adam(module.parameters(), lr=1e-2)
+    _train_one_step(module, opt, master)
+    torch.cuda.synchronize()
+    chk.initialize_context(module, opt, 256, 1)
+    ctx = chk.current_context()
+    per_param = 4 if master else 3
+    assert ctx.tensor_count() == per_param * len(list(module.parameters()))
+    want = []
+    for name, _ in module.named_parameters():
+        want += [name] + (["master_weights::" + name] if master else []) + \
+                ["optimizer.exp_avg::" + name, "optimizer.exp_avg_sq::" + name]
+    assert ctx.names == want
+    pairs = chk.api._named_state_tensors(module, opt)
+    host = [t.detach().contiguous().view(torch.uint8).reshape(-1).cpu().numpy().copy() for _, t in pairs]
+    dtypes = [BF16 if t.dtype == torch.bfloat16 else F32 for _, t in pairs]
+    out_gpu, out_cpu = str(tmp_path / "gpu"), str(tmp_path / "cpu")
+    chk.compress_and_save(out_gpu)       # no analyze_tensors(): every tensor owns its table
+    oracle.compress_and_save([n for n, _ in pairs], host, dtypes, out_cpu)
+    for a, b, what in zip(read_files(out_gpu), read_files(out_cpu), ("states", "mantissa", "tables")):
+        assert a == b, f"{what} file differs from the oracle's"
+    for _, t in pairs:
+        t.detach().zero_()
+    assert chk.load_and_decompress(out_gpu) == len(pairs)
+    torch.cuda.synchronize()
+    for (n, t), h in zip(pairs, host):
+        assert np.array_equal(t.detach().view(torch.uint8).reshape(-1).cpu().numpy(), h), n
+
+
+def test_checkers_py_call_sequence_and_timing_log(tmp_path, monkeypatch):
+    """`import checkers_py` and the call sequence of the reference's training script
+    (examples/FSDP_ZeRO3/train_llama3.py:235-264) on a stand-in engine object."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    monkeypatch.setenv("CHECKERS_LOG_DIR", str(tmp_path / "logs"))
+    monkeypatch.setenv("CHECKERS_LOG_RUN_ID", "t1")
+    import checkers_py
+    torch.manual_seed(1)
+    module = torch.nn.Sequential(torch.nn.Linear(64, 64), torch.nn.Linear(64, 64)).cuda()
+    optimizer = torch.optim.Adam(module.parameters())
+    _train_one_step(module, optimizer, False)
+    engine = types.SimpleNamespace(module=module, optimizer=optimizer, global_rank=2, local_rank=0, global_steps=1)
+    # the script's own call, plus the one added keyword: tiny bias tensors that get clustered would otherwise hit
+    # the reference's undecodable shared tables, which compress_and_save refuses to write
+    checkers_py.initialize_context(engine, optimizer, histogram_bins=4096, background_threads=4, shared_tables="repair")
+    checkers_py.analyze_tensors()
+    out = str(tmp_path / "ckpt")
+    checkers_py.compress_and_save(out)
+    assert os.path.exists(os.path.join(out, "rank_2_states.ansc"))
+    assert os.path.exists(os.path.join(out, "mantissa", "rank_2_mantissa.mant"))
+    assert os.path.exists(os.path.join(out, "tables", "rank_2_tables.dict"))
+    log = open(tmp_path / "logs" / "t1" / "rank_2" / "checkers.log").read()
+    for key in ("setup_ms", "discovery_ms", "flush_ms", "total_ms", "analyze_histograms_ms", "analyze_knn_clusters_ms",
+                "analyze_total_ms", "compress_and_save_total_ms", "compress_computation_ms", "compress_io_ms",
+                "compress_and_save_wall_ms"):
+        assert f"[TIMING] {key}=" in log, key
+    before = [p.detach().clone() for p in module.parameters()]
+    for p in module.parameters():
+        p.data.zero_()
+    assert checkers_py.load_and_decompress(out) == 3 * len(before)
+    torch.cuda.synchronize()
+    for p, b in zip(module.parameters(), before):
+        assert torch.equal(p.detach(), b)
