@@ -14,15 +14,20 @@ chunks of `--chunk-elems` (1 Mi) elements, so per-GPU work is fixed as N grows
 the distributions the benchmark config names.
 
 A step = compress the shard (low-byte split + histograms, tables, 256-lane rANS
-encode, compaction into the file layout) and restore it (decode + merge) with
+encode and gather into the file layout) and restore it (decode + merge) with
 all data resident in HBM.  value = shard bytes / step time, summed over ranks,
 timed with CUDA events on the library's stream, max over ranks.
 
 e2e = the same work for a slice of the shard that starts and ends in pinned host
-memory, through checkers_b200.streaming.ChunkedHostPipeline: every input byte is
-copied host->device, the three file images of every chunk device->host, then the
-images host->device and the restored tensors device->host, all inside the timed
-region (wall clock between device synchronisations, max over ranks).
+memory, through the chk_stream_* entry points (checkers_b200.streaming): every
+input byte is copied host->device, the three file images of every part
+device->host, then the images host->device and the restored tensors
+device->host, all inside the timed region (wall clock between device
+synchronisations, max over ranks).  The same slice size is used at every N.
+
+parity = outside the timed region, the first tensors of the shard (the ones the
+cpu_baseline leg times) are compressed to file images once more and compared byte
+for byte with the files the CPU oracle writes for the same tensors.
 """
 import argparse
 import json
@@ -40,8 +45,9 @@ sys.path.insert(0, os.path.join(ROOT, "tests"))
 
 LLAMA3_8B = dict(hidden=4096, layers=32, inter=14336, q_heads=32, kv_heads=8, head_dim=128, vocab=128256)
 PARAMS_8B = 8030261248
-# measured once under ncu (see profiles/): DRAM read+write bytes per byte of tensor processed
-NCU_DRAM_BYTES_PER_TENSOR_BYTE = {"rans_encode_kernel": (1.013e9 + 0.426e9) / 939.5e6,
+# DRAM read + write bytes per byte of tensor, from one ncu capture of each kernel on a 939.5 MB slice of this
+# workload (1024 tensors of 256 Ki elements); the traffic of a launch grows in proportion to the tensor bytes
+NCU_DRAM_BYTES_PER_TENSOR_BYTE = {"rans_encode_fused_kernel": (1.356e9 + 0.810e9) / 939.5e6,
                                   "rans_decode_kernel": (0.905e9 + 0.902e9) / 939.5e6}
 
 
@@ -210,6 +216,152 @@ def cpu_arm(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def extras(args, torch, chk, ctx, shard_bytes, peak):
+    """Numbers outside the headline step (flag --extras, second JSON line): the per-stage codec sweep of the
+    microbenchmark configuration, the per-shard statistics pass, the Re-Pair tool against the reference's CLI."""
+    dev = torch.device("cuda", torch.cuda.current_device())
+    out = {}
+
+    def timed(fn, reps=3):
+        fn()
+        torch.cuda.synchronize()
+        best = None
+        for _ in range(reps):
+            t0 = time.perf_counter()
+            fn()
+            torch.cuda.synchronize()
+            dt = time.perf_counter() - t0
+            best = dt if best is None else min(best, dt)
+        return best
+
+    # ---- statistics of the resident shard: two passes over every tensor (src/TensorAnalyzer.cpp:64-198)
+    ctx.analyze()
+    ms = min(ctx.timing("analyze_stats_ms") for _ in range(1))
+    for _ in range(2):
+        ctx.analyze()
+        ms = min(ms, ctx.timing("analyze_stats_ms"))
+    out["analyze"] = {"kernel": "tensor_stats_kernel", "ms": ms, "algorithmic_bytes": 2 * shard_bytes,
+                      "gbs": 2 * shard_bytes / ms / 1e6, "frac_of_hbm_peak": 2 * shard_bytes / ms / 1e6 / peak,
+                      "cluster_ms": ctx.timing("analyze_cluster_ms"), "tensors": ctx.tensor_count()}
+
+    # ---- codec microbenchmark configuration: 1 GiB fp32 ~ N(0, 1e-3) and 1 GiB bf16 ~ N(0, 0.02), seed 1, 4 MiB chunks
+    g = torch.Generator(device=dev).manual_seed(1)
+    chunk = 4 << 20
+    sweep = {}
+    for tag, dt, es, make in (("fp32", chk.F32, 4, lambda: torch.randn(256 << 20, generator=g, device=dev) * 1e-3),
+                              ("bf16", chk.BF16, 2,
+                               lambda: (torch.randn(512 << 20, generator=g, device=dev) * 0.02).to(torch.bfloat16))):
+        x = make()
+        B = x.numel() * x.element_size()
+        n_chunks = B // chunk
+        masked = torch.empty(B, dtype=torch.uint8, device=dev)
+        side = torch.empty(B // 2, dtype=torch.uint8, device=dev)
+        back = torch.empty(B, dtype=torch.uint8, device=dev)
+        c = chk.Context(device=dev.index)
+        torch.cuda.synchronize()
+        res = {}
+        # bit-pack only: tensor -> masked copy + packed low bytes (2.5 B moved per byte), and back (2.5 B)
+        t = timed(lambda: c.split(x.data_ptr(), x.numel(), dt, masked.data_ptr(), side.data_ptr()))
+        res["split_only_encode"] = {"ms": t * 1e3, "gbs": B / t / 1e9, "algorithmic_bytes": 2.5 * B}
+        t = timed(lambda: c.merge(masked.data_ptr(), side.data_ptr(), x.numel(), dt, back.data_ptr()))
+        res["split_only_decode"] = {"ms": t * 1e3, "gbs": B / t / 1e9, "algorithmic_bytes": 2.5 * B}
+        assert torch.equal(back, x.view(torch.uint8))
+        # entropy coding only: the masked buffer as byte tensors (all 256 lanes are real chains, zeros included)
+        ca = chk.Context(device=dev.index)
+        dst = []
+        for k in range(n_chunks):
+            ca.register_pointer(f"m.{k}", masked.data_ptr() + k * chunk, chunk, chk.I8)
+            dst.append(back.data_ptr() + k * chunk)
+        dst = np.asarray(dst, dtype=np.uint64)
+        enc, dec = [], []
+        for _ in range(3):
+            ca.compress(host_images=False)
+            enc.append(ca.timing("compress_device_ms"))
+            ca.decompress_resident(dst)
+            dec.append(ca.timing("decode_ms"))
+        sa = ca.summary()
+        pay = sa["states_bytes"] - 16 - 4648 * sa["n_tensors"]
+        res["ans_only_encode"] = {"ms": min(enc), "gbs": B / min(enc) / 1e6, "algorithmic_bytes": 2 * B + pay,
+                                  "note": "counting pass + encode: the tensors are read twice (1 GiB exceeds L2)"}
+        res["ans_only_decode"] = {"ms": min(dec), "gbs": B / min(dec) / 1e6, "algorithmic_bytes": B + pay}
+        assert torch.equal(back, masked)
+        ca.close()
+        # full pipeline on the float tensor
+        cf = chk.Context(device=dev.index)
+        dst = []
+        for k in range(n_chunks):
+            cf.register_pointer(f"t.{k}", x.data_ptr() + k * chunk, chunk // es, dt)
+            dst.append(back.data_ptr() + k * chunk)
+        dst = np.asarray(dst, dtype=np.uint64)
+        enc, dec = [], []
+        for _ in range(3):
+            cf.compress(host_images=False)
+            enc.append(cf.timing("compress_device_ms"))
+            cf.decompress_resident(dst)
+            dec.append(cf.timing("decode_ms"))
+        sf = cf.summary()
+        pay = sf["states_bytes"] - 16 - 4648 * sf["n_tensors"]
+        sidecar = sf["mantissa_bytes"] - 16 - 288 * sf["n_tensors"]
+        res["full_encode"] = {"ms": min(enc), "gbs": B / min(enc) / 1e6, "algorithmic_bytes": B + sidecar + pay}
+        res["full_decode"] = {"ms": min(dec), "gbs": B / min(dec) / 1e6, "algorithmic_bytes": B + sidecar + pay}
+        res["ratio"] = sf["original_bytes"] / (sf["states_bytes"] + sf["mantissa_bytes"] + sf["dict_bytes"])
+        assert torch.equal(back, x.view(torch.uint8))
+        cf.close()
+        c.close()
+        for v in res.values():
+            if isinstance(v, dict):
+                v["frac_of_hbm_peak"] = v["algorithmic_bytes"] / (v["ms"] * 1e-3) / 1e9 / peak
+        sweep[tag] = res
+        del x, masked, side, back
+        torch.cuda.empty_cache()
+    out["stage_sweep"] = {"config": "1 GiB fp32 ~ N(0,1e-3) and 1 GiB bf16 ~ N(0,0.02), seed 1, 4 MiB chunks (256 tensors each)",
+                          "peak_gbs": peak, **sweep}
+
+    # ---- prefix-mask Re-Pair: seconds per export for groups of 2^16 .. 2^22 elements, against the reference CLI
+    import shutil
+    import tempfile
+    from checkers_b200 import repair
+    from oracle_lib import REF_REPAIR_CLI, synth
+    rep = []
+    for lg in (16, 18, 20, 22):
+        root = tempfile.mkdtemp(prefix="chk_repair_")
+        try:
+            os.makedirs(os.path.join(root, "analysis", "plots"))
+            os.makedirs(os.path.join(root, "tensors"))
+            manifest = ["tensor_key,layer,category,state_type,numel,dtype,file"]
+            for layer in range(3):
+                raw, _ = synth("f32_master", 1 << lg, 300 + layer)
+                rel = f"tensors/master_mlp.up_{layer}.bin"
+                raw.tofile(os.path.join(root, rel))
+                manifest.append(f"master.mlp.up.{layer},{layer},mlp.up,master,{1 << lg},float32,{rel}")
+            groups = ["state_type,category,group_id,n_layers,layers,representative_layer,c6,c7,c8,c9",
+                      'master,mlp.up,0,3,"0 1 2",1,0,0,0,0']
+            open(os.path.join(root, "manifest.csv"), "w").write("\n".join(manifest) + "\n")
+            open(os.path.join(root, "analysis", "plots", "grouping_summary.csv"), "w").write("\n".join(groups) + "\n")
+            with open(os.devnull, "w") as null:
+                old = sys.stdout
+                sys.stdout = null
+                try:
+                    repair.main([root])          # the first call pays for the workspace
+                    t0 = time.perf_counter()
+                    repair.main([root])
+                    ours = time.perf_counter() - t0
+                finally:
+                    sys.stdout = old
+            theirs = None
+            if os.path.exists(REF_REPAIR_CLI):
+                t0 = time.perf_counter()
+                subprocess.check_call([REF_REPAIR_CLI, root], stdout=subprocess.DEVNULL)
+                theirs = time.perf_counter() - t0
+            rep.append({"elements_per_tensor": 1 << lg, "tensors": 3, "seconds": ours, "reference_cli_seconds": theirs})
+        finally:
+            shutil.rmtree(root, ignore_errors=True)
+    out["repair"] = {"what": "python -m checkers_b200.repair on one group of three fp32 tensors, default arguments, "
+                             "file reading and report writing included; reference = its own CLI, single-threaded, same box",
+                     "groups": rep}
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -219,15 +371,16 @@ def main():
     ap.add_argument("--world-shards", type=int, default=8, help="flat-index shards of the model; one per rank")
     ap.add_argument("--chunk-elems", type=int, default=1 << 20, help="elements per registered tensor")
     ap.add_argument("--limit-elems", type=int, default=0, help="use only this many parameters of the shard (tests)")
-    ap.add_argument("--e2e-elems", type=int, default=0,
-                    help="parameters in the host-buffer end-to-end leg (default: 256 Mi on one GPU, 128 Mi per GPU on several, "
-                         "to bound pinned host memory)")
-    ap.add_argument("--e2e-steps", type=int, default=2)
-    ap.add_argument("--e2e-workers", type=int, default=4, help="host threads driving chunks of the pipeline")
+    ap.add_argument("--e2e-elems", type=int, default=128 << 20,
+                    help="parameters per GPU in the host-buffer end-to-end leg (14 bytes each; the same at every N)")
+    ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--e2e-workers", type=int, default=4, help="staging slots (and host threads) of the chunk pipeline")
     ap.add_argument("--e2e-chunk-bytes", type=int, default=256 << 20,
                     help="tensor bytes per chunk of the host-buffer pipeline")
     ap.add_argument("--cpu-sample-elems", type=int, default=32 << 20, help="parameters in the timed CPU sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--extras", action="store_true",
+                    help="after the headline line, print a second JSON line: per-stage codec sweep, statistics pass, Re-Pair")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--opt", action="append", default=[], help="library option key=value (chk_set_option)")
     args = ap.parse_args()
@@ -309,14 +462,13 @@ def main():
     launches0 = ctx.kernel_launches()
     mark0 = sampler.mark()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    enc_ms, dec_ms, split_ms, compact_ms, table_ms, cwall_ms, dwall_ms = [], [], [], [], [], [], []
+    enc_ms, dec_ms, split_ms, table_ms, cwall_ms, dwall_ms = [], [], [], [], [], []
     e0.record(lib_stream)
     for _ in range(args.steps):
         summ = step()
         enc_ms.append(ctx.timing("encode_ms"))
         dec_ms.append(ctx.timing("decode_ms"))
         split_ms.append(ctx.timing("split_hist_ms"))
-        compact_ms.append(ctx.timing("compact_ms"))
         table_ms.append(ctx.timing("table_ms"))
         cwall_ms.append(ctx.timing("compress_total_ms"))
         dwall_ms.append(ctx.timing("decompress_total_ms"))
@@ -333,7 +485,7 @@ def main():
     value = shard_bytes * world / (ms_per_step * 1e-3) / 1e9
 
     # ---- end-to-end leg through the C ABI with HOST buffers (pinned), copies timed
-    e_elems = min(args.e2e_elems or ((256 << 20) if world == 1 else (128 << 20)), n_elems)
+    e_elems = min(args.e2e_elems, n_elems)
     e_pieces = [(nm, off, min(n, e_elems - off), nrm) for nm, off, n, nrm in pieces if off < e_elems]
     h_in = [torch.empty(e_elems, dtype=b.dtype).pin_memory() for b in bufs]
     h_out = [torch.empty(e_elems, dtype=b.dtype).pin_memory() for b in bufs]
@@ -347,6 +499,8 @@ def main():
             h_targets.append(ho[off:off + n])
     pipe = ChunkedHostPipeline(h_tensors, device=local_rank, rank=rank, chunk_bytes=args.e2e_chunk_bytes,
                                workers=args.e2e_workers)
+    e2e_keys = ("compress_h2d_ms", "compress_kernel_ms", "compress_d2h_ms", "compress_wall_ms", "restore_h2d_ms",
+                "restore_kernel_ms", "restore_d2h_ms", "restore_wall_ms")
     e_bytes = sum(h.numel() * h.element_size() for h in h_in)
     img_bytes = 0
 
@@ -372,6 +526,38 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s = float(t.item())
     e2e_value = e_bytes * world / e2e_s / 1e9
+    e2e_engines = {k: round(pipe.timing(k), 2) for k in e2e_keys}   # last step, this rank: busy time per engine
+    pipe.close()
+
+    # ---- parity of the benchmark's own tensors with the CPU oracle (outside every timed region)
+    parity = None
+    if rank == 0 and not args.no_cpu_baseline:
+        import tempfile
+        from oracle_lib import BF16, F32, Oracle
+        p_elems = min(args.cpu_sample_elems, n_elems)
+        pctx = chk.Context(device=local_rank, rank=rank, local_rank=local_rank)
+        p_names, p_host, p_dtypes = [], [], []
+        host = [b[:p_elems].cpu() for b in bufs]
+        for name, off, n, _ in pieces:
+            if off >= p_elems:
+                break
+            n = min(n, p_elems - off)
+            for (prefix, _), b, hb, tag, dt in zip(STATE_KINDS, bufs, host, tags, (BF16, F32, F32, F32)):
+                pctx.register_pointer(prefix + name, b.data_ptr() + off * b.element_size(), n, tag)
+                p_names.append(prefix + name)
+                a = hb[off:off + n]
+                p_host.append((a.view(torch.int16) if dt == BF16 else a).numpy())
+                p_dtypes.append(dt)
+        pctx.compress(host_images=True)
+        with tempfile.TemporaryDirectory() as tmp:
+            Oracle().compress_and_save(p_names, p_host, p_dtypes, tmp, rank=rank, threads=os.cpu_count() or 1)
+            same = True
+            for which, rel in enumerate((f"rank_{rank}_states.ansc", f"mantissa/rank_{rank}_mantissa.mant",
+                                         f"tables/rank_{rank}_tables.dict")):
+                same = same and np.array_equal(pctx.image(which), np.fromfile(os.path.join(tmp, rel), np.uint8))
+        pctx.close()
+        parity = {"files_identical": bool(same), "tensors": len(p_names), "against": "CPU oracle, same tensors"}
+        assert same, "the file images of the benchmark shard differ from the CPU oracle's"
 
     # ---- roofline of the dominant kernel (rANS encode): algorithmic bytes = B read + c*B written
     peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -383,25 +569,25 @@ def main():
             pass
     payload_bytes = summ["states_bytes"] - 16 - 4648 * summ["n_tensors"]
     sidecar_bytes = summ["mantissa_bytes"] - 16
-    kernels = {"rans_encode_kernel": (float(np.mean(enc_ms)), shard_bytes + payload_bytes),
+    # algorithmic bytes per launch: the fused encode reads the tensors and writes the payload once (its scratch
+    # round trip and gather are its own overhead and show in `traffic`); decode reads payload + low bytes and
+    # writes the tensors; counting reads the tensors and writes the low bytes
+    kernels = {"rans_encode_fused_kernel": (float(np.mean(enc_ms)), shard_bytes + payload_bytes),
                "rans_decode_kernel": (float(np.mean(dec_ms)), shard_bytes + payload_bytes + sidecar_bytes),
-               "split_hist_kernel": (float(np.mean(split_ms)), shard_bytes + sidecar_bytes),
-               "scan+compact": (float(np.mean(compact_ms)), 2 * payload_bytes)}
-    dom = max(("rans_encode_kernel", "rans_decode_kernel"), key=lambda k: kernels[k][0])
+               "split_hist_kernel": (float(np.mean(split_ms)), shard_bytes + sidecar_bytes)}
+    dom = max(("rans_encode_fused_kernel", "rans_decode_kernel"), key=lambda k: kernels[k][0])
     dom_ms, dom_bytes = kernels[dom]
     achieved = dom_bytes / (dom_ms * 1e-3) / 1e9 if dom_ms > 0 else 0.0
     roofline = {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "peak_kind": peak_kind,
                 "unit": "GB/s", "frac": achieved / peak,
-                # DRAM bytes of one launch: ncu dram__bytes_read+write on a 939.5 MB case (profiles/
-                # rans_kernels_llama3_shard.md), scaled by tensor bytes (traffic grows in proportion)
+                # DRAM bytes of one launch: ncu dram__bytes_read + write on a 939.5 MB slice, scaled by tensor bytes
                 "traffic": shard_bytes * NCU_DRAM_BYTES_PER_TENSOR_BYTE[dom],
                 "per_kernel_ms": {k: v[0] for k, v in kernels.items()},
                 "per_kernel_algorithmic_gbs": {k: (v[1] / (v[0] * 1e-3) / 1e9 if v[0] > 0 else None)
                                                for k, v in kernels.items()},
-                "note": "compress runs as a pipeline: counting, encode grids and compaction of neighbouring segments "
-                        "overlap, so their times are spans measured while sharing the device and add up to more "
-                        "than compress_call_ms; decode runs alone",
-                "host_table_ms": float(np.mean(table_ms)),
+                "note": "compress = counting, then one kernel that encodes every tensor and gathers its lanes; tables are "
+                        "built on the device while the next piece is counted (table_exposed_ms is what that did not hide)",
+                "table_exposed_ms": float(np.mean(table_ms)),
                 "compress_call_ms": float(np.mean(cwall_ms)), "restore_call_ms": float(np.mean(dwall_ms))}
 
     cpu_baseline = None
@@ -440,14 +626,20 @@ def main():
                 "decompress_gbs_per_gpu": shard_bytes / np.mean(dwall_ms) / 1e6,
                 "hbm_frac_of_step": (2 * (shard_bytes + payload_bytes + sidecar_bytes)) / (ms_per_step * 1e-3) / 1e9
                 / peak,
-                "roofline": roofline, "cpu_baseline": cpu_baseline,
+                "roofline": roofline, "cpu_baseline": cpu_baseline, "parity": parity,
                 "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": int(e_bytes + img_bytes),
                         "d2h_bytes_per_step": int(img_bytes + e_bytes), "steps": args.e2e_steps,
                         "sample": f"{e_bytes / 2**30:.2f} GiB of the shard per GPU from pinned host buffers: "
-                                  f"in {len(pipe.chunks)} chunks with copies and kernels overlapped: H2D, compress, D2H of "
-                                  "the file images; then H2D of the images, restore, D2H"},
+                                  f"in {len(pipe.chunks)} parts over {args.e2e_workers} staging slots with copies and "
+                                  "kernels overlapped: H2D, compress, D2H of the file images; then H2D of the images, "
+                                  "restore, D2H",
+                        "engine_busy_ms_rank0_last_step": e2e_engines},
                 "gpu_launches": int(launches), "clocks": clocks}
         print(json.dumps(line), flush=True)
+    if args.extras and rank == 0 and world == 1:
+        del outs, h_in, h_out
+        torch.cuda.empty_cache()
+        print(json.dumps({"extras": extras(args, torch, chk, ctx, shard_bytes, peak)}), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

@@ -56,11 +56,24 @@ def _load():
         "chk_decompress_resident": (C.c_int, [vp, C.POINTER(vp)]),
         "chk_restored_count": (C.c_int, [vp, C.POINTER(u64)]),
         "chk_split": (C.c_int, [vp, vp, u64, C.c_uint8, vp, vp]),
+        "chk_merge": (C.c_int, [vp, vp, vp, u64, C.c_uint8, vp]),
         "chk_byte_histogram": (C.c_int, [vp, vp, u64, u32p]),
         "chk_normalize_histogram": (C.c_int, [u32p, C.c_int, C.c_int, u32p, u32p, u32p, u32p]),
         "chk_get_timing": (C.c_int, [vp, C.c_char_p, C.POINTER(C.c_double)]),
         "chk_kernel_launches": (C.c_int, [vp, C.POINTER(u64)]),
         "chk_get_stream": (C.c_int, [vp, C.POINTER(vp)]),
+        "chk_stream_create": (C.c_int, [C.c_int, C.c_int, u64, C.c_int, C.POINTER(vp)]),
+        "chk_stream_destroy": (C.c_int, [vp]),
+        "chk_stream_add_tensor": (C.c_int, [vp, C.c_char_p, vp, u64, C.c_uint8]),
+        "chk_stream_compress": (C.c_int, [vp]),
+        "chk_stream_restore": (C.c_int, [vp, C.POINTER(vp)]),
+        "chk_stream_part_count": (C.c_int, [vp, C.POINTER(u64)]),
+        "chk_stream_part_info": (C.c_int, [vp, u64, C.POINTER(u64), C.POINTER(u64)]),
+        "chk_stream_get_image": (C.c_int, [vp, u64, C.c_int, C.POINTER(vp), C.POINTER(u64)]),
+        "chk_stream_get_summary": (C.c_int, [vp, C.POINTER(Summary)]),
+        "chk_stream_save": (C.c_int, [vp, C.c_char_p]),
+        "chk_stream_load": (C.c_int, [vp, C.c_char_p]),
+        "chk_stream_get_timing": (C.c_int, [vp, C.c_char_p, C.POINTER(C.c_double)]),
         "chk_encode_tensor_static": (C.c_int, [vp, u64, C.c_uint8, u32p, u32p, vp, vp, C.POINTER(u64),
                                                C.POINTER(C.c_int), vp]),
     }

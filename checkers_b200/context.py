@@ -176,6 +176,10 @@ class Context:
         check(lib.chk_split(self._h, C.c_void_p(src_ptr), int(num_elements), int(dtype), C.c_void_p(masked_ptr),
                             C.c_void_p(sidecar_ptr)))
 
+    def merge(self, masked_ptr, sidecar_ptr, num_elements, dtype, out_ptr):
+        check(lib.chk_merge(self._h, C.c_void_p(masked_ptr), C.c_void_p(sidecar_ptr), int(num_elements), int(dtype),
+                            C.c_void_p(out_ptr)))
+
     def byte_histogram(self, ptr, n_bytes):
         h = np.zeros(256, np.uint32)
         check(lib.chk_byte_histogram(self._h, C.c_void_p(ptr), int(n_bytes), h.ctypes.data_as(C.POINTER(C.c_uint32))))

@@ -28,6 +28,7 @@
 #include <memory>
 #include <mutex>
 #include <string>
+#include <thread>
 #include <unordered_map>
 #include <vector>
 
@@ -132,6 +133,12 @@ struct Context {
     // pinned host staging
     PinBuf h_hdrs, h_poff, h_psize, h_descs, h_status, h_jobs, h_sums, h_freq, h_cum, h_stats, h_order, h_tiles;
     PinBuf img[3];  // states, mantissa, tables
+    // Where the next compress builds its file images instead of img[] (caller-owned pinned memory of
+    // at least the worst-case sizes); the chunked host pipeline keeps one set per part this way.
+    void* img_ext[3] = {nullptr, nullptr, nullptr};
+    size_t img_ext_cap[3] = {0, 0, 0};
+    bool blocking_sync = false;
+    cudaEvent_t ev_block = nullptr;
 
     // result of the last compression
     std::vector<WorkItem> work;
@@ -171,6 +178,10 @@ static void pin_ensure(PinBuf& b, size_t bytes) {
     CHK_CUDA(cudaHostAlloc(&b.p, want, cudaHostAllocMapped | cudaHostAllocPortable));
     b.cap = want;
 }
+
+// Waits for a stream.  A context that is one of several driven by host threads at once (the chunked
+// host pipeline) sleeps on a blocking event instead of spinning on a core.
+static void sync_stream(Context* c, cudaStream_t s);
 
 static double ms_between(cudaEvent_t a, cudaEvent_t b) {
     float ms = 0;
@@ -213,6 +224,30 @@ static void control_zero(Context* c, void* dst, size_t bytes, cudaStream_t s) {
     CHK_CUDA(cudaGetLastError());
     c->launches++;
 }
+
+static void sync_stream(Context* c, cudaStream_t s) {
+    if (!c->blocking_sync) {
+        CHK_CUDA(cudaStreamSynchronize(s));
+        return;
+    }
+    if (!c->ev_block) CHK_CUDA(cudaEventCreateWithFlags(&c->ev_block, cudaEventBlockingSync | cudaEventDisableTiming));
+    CHK_CUDA(cudaEventRecord(c->ev_block, s));
+    CHK_CUDA(cudaEventSynchronize(c->ev_block));
+}
+
+// The buffer image k of the next compress is built in: the caller's, if one was installed, else the context's own.
+static uint8_t* image_buffer(Context* c, int k, size_t bytes) {
+    if (c->img_ext[k]) {
+        if (bytes > c->img_ext_cap[k])
+            throw Error{CHK_ERR_CAPACITY, "file image " + std::to_string(k) + " needs " + std::to_string(bytes) +
+                                              " bytes, the buffer provided holds " + std::to_string(c->img_ext_cap[k])};
+        c->img[k].size = bytes;
+        return static_cast<uint8_t*>(c->img_ext[k]);
+    }
+    pin_ensure(c->img[k], bytes);
+    return static_cast<uint8_t*>(c->img[k].p);
+}
+static const void* image_ptr(const Context* c, int k) { return c->img_ext[k] ? c->img_ext[k] : c->img[k].p; }
 
 // ------------------------------------------------------------------ work list
 // Order, ownership and sharing rules of compress_and_save_all
@@ -390,8 +425,7 @@ static void compress(Context* c, bool host_images) {
             const uint32_t magic[3] = {kStatesMagic, kMantMagic, kDictMagic};
             const uint32_t ver[3] = {kStatesVersion, kMantVersion, kDictVersion};
             for (int k = 0; k < 3; ++k) {
-                pin_ensure(c->img[k], kFileHeader);
-                uint8_t* p = static_cast<uint8_t*>(c->img[k].p);
+                uint8_t* p = image_buffer(c, k, kFileHeader);
                 put<uint32_t>(p, magic[k]);
                 put<uint32_t>(p + 4, ver[k]);
                 put<uint32_t>(p + 8, (uint32_t)(c->rank < 0 ? 0 : c->rank));
@@ -559,7 +593,7 @@ static void compress(Context* c, bool host_images) {
     if (host_images) control_copy(c, c->h_hdrs.p, c->d_hdrs.p, W * 4096, s);
     if (want_tables) control_copy(c, c->h_freq.p, c->d_freq.p, T * 256 * 4, s);
     if (host_images) control_copy(c, c->h_cum.p, c->d_cum.p, T * 257 * 4, s);
-    CHK_CUDA(cudaStreamSynchronize(s));
+    sync_stream(c, s);
 
     c->timing["split_hist_ms"] = ms_between(c->ev[0], c->ev_count[n_win - 1]);
     c->timing["table_ms"] = ms_between(c->ev_count[n_win - 1], c->ev[1]);  // what the counting did not hide
@@ -607,8 +641,7 @@ static void compress(Context* c, bool host_images) {
         const uint32_t rank_u = (uint32_t)(c->rank < 0 ? 0 : c->rank);
         CHK_CUDA(cudaEventRecord(c->ev[5], s));
         // states image (write_rank_states_file, src/ANSCompressor.cpp:751-816)
-        pin_ensure(c->img[0], c->summary.states_bytes);
-        uint8_t* st = static_cast<uint8_t*>(c->img[0].p);
+        uint8_t* st = image_buffer(c, 0, c->summary.states_bytes);
         const size_t st_data = kFileHeader + W * kStatesEntry;
         // heap order -> file order: each tensor's payload goes to its place in the data section
         for (size_t i = 0; i < W; ++i)
@@ -616,14 +649,12 @@ static void compress(Context* c, bool host_images) {
                 CHK_CUDA(cudaMemcpyAsync(st + st_data + poff[i], static_cast<const uint8_t*>(c->d_payload.p) + c->descs[i].payload_off,
                                          psize[i], cudaMemcpyDeviceToHost, s));
         // mantissa image (write_rank_mantissa_file, :839-887)
-        pin_ensure(c->img[1], c->summary.mantissa_bytes);
-        uint8_t* mt = static_cast<uint8_t*>(c->img[1].p);
+        uint8_t* mt = image_buffer(c, 1, c->summary.mantissa_bytes);
         const size_t mt_data = kFileHeader + n_sidecars * kMantEntry;
         if (sidecar_total)
             CHK_CUDA(cudaMemcpyAsync(mt + mt_data, c->d_sidecar.p, sidecar_total, cudaMemcpyDeviceToHost, s));
         // tables image (write_rank_tables_file, :903-931)
-        pin_ensure(c->img[2], c->summary.dict_bytes);
-        uint8_t* dc = static_cast<uint8_t*>(c->img[2].p);
+        uint8_t* dc = image_buffer(c, 2, c->summary.dict_bytes);
 
         put<uint32_t>(st, kStatesMagic);
         put<uint32_t>(st + 4, kStatesVersion);
@@ -679,7 +710,7 @@ static void compress(Context* c, bool host_images) {
             }
         }
         CHK_CUDA(cudaEventRecord(c->ev[6], s));
-        CHK_CUDA(cudaStreamSynchronize(s));
+        sync_stream(c, s);
         c->timing["d2h_ms"] = ms_between(c->ev[5], c->ev[6]);
         c->have_images = true;
     }
@@ -719,7 +750,7 @@ static void compress_and_save(Context* c, const std::string& dir) {
     const auto t0 = std::chrono::steady_clock::now();
     std::string paths[3];
     rank_paths(c, dir, paths);
-    for (int k = 0; k < 3; ++k) write_file(paths[k], c->img[k].p, c->img[k].size);
+    for (int k = 0; k < 3; ++k) write_file(paths[k], image_ptr(c, k), c->img[k].size);
     c->timing["io_ms"] = wall_ms(t0);
 }
 
@@ -751,7 +782,7 @@ static void run_decode(Context* c, size_t W, const uint8_t* d_payload, const uin
     CHK_CUDA(cudaEventRecord(c->ev[2], s));
     control_copy(c, c->h_status.p, c->d_status.p, W * 4, s);
     CHK_CUDA(cudaEventRecord(c->ev[4], s));
-    CHK_CUDA(cudaStreamSynchronize(s));
+    sync_stream(c, s);
     c->timing["decode_ms"] = ms_between(c->ev[1], c->ev[2]);
     c->timing["decode_tail_ms"] = ms_between(c->ev[2], c->ev[4]);
     const uint32_t* st = static_cast<const uint32_t*>(c->h_status.p);
@@ -979,14 +1010,15 @@ static void analyze(Context* c) {
     CHK_CUDA(cudaMemcpyAsync(c->d_stats_desc.p, d.data(), N * sizeof(StatsDesc), cudaMemcpyHostToDevice, s));
     CHK_CUDA(cudaMemsetAsync(c->d_stats_out.p, 0, N * sizeof(StatsOut), s));
     CHK_CUDA(cudaEventRecord(c->ev[0], s));
-    const uint32_t grid = (uint32_t)(N < 148u * 64u ? N : 148u * 64u);
+    const size_t cap = (size_t)(c->sm_count > 0 ? c->sm_count : 1) * 64;
+    const uint32_t grid = (uint32_t)(N < cap ? N : cap);
     tensor_stats_kernel<<<grid, 256, 0, s>>>(static_cast<const StatsDesc*>(c->d_stats_desc.p),
                                              static_cast<StatsOut*>(c->d_stats_out.p), (uint32_t)N);
     CHK_CUDA(cudaGetLastError());
     c->launches++;
     CHK_CUDA(cudaEventRecord(c->ev[1], s));
     CHK_CUDA(cudaMemcpyAsync(c->h_stats.p, c->d_stats_out.p, N * sizeof(StatsOut), cudaMemcpyDeviceToHost, s));
-    CHK_CUDA(cudaStreamSynchronize(s));
+    sync_stream(c, s);
     c->timing["analyze_stats_ms"] = ms_between(c->ev[0], c->ev[1]);
     std::memcpy(c->stats.data(), c->h_stats.p, N * sizeof(StatsOut));
 
@@ -1086,6 +1118,7 @@ int chk_context_destroy(chk_context* c) {
         if (b->p) cudaFreeHost(b->p);
     for (auto& e : c->ev)
         if (e) cudaEventDestroy(e);
+    if (c->ev_block) cudaEventDestroy(c->ev_block);
     for (auto* v : {&c->ev_count, &c->ev_tab})
         for (auto& e : *v)
             if (e) cudaEventDestroy(e);
@@ -1244,7 +1277,7 @@ int chk_get_image(chk_context* c, int which, const void** data, uint64_t* size) 
     CHK_REQUIRE(c && data && size, "NULL argument");
     CHK_REQUIRE(which >= 0 && which < 3, "which must be 0, 1 or 2");
     CHK_REQUIRE(c->have_images, "no host images: call chk_compress(ctx, 1) first");
-    *data = c->img[which].p;
+    *data = image_ptr(c, which);
     *size = c->img[which].size;
     CHK_API_END
 }
@@ -1306,12 +1339,34 @@ int chk_split(chk_context* c, const void* d_src, uint64_t n_elem, uint8_t dtype,
     const uint32_t vec = ((reinterpret_cast<uintptr_t>(d_src) | reinterpret_cast<uintptr_t>(d_masked)) & 15) == 0 &&
                          (reinterpret_cast<uintptr_t>(d_sidecar) & 7) == 0;
     const unsigned long long want = (nb / 16 + 255) / 256 + 1;
-    const uint32_t grid = (uint32_t)(want < 148ull * 16 ? want : 148ull * 16);
+    const unsigned long long cap = (unsigned long long)(c->sm_count > 0 ? c->sm_count : 1) * 16;
+    const uint32_t grid = (uint32_t)(want < cap ? want : cap);
     split_kernel<<<grid, 256, 0, c->stream>>>(static_cast<const uint8_t*>(d_src), nb, es, spe,
                                               static_cast<uint8_t*>(d_masked), static_cast<uint8_t*>(d_sidecar), vec);
     CHK_CUDA(cudaGetLastError());
     c->launches++;
     CHK_CUDA(cudaStreamSynchronize(c->stream));
+    CHK_API_END
+}
+
+int chk_merge(chk_context* c, const void* d_masked, const void* d_sidecar, uint64_t n_elem, uint8_t dtype, void* d_out) {
+    CHK_API_BEGIN
+    CHK_REQUIRE(c && d_masked && d_sidecar && d_out, "NULL argument");
+    const uint32_t es = elem_size(dtype), spe = sidecar_per_elem(dtype);
+    CHK_REQUIRE(es && spe, "dtype has no low-byte split");
+    if (n_elem == 0) return CHK_OK;
+    CHK_CUDA(cudaSetDevice(c->device));
+    const unsigned long long nb = n_elem * es;
+    const uint32_t vec = ((reinterpret_cast<uintptr_t>(d_masked) | reinterpret_cast<uintptr_t>(d_out)) & 15) == 0 &&
+                         (reinterpret_cast<uintptr_t>(d_sidecar) & 7) == 0;
+    const unsigned long long want = (nb / 16 + 255) / 256 + 1;
+    const unsigned long long cap = (unsigned long long)(c->sm_count > 0 ? c->sm_count : 1) * 16;
+    merge_kernel<<<(uint32_t)(want < cap ? want : cap), 256, 0, c->stream>>>(
+        static_cast<const uint8_t*>(d_masked), static_cast<const uint8_t*>(d_sidecar), nb, es, spe,
+        static_cast<uint8_t*>(d_out), vec);
+    CHK_CUDA(cudaGetLastError());
+    c->launches++;
+    sync_stream(c, c->stream);
     CHK_API_END
 }
 
@@ -1325,7 +1380,8 @@ int chk_byte_histogram(chk_context* c, const void* d_data, uint64_t n_bytes, uin
     dev_ensure(c, c->d_hist, 1024);
     CHK_CUDA(cudaMemsetAsync(c->d_hist.p, 0, 1024, c->stream));
     const unsigned long long want = (n_bytes / 16 + 255) / 256 + 1;
-    const uint32_t grid = (uint32_t)(want < 148ull * 8 ? want : 148ull * 8);
+    const unsigned long long cap = (unsigned long long)(c->sm_count > 0 ? c->sm_count : 1) * 8;
+    const uint32_t grid = (uint32_t)(want < cap ? want : cap);
     byte_histogram_kernel<<<grid, 256, 0, c->stream>>>(static_cast<const uint8_t*>(d_data), n_bytes,
                                                        static_cast<uint32_t*>(c->d_hist.p));
     CHK_CUDA(cudaGetLastError());
@@ -1372,6 +1428,8 @@ int chk_kernel_launches(chk_context* c, uint64_t* count) {
 }
 
 }  // extern "C"
+
+#include "host_stream.inc"
 
 // ====================================================================== encode without allocating
 // chk_encode_tensor_static: the rANS encode of ONE tensor whose working memory

@@ -290,6 +290,36 @@ __global__ void __launch_bounds__(256) split_kernel(const uint8_t* __restrict__ 
     }
 }
 
+// Stand-alone inverse of row 1: tensor = masked | low bytes (include/checkers/ANSCompressor.hpp:170).
+// The restore path does this inside the decode kernel; this stage exists for the per-stage sweep.
+__global__ void __launch_bounds__(256) merge_kernel(const uint8_t* __restrict__ masked, const uint8_t* __restrict__ sidecar,
+                                                    unsigned long long n_bytes, uint32_t es, uint32_t spe,
+                                                    uint8_t* __restrict__ out, uint32_t vector_ok) {
+    const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
+    const unsigned long long gid = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x;
+    unsigned long long body = 0;
+    if (vector_ok && spe * 2 == es && (es == 4 || es == 2)) {
+        const unsigned long long nvec = n_bytes >> 4;
+        body = nvec << 4;
+        for (unsigned long long v = gid; v < nvec; v += stride) {
+            const uint4 m = ld_global_v4(masked + v * 16);
+            const uint2 s = *reinterpret_cast<const uint2*>(sidecar + v * 8);
+            uint4 o;
+            if (es == 4) {
+                o = make_uint4(m.x | (s.x & 0xFFFFu), m.y | (s.x >> 16), m.z | (s.y & 0xFFFFu), m.w | (s.y >> 16));
+            } else {
+                o = make_uint4(m.x | __byte_perm(s.x, 0u, 0x4140), m.y | __byte_perm(s.x, 0u, 0x4342),
+                               m.z | __byte_perm(s.y, 0u, 0x4140), m.w | __byte_perm(s.y, 0u, 0x4342));
+            }
+            *reinterpret_cast<uint4*>(out + v * 16) = o;
+        }
+    }
+    for (unsigned long long i = body + gid; i < n_bytes; i += stride) {
+        const uint32_t j = (uint32_t)(i % es);
+        out[i] = j < spe ? sidecar[(i / es) * spe + j] : masked[i];
+    }
+}
+
 // Stand-alone row 2: 256-bin histogram of a byte buffer (hist must start at zero).
 __global__ void __launch_bounds__(256) byte_histogram_kernel(const uint8_t* __restrict__ data,
                                                              unsigned long long n_bytes,

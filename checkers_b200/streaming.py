@@ -1,29 +1,31 @@
-"""Chunked compression of HOST-resident state with overlapped copies.
+"""Chunked compression of HOST-resident state with overlapped copies: the Python face of the
+chk_stream_* entry points (include/checkers_b200.h).
 
-For state that does not live in (or does not fit into) HBM -- the 70B-class
-checkpoints streamed through a GPU in ~1 GiB pieces -- the rank's tensors are
-cut into chunks; every chunk owns a device staging buffer and a context, and
-host threads keep the three engines of the GPU busy at once: while chunk k is
-being compressed, chunk k+1 is on its way host->device and the file images of
-chunk k-1 are on their way device->host (PCIe is full duplex).  Restore runs
-the same way in the other direction.
+For state that does not live in (or does not fit into) HBM -- the 70B-class checkpoints streamed
+through a GPU in ~1 GiB pieces -- the rank's tensors are cut into consecutive parts; a few device
+staging buffers and contexts ("slots") are shared by all parts, and the library keeps the three
+engines of the GPU busy at once: while part k is being compressed, part k+1 is on its way
+host->device and the file images of part k-1 are on their way device->host (PCIe is full duplex).
+Restore runs the same way in the other direction.  The loop over parts, its threads, streams and
+events live in the C++ library; this module only hands over pointers.
 
-Each chunk produces a complete triple of reference-format files
-(<dir>/part_<k>/rank_<r>_states.ansc, mantissa/..., tables/...), so every
-part can be read on its own by anything that reads the reference's layout.
-The reference has no counterpart: it compresses device-resident tensors one
-by one under a global mutex (src/ANSCompressor.cpp:1204-1280 in the Checkers
-tree) and never reads them back.
+Each part is a complete triple of reference-format files
+(<dir>/part_<k>/rank_<r>_states.ansc, mantissa/..., tables/...), so every part can be read on its
+own by anything that reads the reference's layout.  The reference has no counterpart: it compresses
+device-resident tensors one by one under a global mutex (src/ANSCompressor.cpp:1204-1280 in the
+Checkers tree) and never reads them back.
 """
+import ctypes as C
 import os
-import threading
+
+import numpy as np
 
 from . import _lib
-from .context import Context
+from ._lib import check, lib
 
 
 class HostTensor:
-    """One named tensor in pinned host memory (a torch CPU tensor, contiguous)."""
+    """One named tensor in (preferably pinned) host memory: a contiguous torch CPU tensor."""
 
     def __init__(self, name, tensor, dtype_tag):
         if tensor.is_cuda or not tensor.is_contiguous():
@@ -33,15 +35,16 @@ class HostTensor:
         self.numel = self.nbytes // _lib.ELEM_SIZE[self.dtype]
 
 
-class _Chunk:
-    def __init__(self, index):
-        self.index, self.items, self.nbytes = index, [], 0
-        self.ctx = self.dev = self.ready = None
+class _Part:
+    def __init__(self, index, items):
+        self.index, self.items = index, items
+        self.nbytes = sum(t.nbytes for t in items)
 
 
 def plan_chunks(sizes, chunk_bytes):
     """Cut a sequence of tensor sizes (bytes) into consecutive chunks of at most chunk_bytes;
-    a tensor larger than that gets a chunk of its own.  Returns a list of index lists."""
+    a tensor larger than that gets a chunk of its own.  Returns a list of index lists.
+    (The library cuts the same way; this copy serves planning without a GPU.)"""
     chunks, cur, cur_bytes = [], [], 0
     for i, n in enumerate(sizes):
         if cur and cur_bytes + n > chunk_bytes:
@@ -64,7 +67,7 @@ def staging_offsets(sizes, align=256):
 
 
 class ChunkedHostPipeline:
-    """Fixed set of host tensors <-> compressed parts, through per-chunk device buffers.
+    """Fixed set of host tensors <-> compressed parts, through a few device staging slots.
 
     pipeline = ChunkedHostPipeline(host_tensors, device=0, rank=0, chunk_bytes=1 << 30)
     pipeline.compress()            # parts now sit in pinned host memory (pipeline.images(k))
@@ -72,108 +75,74 @@ class ChunkedHostPipeline:
     pipeline.restore(out_tensors)  # decode the parts back into host tensors
     """
 
-    def __init__(self, host_tensors, device=0, rank=0, chunk_bytes=1 << 30, workers=2):
-        import torch
-        self.torch, self.device, self.rank, self.workers = torch, int(device), int(rank), max(1, int(workers))
-        self.dev = torch.device("cuda", self.device)
-        host_tensors = list(host_tensors)
+    def __init__(self, host_tensors, device=0, rank=0, chunk_bytes=1 << 30, workers=3):
+        self.tensors = list(host_tensors)
+        self.device, self.rank = int(device), int(rank)
+        self._h = C.c_void_p()
+        check(lib.chk_stream_create(self.device, self.rank, int(chunk_bytes), max(1, min(int(workers), 8)),
+                                    C.byref(self._h)))
+        for t in self.tensors:
+            check(lib.chk_stream_add_tensor(self._h, t.name.encode(), C.c_void_p(t.tensor.data_ptr()), t.numel, t.dtype))
+        n = C.c_uint64()
+        check(lib.chk_stream_part_count(self._h, C.byref(n)))
         self.chunks = []
-        for idx in plan_chunks([ht.nbytes for ht in host_tensors], chunk_bytes):
-            ch = _Chunk(len(self.chunks))
-            ch.items = [host_tensors[i] for i in idx]
-            ch.nbytes = sum(ht.nbytes for ht in ch.items)
-            self.chunks.append(ch)
-        self.copy_in = torch.cuda.Stream(device=self.dev)
-        self.copy_out = torch.cuda.Stream(device=self.dev)
-        for ch in self.chunks:
-            # one staging allocation per chunk; every tensor starts on a 256-byte boundary
-            offs, total = staging_offsets([ht.nbytes for ht in ch.items])
-            ch.dev = torch.empty(max(total, 1), dtype=torch.uint8, device=self.dev)
-            ch.views = [ch.dev[o:o + ht.nbytes] for o, ht in zip(offs, ch.items)]
-            ch.ctx = Context(device=self.device, rank=self.rank)
-            for ht, v in zip(ch.items, ch.views):
-                ch.ctx.register_pointer(ht.name, v.data_ptr(), ht.numel, ht.dtype)
-            ch.ready = torch.cuda.Event()
-        torch.cuda.synchronize(self.dev)
+        for k in range(n.value):
+            first, cnt = C.c_uint64(), C.c_uint64()
+            check(lib.chk_stream_part_info(self._h, k, C.byref(first), C.byref(cnt)))
+            self.chunks.append(_Part(k, self.tensors[first.value:first.value + cnt.value]))
 
-    # ------------------------------------------------------------------ helpers
-    def _run_workers(self, fn):
-        """fn(chunk) for every chunk, chunk k on worker k % workers, in order within a worker."""
-        errors = []
-
-        def loop(w):
-            try:
-                self.torch.cuda.set_device(self.dev)
-                for ch in self.chunks[w::self.workers]:
-                    fn(ch)
-            except BaseException as e:  # noqa: BLE001 - re-raised on the calling thread
-                errors.append(e)
-
-        threads = [threading.Thread(target=loop, args=(w,)) for w in range(self.workers)]
-        for t in threads:
-            t.start()
-        for t in threads:
-            t.join()
-        if errors:
-            raise errors[0]
-
-    # ------------------------------------------------------------------ compress
     def compress(self):
-        """Host tensors -> per-chunk file images in pinned host memory."""
-        torch = self.torch
-        with torch.cuda.stream(self.copy_in):
-            for ch in self.chunks:
-                for ht, v in zip(ch.items, ch.views):
-                    v.copy_(ht.tensor.view(torch.uint8).reshape(-1), non_blocking=True)
-                ch.ready.record(self.copy_in)
-
-        def work(ch):
-            ch.ready.synchronize()              # this chunk's bytes are on the device
-            ch.ctx.compress(host_images=True)   # kernels + device->host copy of the three images
-
-        self._run_workers(work)
+        """Host tensors -> per-part file images in pinned host memory."""
+        check(lib.chk_stream_compress(self._h))
 
     def images(self, k):
-        return [self.chunks[k].ctx.image(i) for i in range(3)]
+        """The three file images of part k as uint8 numpy views (valid until the next compress)."""
+        out = []
+        for which in range(3):
+            p, n = C.c_void_p(), C.c_uint64()
+            check(lib.chk_stream_get_image(self._h, int(k), which, C.byref(p), C.byref(n)))
+            out.append(np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_uint8)), shape=(n.value,)) if n.value
+                       else np.zeros(0, np.uint8))
+        return out
 
     def summary(self):
-        keys = ("n_tensors", "n_tables", "states_bytes", "mantissa_bytes", "dict_bytes", "original_bytes")
-        tot = dict.fromkeys(keys, 0)
-        for ch in self.chunks:
-            s = ch.ctx.summary()
-            for k in keys:
-                tot[k] += s[k]
-        return tot
+        s = _lib.Summary()
+        check(lib.chk_stream_get_summary(self._h, C.byref(s)))
+        return {k: getattr(s, k) for k, _ in _lib.Summary._fields_}
 
     def save(self, directory):
         """Write every part as a reference-format file triple under directory/part_<k>/."""
-        tag = f"rank_{max(self.rank, 0)}"
-        for ch in self.chunks:
-            base = os.path.join(directory, f"part_{ch.index:04d}")
-            os.makedirs(os.path.join(base, "mantissa"), exist_ok=True)
-            os.makedirs(os.path.join(base, "tables"), exist_ok=True)
-            st, mt, dc = (ch.ctx.image(i) for i in range(3))
-            st.tofile(os.path.join(base, f"{tag}_states.ansc"))
-            mt.tofile(os.path.join(base, "mantissa", f"{tag}_mantissa.mant"))
-            dc.tofile(os.path.join(base, "tables", f"{tag}_tables.dict"))
+        check(lib.chk_stream_save(self._h, os.fspath(directory).encode()))
         return len(self.chunks)
 
-    # ------------------------------------------------------------------ restore
-    def restore(self, out_tensors):
-        """Parts (as left by compress()) -> out_tensors: CPU tensors in the order of the inputs."""
-        torch = self.torch
-        outs = iter(out_tensors)
-        targets = {ch.index: [next(outs) for _ in ch.items] for ch in self.chunks}
+    def load(self, directory):
+        """Read the parts written by save() back (restore() then decodes them)."""
+        check(lib.chk_stream_load(self._h, os.fspath(directory).encode()))
 
-        def work(ch):
-            ch.ctx.decompress_images(*[ch.ctx.image(i) for i in range(3)])  # host->device copy + decode
-            with torch.cuda.stream(self.copy_out):                          # restored bytes back to the host
-                for v, o in zip(ch.views, targets[ch.index]):
-                    o.view(torch.uint8).reshape(-1).copy_(v, non_blocking=True)
+    def restore(self, out_tensors=None):
+        """Parts (as left by compress() or load()) -> out_tensors: CPU tensors in the order of the
+        inputs (None: back into the input tensors)."""
+        if out_tensors is None:
+            check(lib.chk_stream_restore(self._h, None))
+            return
+        outs = list(out_tensors)
+        if len(outs) != len(self.tensors):
+            raise ValueError("one output tensor per input tensor")
+        arr = (C.c_void_p * max(len(outs), 1))(*[o.data_ptr() for o in outs])
+        check(lib.chk_stream_restore(self._h, arr))
 
-        self._run_workers(work)
-        self.copy_out.synchronize()
+    def timing(self, key):
+        v = C.c_double()
+        check(lib.chk_stream_get_timing(self._h, key.encode(), C.byref(v)))
+        return v.value
 
     def close(self):
-        for ch in self.chunks:
-            ch.ctx.close()
+        if self._h:
+            lib.chk_stream_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:  # noqa: BLE001
+            pass

@@ -146,6 +146,10 @@ int chk_restored_count(chk_context* ctx, uint64_t* count);
  * normalize_histogram (:416-503; host arithmetic, no device involved). */
 int chk_split(chk_context* ctx, const void* d_src, uint64_t num_elements, uint8_t dtype, void* d_masked,
               void* d_sidecar);
+/* Inverse of chk_split: out = masked | low bytes (include/checkers/ANSCompressor.hpp:170).  The restore path does
+ * this inside its decode kernel; the stand-alone stage exists for per-stage measurements. */
+int chk_merge(chk_context* ctx, const void* d_masked, const void* d_sidecar, uint64_t num_elements, uint8_t dtype,
+              void* d_out);
 int chk_byte_histogram(chk_context* ctx, const void* d_data, uint64_t n_bytes, uint32_t hist_out[256]);
 int chk_normalize_histogram(const uint32_t hist[256], int ensure_full_alphabet, int repair, uint32_t norm_freq[256],
                             uint32_t cum_freq[257], uint32_t x_max[256], uint32_t* sum_out);
@@ -186,6 +190,37 @@ int chk_repair_build(int device, const void* h_raw, uint64_t numel, uint32_t sto
                      uint64_t* tie_rounds_out);
 int chk_repair_apply(int device, const void* h_raw, uint64_t numel, uint32_t storage_bytes, uint32_t masked_bits,
                      const uint32_t* rule_lhs, const uint32_t* rule_rhs, uint32_t n_rules, uint64_t* tokens_out);
+
+/* ---- host-resident state, streamed through the GPU in chunks ---------------
+ * Has no counterpart in the reference, which compresses device-resident tensors one by one under a
+ * global mutex (src/ANSCompressor.cpp:1204-1280) and has no reader.
+ *
+ * For state that lives in host memory or does not fit into HBM (a 70B-class checkpoint in pieces of
+ * about 1 GiB).  Tensors are added in order (HOST pointers; pinned memory for full copy speed) and cut
+ * into consecutive parts of at most chunk_bytes.  `slots` (1..8, 3 is enough to keep the copy-in engine,
+ * the SMs and the copy-out engine busy at once) device staging buffers and contexts are shared by all
+ * parts, so device memory is slots x (chunk + its compress workspace) whatever the size of the state.
+ * chk_stream_compress leaves every part as a complete triple of reference-format file images in pinned
+ * host memory owned by the stream (chk_stream_get_image; chk_stream_save writes them as
+ * <dir>/part_<k>/rank_<r>_states.ansc, mantissa/..., tables/...); chk_stream_restore decodes the parts
+ * (as left by compress, or read back by chk_stream_load) into host_dst[i] for tensor i (NULL array: into
+ * the tensors' own buffers; NULL entry: skip).  One call drives all parts from one host thread per slot.
+ * Timing keys (sums over parts, CUDA-event times, so engines that overlap add up to more than the wall
+ * time): compress_h2d_ms, compress_kernel_ms, compress_d2h_ms, compress_wall_ms, restore_h2d_ms,
+ * restore_kernel_ms, restore_d2h_ms, restore_wall_ms. */
+typedef struct chk_stream chk_stream;
+int chk_stream_create(int device, int rank, uint64_t chunk_bytes, int slots, chk_stream** out);
+int chk_stream_destroy(chk_stream* s);
+int chk_stream_add_tensor(chk_stream* s, const char* name, void* host_ptr, uint64_t num_elements, uint8_t dtype);
+int chk_stream_compress(chk_stream* s);
+int chk_stream_restore(chk_stream* s, void* const* host_dst);
+int chk_stream_part_count(chk_stream* s, uint64_t* parts);
+int chk_stream_part_info(chk_stream* s, uint64_t part, uint64_t* first_tensor, uint64_t* n_tensors);
+int chk_stream_get_image(chk_stream* s, uint64_t part, int which, const void** data, uint64_t* size);
+int chk_stream_get_summary(chk_stream* s, chk_summary* out);
+int chk_stream_save(chk_stream* s, const char* output_dir);
+int chk_stream_load(chk_stream* s, const char* input_dir);
+int chk_stream_get_timing(chk_stream* s, const char* key, double* ms);
 
 /* ---- encode one tensor without allocating anything -----------------------
  * Has no counterpart in the reference (which allocates and frees device

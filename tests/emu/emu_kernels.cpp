@@ -57,6 +57,12 @@ void emu_split(const uint8_t* src, uint64_t n_bytes, uint32_t es, uint32_t spe, 
     emu::launch(grid, 256, 0, [&] { split_kernel(src, n_bytes, es, spe, masked, sidecar, vec); });
 }
 
+void emu_merge(const uint8_t* masked, const uint8_t* sidecar, uint64_t n_bytes, uint32_t es, uint32_t spe, uint8_t* out,
+               uint32_t grid) {
+    const uint32_t vec = ((uintptr_t)masked & 15) == 0 && ((uintptr_t)out & 15) == 0 && ((uintptr_t)sidecar & 7) == 0;
+    emu::launch(grid, 256, 0, [&] { merge_kernel(masked, sidecar, n_bytes, es, spe, out, vec); });
+}
+
 void emu_byte_histogram(const uint8_t* data, uint64_t n, uint32_t* hist, uint32_t grid) {
     std::memset(hist, 0, 1024);
     emu::launch(grid, 256, 0, [&] { byte_histogram_kernel(data, n, hist); });

@@ -129,6 +129,14 @@ def test_stage_kernels(emu, oracle):
         m, s = emu.split(raw, ELEM_SIZE[dt], SIDECAR_PER_ELEM[dt], misalign=mis)
         m_ref, s_ref = oracle.split(raw, dt)
         assert np.array_equal(m, m_ref) and np.array_equal(s, s_ref)
+        import ctypes as C
+        u8p = C.POINTER(C.c_uint8)
+        for shift in (0, 1):  # aligned (vector path) and not
+            mm, ss, oo = aligned(m.size + 16)[shift:shift + m.size], aligned(s.size + 16)[shift:shift + s.size], aligned(m.size + 16)[shift:shift + m.size]
+            mm[:], ss[:] = m_ref, s_ref
+            emu.lib.emu_merge(mm.ctypes.data_as(u8p), ss.ctypes.data_as(u8p), C.c_uint64(m.size), C.c_uint32(ELEM_SIZE[dt]),
+                              C.c_uint32(SIDECAR_PER_ELEM[dt]), oo.ctypes.data_as(u8p), C.c_uint32(2))
+            assert np.array_equal(oo, raw), (kind, shift)
         assert np.array_equal(emu.byte_histogram(m_ref, misalign=mis + 1), oracle.byte_histogram(m_ref))
 
 
