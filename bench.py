@@ -47,7 +47,7 @@ LLAMA3_8B = dict(hidden=4096, layers=32, inter=14336, q_heads=32, kv_heads=8, he
 PARAMS_8B = 8030261248
 # DRAM read + write bytes per byte of tensor, from one ncu capture of each kernel on a 939.5 MB slice of this
 # workload (1024 tensors of 256 Ki elements); the traffic of a launch grows in proportion to the tensor bytes
-NCU_DRAM_BYTES_PER_TENSOR_BYTE = {"rans_encode_fused_kernel": (1.356e9 + 0.810e9) / 939.5e6,
+NCU_DRAM_BYTES_PER_TENSOR_BYTE = {"rans_encode_fused_kernel": (1.350e9 + 0.810e9) / 939.5e6,
                                   "rans_decode_kernel": (0.905e9 + 0.902e9) / 939.5e6}
 
 

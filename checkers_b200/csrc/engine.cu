@@ -6,15 +6,14 @@
 // (ANSCompressor::compress_and_save_all, src/ANSCompressor.cpp:1014-1401 in the
 // Checkers tree: >= 8 stream syncs and 3 device-to-host copies per tensor) is
 // re-shaped here: all tensors of a rank go through each stage together --
-//   split_hist_kernel   (low bytes -> final .mant data layout, histograms), in a few
-//                       segments whose histograms the host normalises while the next
-//                       segment is counted; build_tables_kernel derives the encode tables
-//   rans_encode_kernel  (persistent grid of 64-thread teams, one tensor at a time each,
-//                       largest tensors first) + zero_lane_kernel on a side stream
-//   lane_scan_kernel / tensor_scan_kernel / compact_kernel
-//                       (payload laid out exactly as the .ansc data section)
-// so the host synchronises a handful of times per checkpoint instead of per tensor, and
-// the file images are filled by three large copies.
+//   split_hist_kernel         low bytes -> final .mant data layout, histograms; in a few pieces
+//   normalize_tables_kernel   frequency tables and encode entries of a piece, on the device,
+//   zero_chain_kernel         while the next piece is counted (a second stream)
+//   rans_encode_fused_kernel  one persistent grid of 64-thread teams, one tensor at a time each,
+//                             largest first: lanes, lane offsets, passthrough rule, headers and
+//                             the gather of the lanes into a payload heap
+// with ONE host synchronisation per checkpoint; the payload of each tensor is then copied
+// to its place in the .ansc image (file order) and the other two images by a large copy each.
 #include <cuda_runtime.h>
 
 #include <chrono>

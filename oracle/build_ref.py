@@ -67,7 +67,8 @@ def cut_block(text, start_regex, what):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("CHECKERS_REFERENCE", "/root/reference"))
+    ap.add_argument("--reference", default=os.environ.get("CHECKERS_REFERENCE", ""),
+                    help="the Checkers source tree (or set CHECKERS_REFERENCE)")
     args = ap.parse_args()
     ref = args.reference
     if not os.path.isdir(os.path.join(ref, "src")):
