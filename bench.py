@@ -235,14 +235,20 @@ def extras(args, torch, chk, ctx, shard_bytes, peak):
         return best
 
     # ---- statistics of the resident shard: two passes over every tensor (src/TensorAnalyzer.cpp:64-198)
-    ctx.analyze()
-    ms = min(ctx.timing("analyze_stats_ms") for _ in range(1))
-    for _ in range(2):
+    def analyze_ms():
         ctx.analyze()
-        ms = min(ms, ctx.timing("analyze_stats_ms"))
-    out["analyze"] = {"kernel": "tensor_stats_kernel", "ms": ms, "algorithmic_bytes": 2 * shard_bytes,
-                      "gbs": 2 * shard_bytes / ms / 1e6, "frac_of_hbm_peak": 2 * shard_bytes / ms / 1e6 / peak,
+        ms = ctx.timing("analyze_stats_ms")
+        for _ in range(2):
+            ctx.analyze()
+            ms = min(ms, ctx.timing("analyze_stats_ms"))
+        return {"ms": ms, "algorithmic_bytes": 2 * shard_bytes, "gbs": 2 * shard_bytes / ms / 1e6,
+                "frac_of_hbm_peak": 2 * shard_bytes / ms / 1e6 / peak}
+
+    out["analyze"] = {"reference_order": dict(analyze_ms(), kernel="tensor_stats_kernel"),
                       "cluster_ms": ctx.timing("analyze_cluster_ms"), "tensors": ctx.tensor_count()}
+    ctx.set_option("fast_stats", 1)
+    out["analyze"]["fast"] = dict(analyze_ms(), kernel="stats_fast_pass1/2_kernel (sums in double, order-free)")
+    ctx.set_option("fast_stats", 0)
 
     # ---- codec microbenchmark configuration: 1 GiB fp32 ~ N(0, 1e-3) and 1 GiB bf16 ~ N(0, 0.02), seed 1, 4 MiB chunks
     g = torch.Generator(device=dev).manual_seed(1)

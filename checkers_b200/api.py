@@ -142,7 +142,7 @@ def _timing(key, ms):
 
 
 def initialize_context(model_engine, optimizer=None, histogram_bins=256, background_threads=1, *,
-                       shared_tables="reference"):
+                       shared_tables="reference", analysis_mode="reference"):
     """Registers the rank's tensors.  `model_engine` may be an engine/module with
     named_parameters(), or a dict / list of (name, CUDA tensor) pairs.
     `background_threads` is accepted for signature compatibility; registration
@@ -151,7 +151,13 @@ def initialize_context(model_engine, optimizer=None, histogram_bins=256, backgro
     shared_tables (an addition): what to do when analyze_tensors() has grouped tensors into clusters
     whose shared table the reference's normalisation leaves undecodable (every bf16 cluster):
     "reference" refuses to write such files (compress_and_save raises), "reference_bytes" writes the
-    reference's exact, unrestorable bytes, "repair" renormalises shared tables so they decode."""
+    reference's exact, unrestorable bytes, "repair" renormalises shared tables so they decode.
+
+    analysis_mode (an addition): "reference" computes the statistics of analyze_tensors() in the
+    reference's order of float additions (bit-identical results, one thread block per tensor); "fast"
+    spreads every tensor over the whole device and sums in double: minimum, maximum and the value
+    histogram are the same, the moments differ by the rounding error of the reference's float sums,
+    so a cluster boundary can fall differently."""
     global _ctx, _initialized, _log_file
     import time
     t0 = time.perf_counter()
@@ -162,6 +168,8 @@ def initialize_context(model_engine, optimizer=None, histogram_bins=256, backgro
             raise RuntimeError("background_threads must be greater than zero")
         if shared_tables not in ("reference", "reference_bytes", "repair"):
             raise RuntimeError("shared_tables must be 'reference', 'reference_bytes' or 'repair'")
+        if analysis_mode not in ("reference", "fast"):
+            raise RuntimeError("analysis_mode must be 'reference' or 'fast'")
         rank = _env_rank(model_engine, "global_rank", "RANK")
         local_rank = _env_rank(model_engine, "local_rank", "LOCAL_RANK")
         t1 = time.perf_counter()
@@ -184,6 +192,7 @@ def initialize_context(model_engine, optimizer=None, histogram_bins=256, backgro
         _ctx.set_histogram_bins(histogram_bins)
         _ctx.set_option("repair_tables", int(shared_tables == "repair"))
         _ctx.set_option("allow_undecodable", int(shared_tables == "reference_bytes"))
+        _ctx.set_option("fast_stats", int(analysis_mode == "fast"))
         for name, t in pairs:
             if not getattr(t, "is_cuda", False):
                 continue  # no local device storage on this rank

@@ -84,8 +84,9 @@ inline ClusterMap build_clusters(const std::vector<std::string>& names, const st
             for (int b = a + 1; b < m; ++b) pairwise.push_back(distance(a, b));
         double threshold = 0.0;
         if (!pairwise.empty()) {
+            // the reference sorts all distances and takes element size/4; that order statistic is all it uses
             std::vector<double> sorted = pairwise;
-            std::sort(sorted.begin(), sorted.end());
+            std::nth_element(sorted.begin(), sorted.begin() + sorted.size() / 4, sorted.end());
             threshold = sorted[sorted.size() / 4];
         }
 

@@ -117,10 +117,11 @@ struct Context {
     std::vector<StatsOut> stats;
 
     bool repair_tables = false, verify_zero_lanes = false, allow_undecodable = false;
+    bool fast_stats = false;      // statistics with order-free sums over the whole device (see stats_kernels.cuh)
     bool decode_two_level = false;
 
     // device buffers (grow-only, from the context's pool)
-    DevBuf d_descs, d_tiles, d_hist, d_sidecar, d_scratch, d_hdrs, d_order, d_ticket, d_psize, d_zslots, d_zregions, d_zslot_of, d_jobs, d_sums,
+    DevBuf d_descs, d_tiles, d_hist, d_sidecar, d_scratch, d_hdrs, d_order, d_ticket, d_psize, d_zslots, d_zregions, d_zslot_of, d_jobs, d_sums, d_stats_part, d_stats_mid,
         d_payload, d_enc, d_freq, d_cum, d_status, d_stats_desc, d_stats_out;
     cudaStream_t side_stream = nullptr;
     std::vector<cudaEvent_t> ev_count, ev_tab;
@@ -1009,12 +1010,45 @@ static void analyze(Context* c) {
     CHK_CUDA(cudaMemcpyAsync(c->d_stats_desc.p, d.data(), N * sizeof(StatsDesc), cudaMemcpyHostToDevice, s));
     CHK_CUDA(cudaMemsetAsync(c->d_stats_out.p, 0, N * sizeof(StatsOut), s));
     CHK_CUDA(cudaEventRecord(c->ev[0], s));
-    const size_t cap = (size_t)(c->sm_count > 0 ? c->sm_count : 1) * 64;
-    const uint32_t grid = (uint32_t)(N < cap ? N : cap);
-    tensor_stats_kernel<<<grid, 256, 0, s>>>(static_cast<const StatsDesc*>(c->d_stats_desc.p),
-                                             static_cast<StatsOut*>(c->d_stats_out.p), (uint32_t)N);
-    CHK_CUDA(cudaGetLastError());
-    c->launches++;
+    if (!c->fast_stats) {
+        const size_t cap = (size_t)(c->sm_count > 0 ? c->sm_count : 1) * 64;
+        const uint32_t grid = (uint32_t)(N < cap ? N : cap);
+        tensor_stats_kernel<<<grid, 256, 0, s>>>(static_cast<const StatsDesc*>(c->d_stats_desc.p),
+                                                 static_cast<StatsOut*>(c->d_stats_out.p), (uint32_t)N);
+        CHK_CUDA(cudaGetLastError());
+        c->launches++;
+    } else {
+        // the order-free variant: tiles of all tensors over the whole device, two passes
+        pin_ensure(c->h_tiles, (N + 1) * 4);
+        uint32_t* tile_start = static_cast<uint32_t*>(c->h_tiles.p);
+        unsigned long long tiles = 0;
+        for (size_t i = 0; i < N; ++i) {
+            tile_start[i] = (uint32_t)tiles;
+            if (d[i].ptr && d[i].n) tiles += (d[i].n * elem_size(c->tensors[i].dtype) + kStatsTileBytes - 1) / kStatsTileBytes;
+            if (tiles > 0xFFFFFFFFull) throw Error{CHK_ERR_CAPACITY, "too many statistics tiles in one batch"};
+        }
+        tile_start[N] = (uint32_t)tiles;
+        if (tiles) {
+            dev_ensure(c, c->d_tiles, (N + 1) * 4);
+            dev_ensure(c, c->d_stats_part, (size_t)tiles * (sizeof(StatsPart1) + sizeof(StatsPart2)));
+            dev_ensure(c, c->d_stats_mid, N * sizeof(StatsMid));
+            control_copy(c, c->d_tiles.p, c->h_tiles.p, (N + 1) * 4, s);
+            auto* p1 = static_cast<StatsPart1*>(c->d_stats_part.p);
+            auto* p2 = reinterpret_cast<StatsPart2*>(p1 + tiles);
+            const auto* dd = static_cast<const StatsDesc*>(c->d_stats_desc.p);
+            const auto* ts = static_cast<const uint32_t*>(c->d_tiles.p);
+            auto* mids = static_cast<StatsMid*>(c->d_stats_mid.p);
+            auto* outs = static_cast<StatsOut*>(c->d_stats_out.p);
+            const unsigned long long cap = (unsigned long long)(c->sm_count > 0 ? c->sm_count : 1) * 8;
+            const uint32_t grid = (uint32_t)(tiles < cap ? tiles : cap);
+            stats_fast_pass1_kernel<<<grid, 256, 0, s>>>(dd, ts, (uint32_t)N, (uint32_t)tiles, p1);
+            stats_fast_reduce1_kernel<<<(uint32_t)N, 256, 0, s>>>(dd, ts, p1, mids, outs, (uint32_t)N);
+            stats_fast_pass2_kernel<<<grid, 256, 0, s>>>(dd, ts, (uint32_t)N, (uint32_t)tiles, mids, p2, outs);
+            stats_fast_reduce2_kernel<<<(uint32_t)N, 256, 0, s>>>(dd, ts, p2, outs, (uint32_t)N);
+            CHK_CUDA(cudaGetLastError());
+            c->launches += 4;
+        }
+    }
     CHK_CUDA(cudaEventRecord(c->ev[1], s));
     CHK_CUDA(cudaMemcpyAsync(c->h_stats.p, c->d_stats_out.p, N * sizeof(StatsOut), cudaMemcpyDeviceToHost, s));
     sync_stream(c, s);
@@ -1107,7 +1141,7 @@ int chk_context_destroy(chk_context* c) {
     if (c->stream) cudaStreamSynchronize(c->stream);
     DevBuf* bufs[] = {&c->d_descs, &c->d_tiles, &c->d_hist, &c->d_sidecar, &c->d_scratch, &c->d_hdrs,
                       &c->d_order, &c->d_ticket, &c->d_psize, &c->d_zslots, &c->d_zregions, &c->d_zslot_of, &c->d_jobs, &c->d_sums, &c->d_payload, &c->d_enc,
-                      &c->d_freq, &c->d_cum, &c->d_status, &c->d_stats_desc, &c->d_stats_out};
+                      &c->d_freq, &c->d_cum, &c->d_status, &c->d_stats_desc, &c->d_stats_out, &c->d_stats_part, &c->d_stats_mid};
     for (DevBuf* b : bufs)
         if (b->p) cudaFreeAsync(b->p, c->stream);
     if (c->stream) cudaStreamSynchronize(c->stream);
@@ -1176,6 +1210,8 @@ int chk_set_option(chk_context* c, const char* key, int64_t value) {
         c->repair_tables = value != 0;
     else if (k == "verify_zero_lanes")
         c->verify_zero_lanes = value != 0;
+    else if (k == "fast_stats")
+        c->fast_stats = value != 0;
     else if (k == "allow_undecodable")
         c->allow_undecodable = value != 0;
 

@@ -65,8 +65,9 @@ struct LaneHeader {
 // is below freq <= 2^s, so x * err < 2^(31+s)).  freq == 1 uses rcp = 2^32-1,
 // which yields x - 1, and folds the missing 4095 into `bias`.
 // The new state is x + q * cmpl + bias with cmpl = 4096 - freq, bias = cum_freq.
-// One 16-byte shared-memory load per symbol.  freq == 0 marks a symbol that is
-// not in the table.
+// This is the layout in global memory; an encode team packs its table into
+// 8-byte entries in shared memory (see EncSmem).  freq == 0 marks a symbol that
+// is not in the table.
 struct EncEntry {
     uint32_t rcp;
     uint32_t freq_shift;  // freq[0:16) | shift[16:32)
@@ -126,8 +127,7 @@ __device__ __forceinline__ void split_one_byte(const TensorDesc& d, unsigned lon
 // packed low bytes straight into its slice of the sidecar section and counts
 // the bytes the codec will see, except the zeroed ones (num_elements*spe are
 // added to bin 0 where the tables are built).  The masked copy is never
-// materialised.  With sidecar == nullptr the pass only counts (the compress
-// pipeline lets the encoder, which reads every byte anyway, write the low bytes).
+// materialised.  With sidecar == nullptr the pass only counts.
 // Tiles are handed to CTAs in contiguous ranges so a CTA mostly stays inside
 // one tensor and merges its bins into global memory once per tensor.
 __global__ void __launch_bounds__(256) split_hist_kernel(const TensorDesc* __restrict__ descs,
@@ -411,6 +411,97 @@ struct StatsOut {
     float pad_;
 };
 
+template <int DT>
+__device__ __forceinline__ float load_value_t(const void* p, unsigned long long i) {
+    if (DT == 0) return reinterpret_cast<const float*>(p)[i];
+    if (DT == 1) return __uint_as_float((uint32_t)reinterpret_cast<const uint16_t*>(p)[i] << 16);
+    if (DT == 2) return half_bits_to_float(reinterpret_cast<const uint16_t*>(p)[i]);
+    if (DT == 3) return (float)reinterpret_cast<const int8_t*>(p)[i];
+    return (float)reinterpret_cast<const int32_t*>(p)[i];
+}
+
+constexpr int kStatsAhead = 8;  // loads a thread has in flight before it uses the first
+
+// Value histogram bin (src/TensorAnalyzer.cpp:139-146): float arithmetic, nothing fused.
+__device__ __forceinline__ int stats_bin(float x, float vmin, float scale, int bins, bool wide) {
+    if (!wide) return 0;
+    int b = (int)__fmul_rn(__fsub_rn(x, vmin), scale);
+    return max(0, min(b, bins - 1));
+}
+
+// Counts go to the warp's private bins, and equal consecutive bins of a thread are
+// added in one go: a skewed tensor (second moments: nearly everything in bin 0)
+// would otherwise serialise 32 lanes on one counter.
+struct BinRun {
+    int cur = -1;
+    uint32_t run = 0;
+    __device__ __forceinline__ void add(uint32_t* wh, int b) {
+        if (b == cur) {
+            ++run;
+        } else {
+            if (run) atomicAdd(&wh[cur], run);
+            cur = b;
+            run = 1;
+        }
+    }
+    __device__ __forceinline__ void flush(uint32_t* wh) {
+        if (run) atomicAdd(&wh[cur], run);
+        cur = -1;
+        run = 0;
+    }
+};
+
+// The two passes of one tensor in the reference's order: thread t takes elements
+// t, t+256, ... one after the other (kStatsAhead of them are loaded before the first
+// is used; the order of the arithmetic is unchanged).
+template <int DT>
+__device__ __forceinline__ void stats_pass1(const void* p, unsigned long long n, uint32_t t, float& lo, float& hi,
+                                            float& sum) {
+    unsigned long long i = t;
+    for (; i + (unsigned long long)(kStatsAhead - 1) * 256 < n; i += (unsigned long long)kStatsAhead * 256) {
+        float v[kStatsAhead];
+#pragma unroll
+        for (int k = 0; k < kStatsAhead; ++k) v[k] = load_value_t<DT>(p, i + (unsigned long long)k * 256);
+#pragma unroll
+        for (int k = 0; k < kStatsAhead; ++k) {
+            lo = fminf(lo, v[k]);
+            hi = fmaxf(hi, v[k]);
+            sum = __fadd_rn(sum, v[k]);
+        }
+    }
+    for (; i < n; i += 256) {
+        const float x = load_value_t<DT>(p, i);
+        lo = fminf(lo, x);
+        hi = fmaxf(hi, x);
+        sum = __fadd_rn(sum, x);
+    }
+}
+
+template <int DT>
+__device__ __forceinline__ void stats_pass2(const void* p, unsigned long long n, uint32_t t, float vmin, float mean,
+                                            float scale, int bins, bool wide, uint32_t* wh, float& m2, float& m3,
+                                            float& m4) {
+    BinRun br;
+    auto one = [&](float x) {
+        if (bins > 0) br.add(wh, stats_bin(x, vmin, scale, bins, wide));
+        const float dd = __fsub_rn(x, mean);
+        const float d2 = __fmul_rn(dd, dd);
+        m2 = __fadd_rn(m2, d2);
+        m3 = __fadd_rn(m3, __fmul_rn(d2, dd));
+        m4 = __fadd_rn(m4, __fmul_rn(d2, d2));
+    };
+    unsigned long long i = t;
+    for (; i + (unsigned long long)(kStatsAhead - 1) * 256 < n; i += (unsigned long long)kStatsAhead * 256) {
+        float v[kStatsAhead];
+#pragma unroll
+        for (int k = 0; k < kStatsAhead; ++k) v[k] = load_value_t<DT>(p, i + (unsigned long long)k * 256);
+#pragma unroll
+        for (int k = 0; k < kStatsAhead; ++k) one(v[k]);
+    }
+    for (; i < n; i += 256) one(load_value_t<DT>(p, i));
+    br.flush(wh);
+}
+
 // One CTA per tensor, 256 threads, two passes, all in float and in the
 // reference's order: thread t accumulates elements t, t+256, ... one after the
 // other, the 256 partials are combined by the same halving tree, and no
@@ -418,22 +509,24 @@ struct StatsOut {
 __global__ void __launch_bounds__(256) tensor_stats_kernel(const StatsDesc* __restrict__ descs,
                                                            StatsOut* __restrict__ outs, uint32_t n_tensors) {
     CHK_SHARED float ra[256], rb[256], rc[256];
-    CHK_SHARED uint32_t s_hist[256];
+    CHK_SHARED uint32_t s_hist[8 * 256];
     CHK_SHARED float s_min, s_max, s_mean;
     const uint32_t t = threadIdx.x;
+    uint32_t* const wh = s_hist + (t >> 5) * 256;
     for (uint32_t ti = blockIdx.x; ti < n_tensors; ti += gridDim.x) {
         const StatsDesc d = descs[ti];
         StatsOut& o = outs[ti];
         const uint32_t bins = d.bins < 256u ? d.bins : 256u;
-        if (!d.ptr || d.n == 0) continue;
-        s_hist[t] = 0;
+        if (!d.ptr || d.n == 0 || d.dtype > 4u) continue;
+        for (uint32_t k = t; k < 8 * 256; k += 256) s_hist[k] = 0;
 
         float lo = 1e37f, hi = -1e37f, sum = 0.0f;
-        for (unsigned long long i = t; i < d.n; i += 256) {
-            const float x = load_value(d.ptr, i, d.dtype);
-            lo = fminf(lo, x);
-            hi = fmaxf(hi, x);
-            sum = __fadd_rn(sum, x);
+        switch (d.dtype) {
+            case 0: stats_pass1<0>(d.ptr, d.n, t, lo, hi, sum); break;
+            case 1: stats_pass1<1>(d.ptr, d.n, t, lo, hi, sum); break;
+            case 2: stats_pass1<2>(d.ptr, d.n, t, lo, hi, sum); break;
+            case 3: stats_pass1<3>(d.ptr, d.n, t, lo, hi, sum); break;
+            default: stats_pass1<4>(d.ptr, d.n, t, lo, hi, sum); break;
         }
         ra[t] = lo;
         rb[t] = hi;
@@ -455,23 +548,16 @@ __global__ void __launch_bounds__(256) tensor_stats_kernel(const StatsDesc* __re
         __syncthreads();
         const float vmin = s_min, mean = s_mean;
         const float range = __fsub_rn(s_max, vmin);
-        const float scale = range > 1e-9f ? __fdiv_rn(__fsub_rn((float)bins, 1.0f), range) : 0.0f;
+        const bool wide = range > 1e-9f;
+        const float scale = wide ? __fdiv_rn(__fsub_rn((float)bins, 1.0f), range) : 0.0f;
 
         float m2 = 0.0f, m3 = 0.0f, m4 = 0.0f;
-        for (unsigned long long i = t; i < d.n; i += 256) {
-            const float x = load_value(d.ptr, i, d.dtype);
-            if (range > 1e-9f) {
-                int b = (int)__fmul_rn(__fsub_rn(x, vmin), scale);
-                b = max(0, min(b, (int)bins - 1));
-                atomicAdd(&s_hist[b], 1u);
-            } else if (bins > 0) {
-                atomicAdd(&s_hist[0], 1u);
-            }
-            const float dd = __fsub_rn(x, mean);
-            const float d2 = __fmul_rn(dd, dd);
-            m2 = __fadd_rn(m2, d2);
-            m3 = __fadd_rn(m3, __fmul_rn(d2, dd));
-            m4 = __fadd_rn(m4, __fmul_rn(d2, d2));
+        switch (d.dtype) {
+            case 0: stats_pass2<0>(d.ptr, d.n, t, vmin, mean, scale, (int)bins, wide, wh, m2, m3, m4); break;
+            case 1: stats_pass2<1>(d.ptr, d.n, t, vmin, mean, scale, (int)bins, wide, wh, m2, m3, m4); break;
+            case 2: stats_pass2<2>(d.ptr, d.n, t, vmin, mean, scale, (int)bins, wide, wh, m2, m3, m4); break;
+            case 3: stats_pass2<3>(d.ptr, d.n, t, vmin, mean, scale, (int)bins, wide, wh, m2, m3, m4); break;
+            default: stats_pass2<4>(d.ptr, d.n, t, vmin, mean, scale, (int)bins, wide, wh, m2, m3, m4); break;
         }
         __syncthreads();
         ra[t] = m2;
@@ -486,7 +572,12 @@ __global__ void __launch_bounds__(256) tensor_stats_kernel(const StatsDesc* __re
             }
             __syncthreads();
         }
-        o.hist[t] = t < bins ? s_hist[t] : 0u;
+        {
+            uint32_t cnt = 0;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) cnt += s_hist[w * 256 + t];
+            o.hist[t] = t < bins ? cnt : 0u;
+        }
         if (t == 0) {
             const float nf = (float)d.n;
             const float M2 = __fdiv_rn(ra[0], nf), M3 = __fdiv_rn(rb[0], nf), M4 = __fdiv_rn(rc[0], nf);
@@ -513,3 +604,5 @@ __global__ void __launch_bounds__(256) tensor_stats_kernel(const StatsDesc* __re
 }
 
 }  // namespace chk
+
+#include "stats_kernels.cuh"

@@ -87,7 +87,12 @@ int chk_tensor_count(chk_context* ctx, uint64_t* count);
  * counted), "encode_teams_per_sm" / "decode_teams_per_sm" (default 0 = as many as
  * fit: cap on the resident teams per SM), "decode_two_level" (0/1; 5 KiB two-level
  * decode table instead of 16 KiB).  None of the tuning options changes the bytes
- * that are produced. */
+ * that are produced.
+ * "fast_stats" (0/1, default 0): chk_analyze sums in double over tiles spread over the
+ * whole device instead of in the reference's order of float additions: minimum,
+ * maximum and value histogram are unchanged, mean / variance / skewness / kurtosis
+ * differ by the rounding error of the reference's float sums (and cluster boundaries
+ * that hang on that error can move). */
 int chk_set_option(chk_context* ctx, const char* key, int64_t value);
 
 /* ---- analysis: checkers::analyze_tensors, src/api.cpp:1033-1253 ----------

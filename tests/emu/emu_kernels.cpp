@@ -240,6 +240,37 @@ void emu_stats(size_t n, const void* const* ptrs, const uint64_t* n_elem, const 
     emu::launch(grid, 256, 0, [&] { tensor_stats_kernel(d.data(), (StatsOut*)outs, (uint32_t)n); });
 }
 
+// the order-free variant: same outputs, four launches
+void emu_stats_fast(size_t n, const void* const* ptrs, const uint64_t* n_elem, const uint32_t* dtype, uint32_t bins,
+                    void* outs, uint32_t grid) {
+    std::vector<StatsDesc> d(n);
+    std::vector<uint32_t> tile_start(n + 1);
+    uint32_t tiles = 0;
+    for (size_t i = 0; i < n; ++i) {
+        d[i] = StatsDesc{ptrs[i], n_elem[i], dtype[i], bins};
+        tile_start[i] = tiles;
+        const uint64_t bytes = n_elem[i] * stats_elem_size(dtype[i]);
+        if (ptrs[i] && n_elem[i]) tiles += (uint32_t)((bytes + kStatsTileBytes - 1) / kStatsTileBytes);
+    }
+    tile_start[n] = tiles;
+    std::memset(outs, 0, n * sizeof(StatsOut));
+    if (!tiles) return;
+    std::vector<StatsPart1> p1(tiles);
+    std::vector<StatsPart2> p2(tiles);
+    std::vector<StatsMid> mids(n);
+    if (grid > tiles) grid = tiles;
+    emu::launch(grid, 256, 0, [&] { stats_fast_pass1_kernel(d.data(), tile_start.data(), (uint32_t)n, tiles, p1.data()); });
+    emu::launch((uint32_t)n, 256, 0, [&] {
+        stats_fast_reduce1_kernel(d.data(), tile_start.data(), p1.data(), mids.data(), (StatsOut*)outs, (uint32_t)n);
+    });
+    emu::launch(grid, 256, 0, [&] {
+        stats_fast_pass2_kernel(d.data(), tile_start.data(), (uint32_t)n, tiles, mids.data(), p2.data(), (StatsOut*)outs);
+    });
+    emu::launch((uint32_t)n, 256, 0, [&] {
+        stats_fast_reduce2_kernel(d.data(), tile_start.data(), p2.data(), (StatsOut*)outs, (uint32_t)n);
+    });
+}
+
 // the host routine the device kernel must agree with
 void emu_host_enc_entries(const uint32_t* nf, const uint32_t* cf, uint32_t* enc_out) {
     FreqTable ft;

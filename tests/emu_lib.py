@@ -147,14 +147,14 @@ class Emu:
                             C.c_uint32(int(float_only)))
         return outs, status
 
-    def stats(self, tensors, n_elem, dtypes, bins=256, grid=2):
+    def stats(self, tensors, n_elem, dtypes, bins=256, grid=2, fast=False):
         n, ptrs = self._arrays(tensors)
         ne = np.array(n_elem, np.uint64)
         dt = np.array(dtypes, np.uint32)
         words = self.lib.emu_stats_out_bytes() // 4
         out = np.zeros((n, words), np.uint32)
-        self.lib.emu_stats(C.c_size_t(n), ptrs, _p(ne, u64p), _p(dt, u32p), C.c_uint32(bins), _p(out, C.c_void_p),
-                           C.c_uint32(grid))
+        fn = self.lib.emu_stats_fast if fast else self.lib.emu_stats
+        fn(C.c_size_t(n), ptrs, _p(ne, u64p), _p(dt, u32p), C.c_uint32(bins), _p(out, C.c_void_p), C.c_uint32(grid))
         res = []
         for i in range(n):
             res.append((out[i, :256].copy(), out[i, 256:260].view(np.float32).copy(),

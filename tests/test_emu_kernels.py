@@ -140,9 +140,36 @@ def test_stage_kernels(emu, oracle):
         assert np.array_equal(emu.byte_histogram(m_ref, misalign=mis + 1), oracle.byte_histogram(m_ref))
 
 
+def _assert_fast_stats(got, want_hist, want_mom, want_mm):
+    """The order-free statistics against the reference-order ones: what does not depend on the order is
+    identical, the rest agrees to the rounding error of the reference's float chains."""
+    hist, mom, mm, fp = got
+    assert np.array_equal(hist, want_hist)
+    assert np.array_equal(mm.view(np.uint32), want_mm.view(np.uint32))
+    spread = max(abs(float(want_mm[0])), abs(float(want_mm[1])), 1e-30)
+    assert abs(float(mom[0]) - float(want_mom[0])) <= 1e-5 * spread                      # mean
+    assert abs(float(mom[1]) - float(want_mom[1])) <= 1e-4 * abs(float(want_mom[1])) + 1e-12   # variance
+    assert abs(float(mom[2]) - float(want_mom[2])) <= 1e-3 * max(1.0, abs(float(want_mom[2])))  # skewness
+    assert abs(float(mom[3]) - float(want_mom[3])) <= 1e-3 * max(1.0, abs(float(want_mom[3])))  # kurtosis
+    assert np.array_equal(fp[:4].view(np.uint32), mom.view(np.uint32))
+    assert fp[4] == np.float32(want_mm[1] - want_mm[0])
+
+
+def test_fast_stats_kernels(emu, oracle):
+    cases = [("bf16_weight", 70001), ("f32_master", 40000), ("f16_weight", 2048), ("i8", 300), ("i32", 1000),
+             ("bf16_norm_gain", 513), ("f32_exp_avg_sq_lognormal", 33000), ("f32_master", 1), ("i8", 140000)]
+    for mis in (None, [1]):   # 16-byte loads possible / not
+        tensors, es, spe, dts = make(cases, 4, mis)
+        for bins, grid in ((256, 3), (64, 64)):
+            res = emu.stats(tensors, [a.size // e for a, e in zip(tensors, es)], dts, bins=bins, grid=grid, fast=True)
+            for i, a in enumerate(tensors):
+                h, mom, mm = oracle.tensor_stats(a, dts[i], bins)
+                _assert_fast_stats(res[i], h, mom, mm)
+
+
 def test_stats_kernel(emu, oracle):
     cases = [("bf16_weight", 5000), ("f32_master", 4099), ("f16_weight", 2048), ("i8", 300), ("i32", 1000),
-             ("bf16_norm_gain", 513), ("f32_exp_avg_sq", 256), ("f32_master", 1)]
+             ("bf16_norm_gain", 513), ("f32_exp_avg_sq", 256), ("f32_master", 1), ("f32_exp_avg_sq_lognormal", 9000)]
     tensors, es, spe, dts = make(cases, 4)
     for bins in (256, 64):
         res = emu.stats(tensors, [a.size // e for a, e in zip(tensors, es)], dts, bins=bins)

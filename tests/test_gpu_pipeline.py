@@ -234,3 +234,43 @@ def test_checkers_py_call_sequence_and_timing_log(tmp_path, monkeypatch):
     torch.cuda.synchronize()
     for p, b in zip(module.parameters(), before):
         assert torch.equal(p.detach(), b)
+
+
+def test_fast_statistics_against_oracle(chk, oracle):
+    """analysis in the order-free mode: minimum, maximum and value histogram identical to the reference-order
+    statistics, moments within the rounding error of the reference's float sums; large and unaligned tensors."""
+    cases = [("bf16_weight", 3_000_001), ("f32_master", 1 << 20), ("f32_exp_avg_sq_lognormal", 700_003),
+             ("bf16_norm_gain", 4096), ("i8", 1_000_000), ("i32", 65_537), ("f16_weight", 250_000), ("f32_exp_avg", 1)]
+    host, dts, dev, views = [], [], [], []
+    for i, (kind, n) in enumerate(cases):
+        raw, dt = synth(kind, n, 300 + i)
+        host.append(raw)
+        dts.append(dt)
+        buf = torch.zeros(raw.size + 64, dtype=torch.uint8, device="cuda")
+        off = ELEM_SIZE[dt] if i % 3 == 2 else 0      # every third tensor starts off a 16-byte boundary
+        buf[off:off + raw.size] = torch.from_numpy(raw.copy()).cuda()
+        dev.append(buf)
+        views.append(buf.data_ptr() + off)
+    ctx = chk.Context(device=0)
+    ctx.set_option("fast_stats", 1)
+    for i, (raw, dt) in enumerate(zip(host, dts)):
+        ctx.register_pointer(f"t{i}", views[i], raw.size // ELEM_SIZE[dt], dt)
+    for bins in (256, 100):
+        ctx.set_histogram_bins(bins)
+        ctx.analyze()
+        first = [ctx.tensor_stats(i) for i in range(len(host))]
+        ctx.analyze()
+        for i, (raw, dt) in enumerate(zip(host, dts)):
+            hist, mom, mm, fp = ctx.tensor_stats(i)
+            h_ref, mom_ref, mm_ref = oracle.tensor_stats(raw, dt, bins=bins)
+            assert np.array_equal(hist, h_ref), i
+            assert np.array_equal(mm.view(np.uint32), mm_ref.view(np.uint32)), i
+            spread = max(abs(float(mm_ref[0])), abs(float(mm_ref[1])), 1e-30)
+            assert abs(float(mom[0]) - float(mom_ref[0])) <= 1e-5 * spread, (i, mom, mom_ref)
+            assert abs(float(mom[1]) - float(mom_ref[1])) <= 1e-4 * abs(float(mom_ref[1])) + 1e-12, (i, mom, mom_ref)
+            assert abs(float(mom[2]) - float(mom_ref[2])) <= 1e-3 * max(1.0, abs(float(mom_ref[2]))), (i, mom, mom_ref)
+            assert abs(float(mom[3]) - float(mom_ref[3])) <= 1e-3 * max(1.0, abs(float(mom_ref[3]))), (i, mom, mom_ref)
+            # the same numbers on every run
+            for a, b in zip(first[i], (hist, mom, mm, fp)):
+                assert np.array_equal(a.view(np.uint32), b.view(np.uint32)), i
+    ctx.close()
