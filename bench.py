@@ -234,6 +234,31 @@ def extras(args, torch, chk, ctx, shard_bytes, peak):
             best = dt if best is None else min(best, dt)
         return best
 
+    # ---- container version 3 (opt-in experiment; before the analysis below groups tensors into clusters): every high byte plane coded with its own table, same coder
+    def one_format():
+        best_c = best_d = None
+        for _ in range(3):
+            ctx.compress(host_images=False)
+            cm, sm = ctx.timing("compress_device_ms"), ctx.timing("plane_split_ms")
+            s = ctx.summary()
+            t0 = time.perf_counter()
+            ctx.decompress_resident(None)       # restores in place: the registered tensors are their own targets
+            torch.cuda.synchronize()
+            dm = (time.perf_counter() - t0) * 1e3
+            best_c = cm if best_c is None else min(best_c, cm)
+            best_d = dm if best_d is None else min(best_d, dm)
+        total = s["states_bytes"] + s["mantissa_bytes"] + s["dict_bytes"]
+        return {"compress_device_ms": best_c, "restore_call_ms": best_d, "ratio_all_files": s["original_bytes"] / total,
+                "files_bytes": total, "plane_split_ms": sm, "plane_merge_ms": ctx.timing("plane_merge_ms")}
+
+    v2 = one_format()
+    ctx.set_option("format_version", 3)
+    v3 = one_format()
+    ctx.set_option("format_version", 2)
+    out["format_v3"] = {"what": "the benchmark shard through container version 2 (the reference's) and version 3 (byte planes "
+                                "with a table each); restore_call_ms is host wall time of the call, device-resident",
+                        "v2": v2, "v3": v3}
+
     # ---- statistics of the resident shard: two passes over every tensor (src/TensorAnalyzer.cpp:64-198)
     def analyze_ms():
         ctx.analyze()

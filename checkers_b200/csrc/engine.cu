@@ -93,6 +93,7 @@ struct Tensor {
     void* ptr;
     uint64_t n_elem;
     uint8_t dtype, category;
+    bool hot = false;  // an 8-bit plane whose bytes take few values (container version 3): counted in the spread bins
 };
 
 struct WorkItem {
@@ -118,6 +119,10 @@ struct Context {
 
     bool repair_tables = false, verify_zero_lanes = false, allow_undecodable = false;
     bool fast_stats = false;      // statistics with order-free sums over the whole device (see stats_kernels.cuh)
+    int format_version = 2;       // 2: the reference's container; 3: byte planes with a table each (format_v3.inc)
+    uint32_t file_version[3] = {kStatesVersion, kMantVersion, kDictVersion};  // written to and expected in the headers
+    struct V3State* v3 = nullptr;
+    uint64_t registry_epoch = 0;  // changes whenever the registered tensors change
     bool decode_two_level = false;
 
     // device buffers (grow-only, from the context's pool)
@@ -153,6 +158,15 @@ struct Context {
     std::map<std::string, double> timing;
     uint64_t launches = 0;
 };
+
+// container version 3 (format_v3.inc, at the end of this file)
+static void v3_compress(Context* c, bool host_images);
+static void v3_decompress_resident(Context* c, void* const* dst);
+static void v3_decompress_images(Context* c, const uint8_t* st, size_t st_n, const uint8_t* mt, size_t mt_n,
+                                 const uint8_t* dc, size_t dc_n);
+static const void* v3_image_ptr(const Context* c, int k);
+static size_t v3_image_size(const Context* c, int k);
+static void v3_destroy(Context* c);
 
 static void dev_ensure(Context* c, DevBuf& b, size_t bytes) {
     bytes = (bytes + 255) & ~(size_t)255;
@@ -247,7 +261,14 @@ static uint8_t* image_buffer(Context* c, int k, size_t bytes) {
     pin_ensure(c->img[k], bytes);
     return static_cast<uint8_t*>(c->img[k].p);
 }
-static const void* image_ptr(const Context* c, int k) { return c->img_ext[k] ? c->img_ext[k] : c->img[k].p; }
+static const void* image_ptr(const Context* c, int k) {
+    if (c->format_version == 3 && k != 1) return v3_image_ptr(c, k);
+    return c->img_ext[k] ? c->img_ext[k] : c->img[k].p;
+}
+static size_t image_size(const Context* c, int k) {
+    if (c->format_version == 3 && k != 1) return v3_image_size(c, k);
+    return c->img[k].size;
+}
 
 // ------------------------------------------------------------------ work list
 // Order, ownership and sharing rules of compress_and_save_all
@@ -373,6 +394,7 @@ static uint32_t persistent_grid(Context* c, const void* kernel, size_t smem, siz
 // lookups): run side by side they only take turns, so they run one after the other, while the
 // memory-bound gather of finished tensors hides under the issue-bound chains of the others.
 static void compress(Context* c, bool host_images) {
+    if (c->format_version == 3) return v3_compress(c, host_images);
     const auto t_total = std::chrono::steady_clock::now();
     CHK_CUDA(cudaSetDevice(c->device));
     c->have_resident = c->have_images = false;
@@ -405,6 +427,7 @@ static void compress(Context* c, bool host_images) {
         const unsigned long long c_max = (w.bytes + 255) / 256;
         d.chunk_stride = (uint32_t)((2 * c_max + 31) & ~31ull);
         d.flags = w.owns ? kFlagNeedHist : 0u;
+        if (c->tensors[w.idx].hot) d.flags |= kFlagHotBins;
         if ((reinterpret_cast<uintptr_t>(d.src) & 15) == 0 && (sidecar_total & 15) == 0) d.flags |= kFlagAligned;
         sidecar_total += (unsigned long long)c->tensors[w.idx].n_elem * w.spe;
         // value-lane regions, plus one shared region for the lanes that only see zeroed bytes
@@ -423,7 +446,7 @@ static void compress(Context* c, bool host_images) {
         c->table_sums.clear();
         if (host_images) {
             const uint32_t magic[3] = {kStatesMagic, kMantMagic, kDictMagic};
-            const uint32_t ver[3] = {kStatesVersion, kMantVersion, kDictVersion};
+            const uint32_t* ver = c->file_version;
             for (int k = 0; k < 3; ++k) {
                 uint8_t* p = image_buffer(c, k, kFileHeader);
                 put<uint32_t>(p, magic[k]);
@@ -657,15 +680,15 @@ static void compress(Context* c, bool host_images) {
         uint8_t* dc = image_buffer(c, 2, c->summary.dict_bytes);
 
         put<uint32_t>(st, kStatesMagic);
-        put<uint32_t>(st + 4, kStatesVersion);
+        put<uint32_t>(st + 4, c->file_version[0]);
         put<uint32_t>(st + 8, rank_u);
         put<uint32_t>(st + 12, (uint32_t)W);
         put<uint32_t>(mt, kMantMagic);
-        put<uint32_t>(mt + 4, kMantVersion);
+        put<uint32_t>(mt + 4, c->file_version[1]);
         put<uint32_t>(mt + 8, rank_u);
         put<uint32_t>(mt + 12, (uint32_t)n_sidecars);
         put<uint32_t>(dc, kDictMagic);
-        put<uint32_t>(dc + 4, kDictVersion);
+        put<uint32_t>(dc + 4, c->file_version[2]);
         put<uint32_t>(dc + 8, rank_u);
         put<uint32_t>(dc + 12, (uint32_t)T);
 
@@ -750,7 +773,7 @@ static void compress_and_save(Context* c, const std::string& dir) {
     const auto t0 = std::chrono::steady_clock::now();
     std::string paths[3];
     rank_paths(c, dir, paths);
-    for (int k = 0; k < 3; ++k) write_file(paths[k], image_ptr(c, k), c->img[k].size);
+    for (int k = 0; k < 3; ++k) write_file(paths[k], image_ptr(c, k), image_size(c, k));
     c->timing["io_ms"] = wall_ms(t0);
 }
 
@@ -795,6 +818,7 @@ static void run_decode(Context* c, size_t W, const uint8_t* d_payload, const uin
 }
 
 static void decompress_resident(Context* c, void* const* dst) {
+    if (c->format_version == 3) return v3_decompress_resident(c, dst);
     const auto t_total = std::chrono::steady_clock::now();
     CHK_CUDA(cudaSetDevice(c->device));
     if (!c->have_resident) throw Error{CHK_ERR_INVALID, "no device-resident compressed state: call chk_compress first"};
@@ -836,15 +860,16 @@ static void decompress_resident(Context* c, void* const* dst) {
 
 static void decompress_images(Context* c, const uint8_t* st, size_t st_n, const uint8_t* mt, size_t mt_n,
                               const uint8_t* dc, size_t dc_n) {
+    if (c->format_version == 3) return v3_decompress_images(c, st, st_n, mt, mt_n, dc, dc_n);
     const auto t_total = std::chrono::steady_clock::now();
     CHK_CUDA(cudaSetDevice(c->device));
     c->restored = 0;
     c->have_resident = false;  // device buffers are about to be reused
-    if (st_n < kFileHeader || get<uint32_t>(st) != kStatesMagic || get<uint32_t>(st + 4) != kStatesVersion)
+    if (st_n < kFileHeader || get<uint32_t>(st) != kStatesMagic || get<uint32_t>(st + 4) != c->file_version[0])
         throw Error{CHK_ERR_FORMAT, "states file: bad magic or version"};
-    if (mt_n < kFileHeader || get<uint32_t>(mt) != kMantMagic || get<uint32_t>(mt + 4) != kMantVersion)
+    if (mt_n < kFileHeader || get<uint32_t>(mt) != kMantMagic || get<uint32_t>(mt + 4) != c->file_version[1])
         throw Error{CHK_ERR_FORMAT, "mantissa file: bad magic or version"};
-    if (dc_n < kFileHeader || get<uint32_t>(dc) != kDictMagic || get<uint32_t>(dc + 4) != kDictVersion)
+    if (dc_n < kFileHeader || get<uint32_t>(dc) != kDictMagic || get<uint32_t>(dc + 4) != c->file_version[2])
         throw Error{CHK_ERR_FORMAT, "tables file: bad magic or version"};
     const size_t n_st = get<uint32_t>(st + 12), n_mt = get<uint32_t>(mt + 12), n_dc = get<uint32_t>(dc + 12);
     const size_t st_data = kFileHeader + n_st * kStatesEntry;
@@ -1138,6 +1163,7 @@ int chk_context_destroy(chk_context* c) {
     CHK_API_BEGIN
     if (!c) return CHK_OK;
     cudaSetDevice(c->device);
+    v3_destroy(c);
     if (c->stream) cudaStreamSynchronize(c->stream);
     DevBuf* bufs[] = {&c->d_descs, &c->d_tiles, &c->d_hist, &c->d_sidecar, &c->d_scratch, &c->d_hdrs,
                       &c->d_order, &c->d_ticket, &c->d_psize, &c->d_zslots, &c->d_zregions, &c->d_zslot_of, &c->d_jobs, &c->d_sums, &c->d_payload, &c->d_enc,
@@ -1166,6 +1192,7 @@ int chk_reset(chk_context* c) {
     CHK_API_BEGIN
     CHK_REQUIRE(c, "context is NULL");
     c->tensors.clear();
+    c->registry_epoch++;
     c->clusters = ClusterMap{};
     c->have_clusters = false;
     c->stats.clear();
@@ -1192,6 +1219,7 @@ int chk_register_tensor(chk_context* c, const char* name, const void* ptr, uint6
     CHK_REQUIRE(c && name, "context or name is NULL");
     c->tensors.push_back(Tensor{name, const_cast<void*>(ptr), n, dtype, cat});
     c->have_resident = false;
+    c->registry_epoch++;
     CHK_API_END
 }
 
@@ -1212,6 +1240,11 @@ int chk_set_option(chk_context* c, const char* key, int64_t value) {
         c->verify_zero_lanes = value != 0;
     else if (k == "fast_stats")
         c->fast_stats = value != 0;
+    else if (k == "format_version") {
+        if (value != 2 && value != 3) throw chk::Error{CHK_ERR_INVALID, "format_version must be 2 or 3"};
+        if (c->format_version != (int)value) c->have_resident = c->have_images = false;
+        c->format_version = (int)value;
+    }
     else if (k == "allow_undecodable")
         c->allow_undecodable = value != 0;
 
@@ -1313,7 +1346,7 @@ int chk_get_image(chk_context* c, int which, const void** data, uint64_t* size) 
     CHK_REQUIRE(which >= 0 && which < 3, "which must be 0, 1 or 2");
     CHK_REQUIRE(c->have_images, "no host images: call chk_compress(ctx, 1) first");
     *data = image_ptr(c, which);
-    *size = c->img[which].size;
+    *size = image_size(c, which);
     CHK_API_END
 }
 
@@ -1465,6 +1498,7 @@ int chk_kernel_launches(chk_context* c, uint64_t* count) {
 }  // extern "C"
 
 #include "host_stream.inc"
+#include "format_v3.inc"
 
 // ====================================================================== encode without allocating
 // chk_encode_tensor_static: the rANS encode of ONE tensor whose working memory

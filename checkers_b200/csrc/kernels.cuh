@@ -28,6 +28,7 @@ enum : uint32_t {
     kFlagNeedHist = 1u,   // this tensor owns a table: count its bytes
     kFlagAligned = 2u,    // tensor, sidecar slice and decode target allow 16-byte vectors
     kFlagRaw = 4u,        // payload is the masked tensor itself (passthrough rule)
+    kFlagHotBins = 8u,    // an 8-bit tensor whose bytes take few values (a sign/exponent plane): count in the spread bins
 };
 
 enum : uint32_t {
@@ -234,12 +235,22 @@ __global__ void __launch_bounds__(256) split_hist_kernel(const TensorDesc* __res
                 for (uint32_t v = tid; v < nvec; v += 256) {
                     const uint4 q = ld_global_v4(d.src + base + (size_t)v * 16);
                     const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+                    if (d.flags & kFlagHotBins) {
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        bin_add(mine, w[k] & 0xFF);
-                        bin_add(mine, (w[k] >> 8) & 0xFF);
-                        bin_add(mine, (w[k] >> 16) & 0xFF);
-                        bin_add(mine, w[k] >> 24);
+                        for (int k = 0; k < 4; ++k) {
+                            bin_add_hot(mine_hot, w[k] & 0xFF);
+                            bin_add_hot(mine_hot, (w[k] >> 8) & 0xFF);
+                            bin_add_hot(mine_hot, (w[k] >> 16) & 0xFF);
+                            bin_add_hot(mine_hot, w[k] >> 24);
+                        }
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            bin_add(mine, w[k] & 0xFF);
+                            bin_add(mine, (w[k] >> 8) & 0xFF);
+                            bin_add(mine, (w[k] >> 16) & 0xFF);
+                            bin_add(mine, w[k] >> 24);
+                        }
                     }
                 }
                 for (uint32_t i = (nvec << 4) + tid; i < nb; i += 256) bin_add(mine, d.src[base + i]);
@@ -606,3 +617,4 @@ __global__ void __launch_bounds__(256) tensor_stats_kernel(const StatsDesc* __re
 }  // namespace chk
 
 #include "stats_kernels.cuh"
+#include "plane_kernels.cuh"

@@ -92,7 +92,13 @@ int chk_tensor_count(chk_context* ctx, uint64_t* count);
  * whole device instead of in the reference's order of float additions: minimum,
  * maximum and value histogram are unchanged, mean / variance / skewness / kurtosis
  * differ by the rounding error of the reference's float sums (and cluster boundaries
- * that hang on that error can move). */
+ * that hang on that error can move).
+ * "format_version" (2 or 3, default 2).  2 is the reference's container.  3 is an
+ * experiment the reference has no counterpart for: every high byte of a
+ * floating-point element becomes a byte plane that is coded as an 8-bit tensor of its
+ * own ("<name>#b<byte>") with its own table, by the same coder; low bytes stay raw.
+ * The three files keep their layouts and carry version 3 in their headers; a context
+ * reads only the version it is set to.  Cluster-shared tables are not used. */
 int chk_set_option(chk_context* ctx, const char* key, int64_t value);
 
 /* ---- analysis: checkers::analyze_tensors, src/api.cpp:1033-1253 ----------

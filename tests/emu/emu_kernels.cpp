@@ -271,6 +271,36 @@ void emu_stats_fast(size_t n, const void* const* ptrs, const uint64_t* n_elem, c
     });
 }
 
+// byte planes: split n tensors into low bytes + planes, or merge them back (merge != 0: `tensors` are written)
+void emu_planes(size_t n, void* const* tensors, const uint64_t* n_elem, const uint32_t* es, const uint32_t* spe,
+                const uint64_t* low_off, const uint64_t* plane_off, const uint64_t* stride, uint8_t* low, uint8_t* planes,
+                uint32_t grid, uint32_t merge) {
+    std::vector<PlaneDesc> d(n);
+    std::vector<uint32_t> ts(n + 1);
+    uint32_t tiles = 0;
+    for (size_t i = 0; i < n; ++i) {
+        d[i] = PlaneDesc{};
+        d[i].tensor = (uint8_t*)tensors[i];
+        d[i].n_elem = n_elem[i];
+        d[i].low_off = low_off[i];
+        d[i].plane_off = plane_off[i];
+        d[i].plane_stride = stride[i];
+        d[i].es = es[i];
+        d[i].spe = spe[i];
+        d[i].vector_ok = ((uintptr_t)tensors[i] & 15) == 0 && (low_off[i] & 15) == 0 && ((uintptr_t)low & 15) == 0 &&
+                         ((uintptr_t)planes & 15) == 0;
+        ts[i] = tiles;
+        tiles += (uint32_t)((n_elem[i] * es[i] + kPlaneTileBytes - 1) / kPlaneTileBytes);
+    }
+    ts[n] = tiles;
+    if (!tiles) return;
+    if (grid > tiles) grid = tiles;
+    if (merge)
+        emu::launch(grid, 256, 0, [&] { plane_merge_kernel(d.data(), ts.data(), (uint32_t)n, tiles, low, planes); });
+    else
+        emu::launch(grid, 256, 0, [&] { plane_split_kernel(d.data(), ts.data(), (uint32_t)n, tiles, low, planes); });
+}
+
 // the host routine the device kernel must agree with
 void emu_host_enc_entries(const uint32_t* nf, const uint32_t* cf, uint32_t* enc_out) {
     FreqTable ft;

@@ -147,6 +147,14 @@ class Emu:
                             C.c_uint32(int(float_only)))
         return outs, status
 
+    def planes(self, tensors, n_elem, es, spe, low_off, plane_off, stride, low, planes, grid=3, merge=False):
+        n, ptrs = self._arrays(tensors)
+        a = lambda x, t: np.array(x, t)
+        ne, e, sp = a(n_elem, np.uint64), a(es, np.uint32), a(spe, np.uint32)
+        lo, po, st = a(low_off, np.uint64), a(plane_off, np.uint64), a(stride, np.uint64)
+        self.lib.emu_planes(C.c_size_t(n), ptrs, _p(ne, u64p), _p(e, u32p), _p(sp, u32p), _p(lo, u64p), _p(po, u64p),
+                            _p(st, u64p), _p(low), _p(planes), C.c_uint32(grid), C.c_uint32(int(merge)))
+
     def stats(self, tensors, n_elem, dtypes, bins=256, grid=2, fast=False):
         n, ptrs = self._arrays(tensors)
         ne = np.array(n_elem, np.uint64)

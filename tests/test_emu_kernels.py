@@ -179,3 +179,39 @@ def test_stats_kernel(emu, oracle):
             assert np.array_equal(res[i][1].view(np.uint32), mom.view(np.uint32)), i
             assert np.array_equal(res[i][2].view(np.uint32), mm.view(np.uint32)), i
             assert res[i][3][4] == np.float32(mm[1] - mm[0])
+
+
+@pytest.mark.parametrize("misalign", [None, [1, 0, 2]])
+def test_plane_split_and_merge(emu, misalign):
+    """Byte planes of container version 3: low bytes element-major, every high byte a plane of its own; the
+    merge restores the tensor.  16-byte path, ragged tails and unaligned tensors."""
+    cases = [("f32_master", 20000), ("bf16_weight", 70001), ("f16_weight", 4099), ("f32_exp_avg", 3), ("bf16_weight", 1),
+             ("f32_exp_avg_sq", 8192 + 16)]
+    tensors, es, spe, dts = make(cases, 9, misalign)
+    n_elem = [a.size // e for a, e in zip(tensors, es)]
+    low_off, plane_off, stride = [], [], []
+    lo = po = 0
+    for n, e, sp in zip(n_elem, es, spe):
+        low_off.append(lo); plane_off.append(po); stride.append((n + 31) & ~31)
+        lo += n * sp
+        po += stride[-1] * (e - sp)
+    low, planes = aligned(lo + 64), aligned(po + 64)
+    low[:] = 0xAA; planes[:] = 0xBB
+    emu.planes(tensors, n_elem, es, spe, low_off, plane_off, stride, low, planes)
+    for i, a in enumerate(tensors):
+        m = a.reshape(n_elem[i], es[i])
+        assert np.array_equal(low[low_off[i]:low_off[i] + n_elem[i] * spe[i]], m[:, :spe[i]].reshape(-1)), i
+        for k in range(es[i] - spe[i]):
+            p0 = plane_off[i] + k * stride[i]
+            assert np.array_equal(planes[p0:p0 + n_elem[i]], m[:, spe[i] + k]), (i, k)
+            assert np.all(planes[p0 + n_elem[i]:p0 + stride[i]] == 0xBB), (i, k)
+    assert np.all(low[lo:] == 0xAA)
+    outs = []
+    for a in tensors:
+        off = (a.ctypes.data & 15)
+        o = aligned(a.size + 64)[off:off + a.size]
+        o[:] = 0
+        outs.append(o)
+    emu.planes(outs, n_elem, es, spe, low_off, plane_off, stride, low, planes, grid=5, merge=True)
+    for a, o in zip(tensors, outs):
+        assert np.array_equal(a, o)

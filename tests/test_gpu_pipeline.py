@@ -274,3 +274,98 @@ def test_fast_statistics_against_oracle(chk, oracle):
             for a, b in zip(first[i], (hist, mom, mm, fp)):
                 assert np.array_equal(a.view(np.uint32), b.view(np.uint32)), i
     ctx.close()
+
+
+def _v3_expected(oracle, names, host, dtypes, tmp_path, rank):
+    """What container version 3 must write, from the version-2 oracle: states / tables = the oracle's files for the
+    byte planes as 8-bit tensors (integer tensors as they are); mantissa = its file for the original tensors."""
+    from oracle_lib import SIDECAR_PER_ELEM
+    p_names, p_host, p_dt = [], [], []
+    for name, raw, dt in zip(names, host, dtypes):
+        es, spe = ELEM_SIZE[dt], SIDECAR_PER_ELEM[dt]
+        if spe == 0:
+            p_names.append(name); p_host.append(raw); p_dt.append(dt)
+            continue
+        m = raw.reshape(-1, es)
+        for k in range(spe, es):
+            p_names.append(f"{name}#b{k}"); p_host.append(np.ascontiguousarray(m[:, k])); p_dt.append(I8)
+    d_planes, d_orig = str(tmp_path / "o_planes"), str(tmp_path / "o_orig")
+    oracle.compress_and_save(p_names, p_host, p_dt, d_planes, rank=rank)
+    oracle.compress_and_save(names, host, dtypes, d_orig, rank=rank)
+    st, _, dc = read_files(d_planes, rank)
+    _, mt, _ = read_files(d_orig, rank)
+
+    def v3(b):
+        b = bytearray(b)
+        b[4:8] = (3).to_bytes(4, "little")
+        return bytes(b)
+    return v3(st), v3(mt), v3(dc)
+
+
+def test_container_version3_byte_planes(chk, oracle, tmp_path):
+    """Opt-in container version 3: every high byte plane of a float tensor coded as an 8-bit tensor of its own.
+    Files equal what the version-2 oracle writes for those planes; restore from the device-resident result and
+    from files is lossless; the result is smaller than version 2's; version 2 is unaffected by the switch."""
+    names, host, dtypes = make_state_v3()
+    dev = [dev_bytes(h) for h in host]
+    ctx = chk.Context(device=0, rank=2)
+    register_all(ctx, names, dev, dtypes)
+    out2 = str(tmp_path / "v2")
+    ctx.compress_and_save(out2)
+    v2_files = read_files(out2, 2)
+    v2_total = sum(len(f) for f in v2_files)
+
+    ctx.set_option("format_version", 3)
+    out3 = str(tmp_path / "v3")
+    ctx.compress_and_save(out3)
+    got = read_files(out3, 2)
+    want = _v3_expected(oracle, names, host, dtypes, tmp_path, 2)
+    for g, w, what in zip(got, want, ("states", "mantissa", "tables")):
+        assert g == w, f"{what} file differs from the oracle's files of the planes"
+    s = ctx.summary()
+    assert s["states_bytes"] + s["mantissa_bytes"] + s["dict_bytes"] == sum(len(f) for f in got)
+    assert s["original_bytes"] == sum(h.size for h in host)
+    v3_payload = s["states_bytes"] + s["mantissa_bytes"]
+    assert v3_payload < 0.93 * (len(v2_files[0]) + len(v2_files[1])), (v3_payload, v2_total)
+
+    # device-resident round trip into separate buffers
+    ctx.compress(host_images=False)
+    outs = [torch.zeros(h.size, dtype=torch.uint8, device="cuda") for h in host]
+    assert ctx.decompress_resident([o.data_ptr() for o in outs]) == len(names)
+    for o, d in zip(outs, dev):
+        assert torch.equal(o, d)
+    # from the files, into a fresh context with fresh tensors
+    fresh = [torch.zeros_like(d) for d in dev]
+    ctx2 = chk.Context(device=0, rank=2)
+    register_all(ctx2, names, fresh, dtypes)
+    ctx2.set_option("format_version", 3)
+    assert ctx2.load_and_decompress(out3) == len(names)
+    for f, d in zip(fresh, dev):
+        assert torch.equal(f, d)
+    # a version-2 reader refuses the files, and the other way round
+    ctx2.set_option("format_version", 2)
+    with pytest.raises(chk.CheckersError):
+        ctx2.load_and_decompress(out3)
+    ctx2.set_option("format_version", 3)
+    with pytest.raises(chk.CheckersError):
+        ctx2.load_and_decompress(out2)
+    # back to version 2: the same bytes as before
+    ctx.set_option("format_version", 2)
+    out2b = str(tmp_path / "v2b")
+    ctx.compress_and_save(out2b)
+    assert read_files(out2b, 2) == v2_files
+    ctx.close(); ctx2.close()
+
+
+def make_state_v3():
+    kinds = [("model.embed.weight", "bf16_weight", 300001), ("master_weights::model.embed.weight", "f32_master", 300001),
+             ("optimizer.exp_avg::model.embed.weight", "f32_exp_avg", 300001),
+             ("optimizer.exp_avg_sq::model.embed.weight", "f32_exp_avg_sq_lognormal", 300001),
+             ("model.norm.weight", "bf16_norm_gain", 4096), ("half.w", "f16_weight", 70000), ("tiny", "f32_master", 1),
+             ("ints.i8", "i8", 50000), ("ints.i32", "i32", 12345), ("model.q.weight", "bf16_weight", 1 << 20),
+             ("master_weights::model.q.weight", "f32_master", 1 << 20)]
+    names, host, dtypes = [], [], []
+    for i, (name, kind, n) in enumerate(kinds):
+        raw, dt = synth(kind, n, 900 + i)
+        names.append(name); host.append(raw.copy()); dtypes.append(dt)
+    return names, host, dtypes
