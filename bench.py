@@ -44,6 +44,7 @@ sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.join(ROOT, "tests"))
 
 LLAMA3_8B = dict(hidden=4096, layers=32, inter=14336, q_heads=32, kv_heads=8, head_dim=128, vocab=128256)
+LLAMA3_70B = dict(hidden=8192, layers=80, inter=28672, q_heads=64, kv_heads=8, head_dim=128, vocab=128256)
 PARAMS_8B = 8030261248
 # DRAM read + write bytes per byte of tensor, from one ncu capture of each kernel on a 939.5 MB slice of this
 # workload (1024 tensors of 256 Ki elements); the traffic of a launch grows in proportion to the tensor bytes
@@ -118,6 +119,34 @@ def make_shard_on_host(pieces, n_elems, seed):
     exp_avg = rng.normal(0.0, 1e-4, n_elems).astype(np.float32)
     exp_avg_sq = np.exp(rng.normal(-18.0, 2.0, n_elems)).astype(np.float32)
     return [weight, master, exp_avg, exp_avg_sq]
+
+
+def pcie_rates(torch, pinned, device):
+    """Plain copies of one pinned host buffer: host->device, device->host, and both at once (GB/s each way)."""
+    nbytes = pinned.numel() * pinned.element_size()
+    up = torch.empty_like(pinned, device=device)
+    down_src = torch.empty_like(pinned, device=device)
+    down = torch.empty_like(pinned).pin_memory()
+    s1, s2 = torch.cuda.Stream(device=device), torch.cuda.Stream(device=device)
+
+    def run(do_up, do_down):
+        best = None
+        for _ in range(3):
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            if do_up:
+                with torch.cuda.stream(s1):
+                    up.copy_(pinned, non_blocking=True)
+            if do_down:
+                with torch.cuda.stream(s2):
+                    down.copy_(down_src, non_blocking=True)
+            torch.cuda.synchronize()
+            dt = time.perf_counter() - t0
+            best = dt if best is None else min(best, dt)
+        return nbytes / best / 1e9
+
+    return {"h2d_gbs": round(run(True, False), 1), "d2h_gbs": round(run(False, True), 1),
+            "both_directions_gbs_each": round(run(True, True), 1), "copy_bytes": nbytes}
 
 
 class ClockSampler:
@@ -216,6 +245,54 @@ def cpu_arm(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def host_stream_70b(args, torch):
+    """Llama-3-70B ZeRO-3 state, shard 0 of 8 (123 GB per rank at 14 B per parameter): the first --c4-elems
+    parameters of it, resident in pinned host memory, through the chunked host pipeline in 1 GiB parts."""
+    from checkers_b200.streaming import ChunkedHostPipeline, HostTensor
+    dev = torch.device("cuda", torch.cuda.current_device())
+    import checkers_b200 as chk
+    pieces, n_elems, total = shard_pieces(LLAMA3_70B, 0, 8, args.chunk_elems, limit_elems=args.c4_elems)
+    bufs = make_shard_on_device(torch, pieces, n_elems, 70, dev)
+    h_in = [torch.empty(n_elems, dtype=b.dtype).pin_memory() for b in bufs]
+    h_out = [torch.empty(n_elems, dtype=b.dtype).pin_memory() for b in bufs]
+    for h, b in zip(h_in, bufs):
+        h.copy_(b)
+    del bufs
+    torch.cuda.empty_cache()
+    tags = (chk.BF16, chk.F32, chk.F32, chk.F32)
+    tensors, targets = [], []
+    for name, off, n, _ in pieces:
+        for (prefix, _), hi, ho, tag in zip(STATE_KINDS, h_in, h_out, tags):
+            tensors.append(HostTensor(prefix + name, hi[off:off + n], tag))
+            targets.append(ho[off:off + n])
+    nbytes = sum(h.numel() * h.element_size() for h in h_in)
+    pipe = ChunkedHostPipeline(tensors, device=dev.index, rank=0, chunk_bytes=1 << 30, workers=3)
+    best_c = best_r = None
+    for it in range(3):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        pipe.compress()
+        t1 = time.perf_counter()
+        pipe.restore(targets)
+        torch.cuda.synchronize()
+        t2 = time.perf_counter()
+        if it:
+            best_c = t1 - t0 if best_c is None else min(best_c, t1 - t0)
+            best_r = t2 - t1 if best_r is None else min(best_r, t2 - t1)
+    for h, g in zip(h_in, h_out):
+        assert torch.equal(h.view(torch.uint8), g.view(torch.uint8)), "70B-shaped host round trip is not lossless"
+    s = pipe.summary()
+    res = {"what": "Llama-3-70B shapes, shard 0 of 8 (123 GB per rank), first %d Mi parameters = %.2f GiB from pinned host "
+                   "memory in 1 GiB parts over 3 staging slots, tensors of <= %d elements" % (n_elems >> 20, nbytes / 2**30, args.chunk_elems),
+           "shard_bytes_full": total // 8 * 14, "sample_bytes": nbytes, "parts": len(pipe.chunks),
+           "compress_s": best_c, "restore_s": best_r, "compress_gbs": nbytes / best_c / 1e9,
+           "restore_gbs": nbytes / best_r / 1e9, "compress_plus_restore_gbs": nbytes / (best_c + best_r) / 1e9,
+           "ratio": s["original_bytes"] / (s["states_bytes"] + s["mantissa_bytes"] + s["dict_bytes"]),
+           "full_shard_estimate_s": (best_c + best_r) * (total // 8 * 14) / nbytes}
+    pipe.close()
+    return res
+
+
 def extras(args, torch, chk, ctx, shard_bytes, peak):
     """Numbers outside the headline step (flag --extras, second JSON line): the per-stage codec sweep of the
     microbenchmark configuration, the per-shard statistics pass, the Re-Pair tool against the reference's CLI."""
@@ -258,6 +335,9 @@ def extras(args, torch, chk, ctx, shard_bytes, peak):
     out["format_v3"] = {"what": "the benchmark shard through container version 2 (the reference's) and version 3 (byte planes "
                                 "with a table each); restore_call_ms is host wall time of the call, device-resident",
                         "v2": v2, "v3": v3}
+
+    # ---- host-resident state in 1 GiB pieces (70B shapes): a bounded sample of shard 0 of 8 from pinned host memory
+    out["host_stream_70b"] = host_stream_70b(args, torch)
 
     # ---- statistics of the resident shard: two passes over every tensor (src/TensorAnalyzer.cpp:64-198)
     def analyze_ms():
@@ -405,6 +485,8 @@ def main():
     ap.add_argument("--e2e-elems", type=int, default=128 << 20,
                     help="parameters per GPU in the host-buffer end-to-end leg (14 bytes each; the same at every N)")
     ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--c4-elems", type=int, default=512 << 20,
+                    help="--extras: parameters of the 70B-shaped shard streamed from host memory (14 bytes each)")
     ap.add_argument("--e2e-workers", type=int, default=4, help="staging slots (and host threads) of the chunk pipeline")
     ap.add_argument("--e2e-chunk-bytes", type=int, default=256 << 20,
                     help="tensor bytes per chunk of the host-buffer pipeline")
@@ -559,6 +641,13 @@ def main():
     e2e_value = e_bytes * world / e2e_s / 1e9
     e2e_engines = {k: round(pipe.timing(k), 2) for k in e2e_keys}   # last step, this rank: busy time per engine
     pipe.close()
+    pcie = pcie_rates(torch, h_in[1], device) if rank == 0 else None
+    if pcie:
+        # every step moves h2d_bytes up and d2h_bytes down; with both directions busy the link cannot do better than
+        floor_s = max(e_bytes + img_bytes, img_bytes + e_bytes) / (pcie["both_directions_gbs_each"] * 1e9)
+        pcie["link_floor_ms_per_step"] = round(floor_s * 1e3, 2)
+        pcie["measured_ms_per_step"] = round(e2e_s * 1e3, 2)
+        pcie["link_fraction"] = round(floor_s / e2e_s, 3)
 
     # ---- parity of the benchmark's own tensors with the CPU oracle (outside every timed region)
     parity = None
@@ -664,7 +753,7 @@ def main():
                                   f"in {len(pipe.chunks)} parts over {args.e2e_workers} staging slots with copies and "
                                   "kernels overlapped: H2D, compress, D2H of the file images; then H2D of the images, "
                                   "restore, D2H",
-                        "engine_busy_ms_rank0_last_step": e2e_engines},
+                        "engine_busy_ms_rank0_last_step": e2e_engines, "pcie_rank0": pcie},
                 "gpu_launches": int(launches), "clocks": clocks}
         print(json.dumps(line), flush=True)
     if args.extras and rank == 0 and world == 1:

@@ -126,7 +126,7 @@ struct Context {
     bool decode_two_level = false;
 
     // device buffers (grow-only, from the context's pool)
-    DevBuf d_descs, d_tiles, d_hist, d_sidecar, d_scratch, d_hdrs, d_order, d_ticket, d_psize, d_zslots, d_zregions, d_zslot_of, d_jobs, d_sums, d_stats_part, d_stats_mid,
+    DevBuf d_descs, d_tiles, d_hist, d_sidecar, d_scratch, d_hdrs, d_order, d_ticket, d_psize, d_zslots, d_zregions, d_zslot_of, d_jobs, d_sums, d_stats_part, d_stats_mid, d_poff, d_fileorder,
         d_payload, d_enc, d_freq, d_cum, d_status, d_stats_desc, d_stats_out;
     cudaStream_t side_stream = nullptr;
     std::vector<cudaEvent_t> ev_count, ev_tab;
@@ -666,11 +666,20 @@ static void compress(Context* c, bool host_images) {
         // states image (write_rank_states_file, src/ANSCompressor.cpp:751-816)
         uint8_t* st = image_buffer(c, 0, c->summary.states_bytes);
         const size_t st_data = kFileHeader + W * kStatesEntry;
-        // heap order -> file order: each tensor's payload goes to its place in the data section
-        for (size_t i = 0; i < W; ++i)
-            if (psize[i])
-                CHK_CUDA(cudaMemcpyAsync(st + st_data + poff[i], static_cast<const uint8_t*>(c->d_payload.p) + c->descs[i].payload_off,
-                                         psize[i], cudaMemcpyDeviceToHost, s));
+        // heap order -> file order on the device, then the data section in one copy
+        if (payload_total) {
+            dev_ensure(c, c->d_poff, (W + 1) * 8);
+            dev_ensure(c, c->d_fileorder, payload_total + 64);
+            control_copy(c, c->d_poff.p, c->h_poff.p, (W + 1) * 8, s);
+            const size_t cap = (size_t)(c->sm_count > 0 ? c->sm_count : 1) * 8;
+            order_payload_kernel<<<(uint32_t)(W < cap ? W : cap), 256, 0, s>>>(
+                static_cast<const TensorDesc*>(c->d_descs.p), static_cast<const unsigned long long*>(c->d_psize.p),
+                static_cast<const unsigned long long*>(c->d_poff.p), static_cast<const uint8_t*>(c->d_payload.p),
+                static_cast<uint8_t*>(c->d_fileorder.p), (uint32_t)W);
+            CHK_CUDA(cudaGetLastError());
+            c->launches++;
+            CHK_CUDA(cudaMemcpyAsync(st + st_data, c->d_fileorder.p, payload_total, cudaMemcpyDeviceToHost, s));
+        }
         // mantissa image (write_rank_mantissa_file, :839-887)
         uint8_t* mt = image_buffer(c, 1, c->summary.mantissa_bytes);
         const size_t mt_data = kFileHeader + n_sidecars * kMantEntry;
@@ -1167,7 +1176,7 @@ int chk_context_destroy(chk_context* c) {
     if (c->stream) cudaStreamSynchronize(c->stream);
     DevBuf* bufs[] = {&c->d_descs, &c->d_tiles, &c->d_hist, &c->d_sidecar, &c->d_scratch, &c->d_hdrs,
                       &c->d_order, &c->d_ticket, &c->d_psize, &c->d_zslots, &c->d_zregions, &c->d_zslot_of, &c->d_jobs, &c->d_sums, &c->d_payload, &c->d_enc,
-                      &c->d_freq, &c->d_cum, &c->d_status, &c->d_stats_desc, &c->d_stats_out, &c->d_stats_part, &c->d_stats_mid};
+                      &c->d_freq, &c->d_cum, &c->d_status, &c->d_stats_desc, &c->d_stats_out, &c->d_stats_part, &c->d_stats_mid, &c->d_poff, &c->d_fileorder};
     for (DevBuf* b : bufs)
         if (b->p) cudaFreeAsync(b->p, c->stream);
     if (c->stream) cudaStreamSynchronize(c->stream);

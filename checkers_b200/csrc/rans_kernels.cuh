@@ -590,6 +590,26 @@ __global__ void __launch_bounds__(256) compact_kernel(const TensorDesc* __restri
     }
 }
 
+// Heap order -> file order.  The fused encode kernel hands out payload space in the order tensors finish;
+// the data section of the states file wants them in index order (src/ANSCompressor.cpp:751-816).  One block
+// per tensor at a time, its warps taking 8 KiB pieces in turn, so the host receives the whole data section
+// in one device-to-host copy instead of one per tensor.
+__global__ void __launch_bounds__(256) order_payload_kernel(const TensorDesc* __restrict__ descs,
+                                                            const unsigned long long* __restrict__ size,
+                                                            const unsigned long long* __restrict__ file_off,
+                                                            const uint8_t* __restrict__ heap, uint8_t* __restrict__ out,
+                                                            uint32_t n_tensors) {
+    constexpr unsigned long long kPiece = 8192;
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (uint32_t ti = blockIdx.x; ti < n_tensors; ti += gridDim.x) {
+        const unsigned long long n = size[ti];
+        const uint8_t* src = heap + descs[ti].payload_off;
+        uint8_t* dst = out + file_off[ti];
+        for (unsigned long long at = warp * kPiece; at < n; at += 8 * kPiece)
+            warp_copy<4>(dst + at, src + at, (uint32_t)(n - at < kPiece ? n - at : kPiece), lane);
+    }
+}
+
 // ------------------------------------------------------------------ shared symbol-0 chains of a batch
 // The symbol-0 chain of a tensor depends on nothing but the table entry of symbol 0 and the
 // number of symbols per lane.  Half of a float tensor's codec input is zeroed bytes, so that
