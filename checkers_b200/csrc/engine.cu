@@ -123,7 +123,7 @@ struct Context {
     uint32_t file_version[3] = {kStatesVersion, kMantVersion, kDictVersion};  // written to and expected in the headers
     struct V3State* v3 = nullptr;
     uint64_t registry_epoch = 0;  // changes whenever the registered tensors change
-    bool decode_two_level = false;
+    bool decode_zero_skip = false; // float tensors whose table allows it are decoded with the short slot table (measured slower)
 
     // device buffers (grow-only, from the context's pool)
     DevBuf d_descs, d_tiles, d_hist, d_sidecar, d_scratch, d_hdrs, d_order, d_ticket, d_psize, d_zslots, d_zregions, d_zslot_of, d_jobs, d_sums, d_stats_part, d_stats_mid, d_poff, d_fileorder,
@@ -794,23 +794,43 @@ static void run_decode(Context* c, size_t W, const uint8_t* d_payload, const uin
     dev_ensure(c, c->d_status, W * 4 + 256);
     pin_ensure(c->h_status, W * 4 + 256);
     control_zero(c, c->d_status.p, W * 4, s);
-    // integer tensors run four chains per thread and need the larger ring area
-    bool any_int = false;
+    // Two launches at most.  With option "decode_zero_skip", floating-point tensors whose table gives symbol 0
+    // half of the slots (all of them, as a rule) go to the kernel with the short table, of which more teams fit an
+    // SM; integer tensors -- four chains per thread, larger rings -- and whatever does not qualify go to the
+    // full-table kernel.  Off by default: on a B200 the two extra instructions per symbol cost more than the
+    // added teams bring (9.8 ms against 9.6 ms for the 14 GB benchmark shard).
     const TensorDesc* hd = static_cast<const TensorDesc*>(c->h_descs.p);
-    for (size_t i = 0; i < W && !any_int; ++i) any_int = hd[i].spe * 2 != hd[i].es;
-    const bool tl = c->decode_two_level;
-    const uint32_t smem = kDecSmemBytes[any_int ? 1 : 0][tl ? 1 : 0];
-    upload_order(c, W, [&](size_t i) { return hd[i].n_bytes; });
-    auto kernel = any_int ? (tl ? rans_decode_kernel<true, true> : rans_decode_kernel<true, false>)
-                          : (tl ? rans_decode_kernel<false, true> : rans_decode_kernel<false, false>);
-    const uint32_t grid = persistent_grid(c, reinterpret_cast<const void*>(kernel), smem, W, c->decode_teams_per_sm);
+    std::vector<uint32_t> order(W);
+    for (size_t i = 0; i < W; ++i) order[i] = (uint32_t)i;
+    std::stable_sort(order.begin(), order.end(), [&](uint32_t a, uint32_t b) { return hd[a].n_bytes > hd[b].n_bytes; });
+    auto short_table = [&](uint32_t i) {
+        return c->decode_zero_skip && hd[i].spe * 2 == hd[i].es && (hd[i].flags & kFlagZeroSkip) && !(hd[i].flags & kFlagRaw);
+    };
+    const size_t n_short = (size_t)(std::stable_partition(order.begin(), order.end(), short_table) - order.begin());
+    bool any_int = false;
+    for (size_t k = n_short; k < W && !any_int; ++k) any_int = hd[order[k]].spe * 2 != hd[order[k]].es;
+    pin_ensure(c->h_order, W * 4);
+    std::memcpy(c->h_order.p, order.data(), W * 4);
+    dev_ensure(c, c->d_order, W * 4);
+    dev_ensure(c, c->d_ticket, 256);
+    control_copy(c, c->d_order.p, c->h_order.p, W * 4, s);
+    control_zero(c, c->d_ticket.p, 256, s);
     CHK_CUDA(cudaEventRecord(c->ev[1], s));
-    kernel<<<grid, kTeam, smem, s>>>(static_cast<const TensorDesc*>(c->d_descs.p), d_freq, d_cum, d_hdrs, d_payload,
-                                     d_sidecar, static_cast<const uint32_t*>(c->d_order.p),
-                                     static_cast<uint32_t*>(c->d_ticket.p), (uint32_t)W,
-                                     c->verify_zero_lanes ? 1u : 0u, static_cast<uint32_t*>(c->d_status.p));
-    CHK_CUDA(cudaGetLastError());
-    c->launches++;
+    auto launch = [&](auto kernel, uint32_t smem, size_t first, size_t n, uint32_t ticket_word) {
+        if (!n) return;
+        const uint32_t grid = persistent_grid(c, reinterpret_cast<const void*>(kernel), smem, n, c->decode_teams_per_sm);
+        kernel<<<grid, kTeam, smem, s>>>(static_cast<const TensorDesc*>(c->d_descs.p), d_freq, d_cum, d_hdrs, d_payload,
+                                         d_sidecar, static_cast<const uint32_t*>(c->d_order.p) + first,
+                                         static_cast<uint32_t*>(c->d_ticket.p) + ticket_word, (uint32_t)n,
+                                         c->verify_zero_lanes ? 1u : 0u, static_cast<uint32_t*>(c->d_status.p));
+        CHK_CUDA(cudaGetLastError());
+        c->launches++;
+    };
+    launch(rans_decode_kernel<false, true>, kDecSmemBytes[0][1], 0, n_short, 0);
+    if (any_int)
+        launch(rans_decode_kernel<true, false>, kDecSmemBytes[1][0], n_short, W - n_short, 8);
+    else
+        launch(rans_decode_kernel<false, false>, kDecSmemBytes[0][0], n_short, W - n_short, 8);
     CHK_CUDA(cudaEventRecord(c->ev[2], s));
     control_copy(c, c->h_status.p, c->d_status.p, W * 4, s);
     CHK_CUDA(cudaEventRecord(c->ev[4], s));
@@ -835,6 +855,13 @@ static void decompress_resident(Context* c, void* const* dst) {
     std::vector<TensorDesc> run;
     std::vector<size_t> src_index;
     std::vector<size_t> tensor_of;
+    // which tables leave room for the short decode table: the frequency of symbol 0 of each (4 bytes per table)
+    std::vector<uint32_t> f0;
+    if (c->decode_zero_skip && c->n_tables) {
+        f0.resize(c->n_tables);
+        CHK_CUDA(cudaMemcpy2DAsync(f0.data(), 4, c->d_freq.p, 1024, 4, c->n_tables, cudaMemcpyDeviceToHost, c->stream));
+        sync_stream(c, c->stream);
+    }
     for (size_t i = 0; i < c->work.size(); ++i) {
         const WorkItem& w = c->work[i];
         void* target = dst ? dst[w.idx] : c->tensors[w.idx].ptr;
@@ -846,7 +873,8 @@ static void decompress_resident(Context* c, void* const* dst) {
                                             ", not 4096: the stream cannot be decoded"};
         d.dst = static_cast<uint8_t*>(target);
         d.src = nullptr;
-        d.flags &= ~kFlagAligned;
+        d.flags &= ~(kFlagAligned | kFlagZeroSkip);
+        if (!f0.empty() && zero_skip_fits(f0[w.table])) d.flags |= kFlagZeroSkip;
         if ((reinterpret_cast<uintptr_t>(target) & 15) == 0 && (d.sidecar_off & 15) == 0) d.flags |= kFlagAligned;
         run.push_back(d);
         src_index.push_back(i);
@@ -928,6 +956,7 @@ static void decompress_images(Context* c, const uint8_t* st, size_t st_n, const 
             if (tb == tab.end()) throw Error{CHK_ERR_FORMAT, "entry '" + name + "': table '" + key + "' not in tables file"};
             d.table_idx = (uint32_t)tb->second;
             const uint8_t* te = dc + kFileHeader + tb->second * kDictEntry;
+            if (zero_skip_fits(get<uint32_t>(te + 256))) d.flags |= kFlagZeroSkip;  // frequency of symbol 0
             const uint32_t sum = get<uint32_t>(te + 1280 + 256 * 4);
             if (sum != kM)
                 throw Error{CHK_ERR_FORMAT, "table '" + key + "' sums to " + std::to_string(sum) +
@@ -1261,8 +1290,8 @@ int chk_set_option(chk_context* c, const char* key, int64_t value) {
         if (value < 0) throw chk::Error{CHK_ERR_INVALID, "workspace_bytes must not be negative (0 = no bound)"};
         c->workspace_bytes = (uint64_t)value;
     }
-    else if (k == "decode_two_level")
-        c->decode_two_level = value != 0;
+    else if (k == "decode_zero_skip")
+        c->decode_zero_skip = value != 0;
     else if (k == "segments") {
         if (value < 1 || value > 8) throw chk::Error{CHK_ERR_INVALID, "segments must be 1..8"};
         c->segments = (int)value;

@@ -24,10 +24,16 @@ constexpr uint32_t kScaleBits = 12;
 constexpr uint32_t kM = 1u << kScaleBits;
 constexpr uint32_t kL = 1u << 23;
 
+// Entries of the decoder's short slot table, and whether a table (by its frequency of symbol 0) can use it:
+// see the decode section of rans_kernels.cuh.
+constexpr uint32_t kZsEntries = 2176;
+__host__ __device__ inline bool zero_skip_fits(uint32_t f0) { return (f0 < 2048u ? f0 : 2048u) + kZsEntries >= kM + 1u; }
+
 enum : uint32_t {
     kFlagNeedHist = 1u,   // this tensor owns a table: count its bytes
     kFlagAligned = 2u,    // tensor, sidecar slice and decode target allow 16-byte vectors
     kFlagRaw = 4u,        // payload is the masked tensor itself (passthrough rule)
+    kFlagZeroSkip = 16u,  // symbol 0 owns so many slots of the tensor's table that the short decode table fits
     kFlagHotBins = 8u,    // an 8-bit tensor whose bytes take few values (a sign/exponent plane): count in the spread bins
 };
 

@@ -869,16 +869,20 @@ __global__ void __launch_bounds__(kTeam, kInts ? 1 : CHK_ENC_MINBLOCKS) rans_enc
 }
 
 // ------------------------------------------------------------------ rANS decode
-// Two table shapes, chosen per launch by the TL template flag:
-//   one level : slot -> symbol[0:8) | (freq-1)[8:20) | (slot - cum[symbol])[20:32)     16 KiB per tensor
-//   two levels: slot -> symbol (1 byte), symbol -> freq[0:16) | cum[16:32)              5 KiB per tensor
-// The second costs one more dependent shared-memory load per symbol but lets about
-// twice as many teams be resident on an SM.
+// The slot table: slot -> symbol[0:8) | (freq-1)[8:20) | (slot - cum[symbol])[20:32), 16 KiB per tensor.
+// Two shapes, chosen per launch by the ZS template flag:
+//   full      : one entry per slot.
+//   zero-skip : for tensors whose symbol 0 owns the first `skip` >= kM - kZsEntries + 1 slots -- every
+//               floating-point tensor: its zeroed low bytes are half of what the table was counted over, while
+//               the lanes that are decoded here hardly ever see a zero -- all of those slots share entry 0 and
+//               the table is about half as long, so more teams fit an SM.  With s1 = skip - 1 and
+//               m = max(slot, s1) the entry is dtab[m - s1], and the state needs slot - m added (entry 0 holds
+//               offset s1, so a slot below skip gets f0 * (x >> 12) + slot as it must).  Two more integer
+//               instructions per symbol, no extra load.
 constexpr uint32_t kRingWords = 17;
-template <int NV, bool TL>
+template <int NV, bool ZS>
 struct DecSmem {
-    uint32_t dtab[TL ? 256 : kM];  // two levels: freq | cum<<16 per symbol
-    uint8_t slot_sym[TL ? kM : 4];
+    uint32_t dtab[ZS ? kZsEntries : kM];
     // 64-byte input ring per chain (two 32-byte blocks) plus a 17th word that repeats word 0,
     // so the word after any ring word is the next one without a wrap.  The rings of a warp are
     // interleaved word by word (word w of lane l at [w * 32 + l]): every lane stays in its own
@@ -890,6 +894,7 @@ struct DecSmem {
 // shared memory per team: [chains per thread: 2 = float tensors only, 4 = integers present][table shape]
 constexpr uint32_t kDecSmemBytes[2][2] = {{(uint32_t)sizeof(DecSmem<2, false>), (uint32_t)sizeof(DecSmem<2, true>)},
                                           {(uint32_t)sizeof(DecSmem<4, false>), (uint32_t)sizeof(DecSmem<4, true>)}};
+
 
 __device__ __forceinline__ void prefetch_l2(const void* p) {
 #ifndef CHK_CPU_EMULATION
@@ -959,16 +964,16 @@ __device__ __forceinline__ uint32_t put_byte(uint32_t acc, uint32_t v, uint32_t 
 // stream bytes without branching: the two candidate bytes are placed at the top
 // of a word and funnel-shifted into the state by 0, 8 or 16 bits.  Returns the
 // table entry (symbol in its low byte).
-template <bool TL>
-__device__ __forceinline__ uint32_t dec_step(DecChain& c, const uint32_t* dtab, const uint8_t* slot_sym,
-                                             const uint8_t* ring_bytes) {
+template <bool ZS>
+__device__ __forceinline__ uint32_t dec_step(DecChain& c, const uint32_t* dtab, int s1, const uint8_t* ring_bytes) {
     const uint32_t slot = c.x & (kM - 1);
     const uint32_t xs = c.x >> kScaleBits;
     uint32_t x, sym;
-    if (TL) {
-        sym = slot_sym[slot];
-        const uint32_t t = dtab[sym];
-        x = (t & 0xFFFFu) * xs + slot - (t >> 16);
+    if (ZS) {
+        const int m = max((int)slot, s1);
+        const uint32_t e = dtab[m - s1];
+        sym = e;
+        x = ((e >> 8) & 0xFFFu) * xs + xs + ((e >> 20) + (slot - (uint32_t)m));
     } else {
         const uint32_t e = dtab[slot];
         sym = e;
@@ -986,7 +991,7 @@ __device__ __forceinline__ uint32_t dec_step(DecChain& c, const uint32_t* dtab, 
     return sym;
 }
 
-template <int NV, int B0, bool TL>
+template <int NV, int B0, bool ZS>
 __device__ __forceinline__ void decode_tensor(const TensorDesc& d, uint32_t ti,
                                               const uint32_t* __restrict__ freq_tables,
                                               const uint32_t* __restrict__ cum_tables,
@@ -994,7 +999,7 @@ __device__ __forceinline__ void decode_tensor(const TensorDesc& d, uint32_t ti,
                                               const uint8_t* __restrict__ payload,
                                               const uint8_t* __restrict__ sidecar, uint32_t check_zero_lanes,
                                               uint32_t* __restrict__ status, unsigned char* smem_raw) {
-    DecSmem<NV, TL>* sm = reinterpret_cast<DecSmem<NV, TL>*>(smem_raw);
+    DecSmem<NV, ZS>* sm = reinterpret_cast<DecSmem<NV, ZS>*>(smem_raw);
     const uint32_t j = threadIdx.x;
     const unsigned long long B = d.n_bytes;
 
@@ -1003,19 +1008,24 @@ __device__ __forceinline__ void decode_tensor(const TensorDesc& d, uint32_t ti,
     const uint32_t* cq = cum_tables + (size_t)d.table_idx * 257;
     for (uint32_t i = j; i < 257; i += kTeam) sm->cum[i] = cq[i];
     __syncthreads();
-    for (uint32_t slot = j; slot < kM; slot += kTeam) {
+    // zero-skip: slots below `skip` (all symbol 0) share entry 0; the host sends only tensors that fit
+    const uint32_t f0 = sm->cum[1];
+    const uint32_t skip = ZS ? (f0 < 2048u ? f0 : 2048u) : 0u;
+    const int s1 = (int)skip - 1;
+    for (uint32_t slot = skip + j; slot < kM; slot += kTeam) {
         uint32_t lo = 0, hi = 256;  // last s with cum[s] <= slot
         while (hi - lo > 1) {
             const uint32_t mid = (lo + hi) >> 1;
             if (sm->cum[mid] <= slot) lo = mid; else hi = mid;
         }
-        if (TL)
-            sm->slot_sym[slot] = (uint8_t)lo;
-        else
-            sm->dtab[slot] = lo | ((sm->cum[lo + 1] - sm->cum[lo] - 1) << 8) | ((slot - sm->cum[lo]) << 20);
+        const uint32_t e = lo | ((sm->cum[lo + 1] - sm->cum[lo] - 1) << 8) | ((slot - sm->cum[lo]) << 20);
+        if (ZS) {
+            if (slot - (uint32_t)s1 < kZsEntries) sm->dtab[slot - (uint32_t)s1] = e;
+        } else {
+            sm->dtab[slot] = e;
+        }
     }
-    if (TL)
-        for (uint32_t sy = j; sy < 256; sy += kTeam) sm->dtab[sy] = (sm->cum[sy + 1] - sm->cum[sy]) | (sm->cum[sy] << 16);
+    if (ZS && j == 0 && skip) sm->dtab[0] = ((f0 - 1u) << 8) | ((uint32_t)s1 << 20);
 
     DecChain ch[NV];
     uint32_t* ringw[NV];
@@ -1088,7 +1098,7 @@ __device__ __forceinline__ void decode_tensor(const TensorDesc& d, uint32_t ti,
         for (int u = 0; u < 8; ++u) {
             uint32_t acc = side[u];
 #pragma unroll
-            for (int k = 0; k < NV; ++k) acc = put_byte(acc, dec_step<TL>(ch[k], sm->dtab, sm->slot_sym, ringb[k]), chain_byte<NV, B0>(k));
+            for (int k = 0; k < NV; ++k) acc = put_byte(acc, dec_step<ZS>(ch[k], sm->dtab, s1, ringb[k]), chain_byte<NV, B0>(k));
             store_word(r + u, acc);
         }
 #pragma unroll
@@ -1105,14 +1115,14 @@ __device__ __forceinline__ void decode_tensor(const TensorDesc& d, uint32_t ti,
     for (; r < full_rows; ++r) {
         uint32_t acc = side_word(r);
 #pragma unroll
-        for (int k = 0; k < NV; ++k) acc = put_byte(acc, dec_step<TL>(ch[k], sm->dtab, sm->slot_sym, ringb[k]), chain_byte<NV, B0>(k));
+        for (int k = 0; k < NV; ++k) acc = put_byte(acc, dec_step<ZS>(ch[k], sm->dtab, s1, ringb[k]), chain_byte<NV, B0>(k));
         store_word(r, acc);
     }
     if (tail) {
         uint32_t acc = 0;
 #pragma unroll
         for (int k = 0; k < NV; ++k)
-            if (4 * j + chain_byte<NV, B0>(k) < tail) acc = put_byte(acc, dec_step<TL>(ch[k], sm->dtab, sm->slot_sym, ringb[k]), chain_byte<NV, B0>(k));
+            if (4 * j + chain_byte<NV, B0>(k) < tail) acc = put_byte(acc, dec_step<ZS>(ch[k], sm->dtab, s1, ringb[k]), chain_byte<NV, B0>(k));
 #pragma unroll
         for (uint32_t b = 0; b < 4; ++b) {
             const uint32_t t = 4 * j + b;
@@ -1143,15 +1153,10 @@ __device__ __forceinline__ void decode_tensor(const TensorDesc& d, uint32_t ti,
             bool bad = false;
             for (unsigned long long i = 0; i < n && !bad; ++i) {
                 const uint32_t slot = x & (kM - 1);
-                if (TL) {
-                    const uint32_t sy = sm->slot_sym[slot], t = sm->dtab[sy];
-                    if (sy) bad = true;  // must decode to symbol 0
-                    x = (t & 0xFFFFu) * (x >> kScaleBits) + slot - (t >> 16);
-                } else {
-                    const uint32_t e = sm->dtab[slot];
-                    if (e & 0xFFu) bad = true;
-                    x = (((e >> 8) & 0xFFFu) + 1u) * (x >> kScaleBits) + (e >> 20);
-                }
+                const int m = ZS ? max((int)slot, s1) : (int)slot;
+                const uint32_t e = sm->dtab[ZS ? m - s1 : (int)slot];
+                if (e & 0xFFu) bad = true;  // must decode to symbol 0
+                x = (((e >> 8) & 0xFFFu) + 1u) * (x >> kScaleBits) + (e >> 20) + (slot - (uint32_t)m);
                 while (x < kL && !bad) {
                     if (p >= end) bad = true; else x = (x << 8) | *p++;
                 }
@@ -1166,12 +1171,15 @@ __device__ __forceinline__ void decode_tensor(const TensorDesc& d, uint32_t ti,
 
 // One team (CTA of 64 threads) per tensor.  Each thread rebuilds one 32-bit word
 // of every row from its decoded bytes and the sidecar and stores it directly.
-// kInts as for the encoder; TL selects the table shape.
+// kInts as for the encoder; ZS selects the table shape.
 #ifndef CHK_DEC_MINBLOCKS
 #define CHK_DEC_MINBLOCKS 1
 #endif
-template <bool kInts, bool TL>
-__global__ void __launch_bounds__(kTeam, CHK_DEC_MINBLOCKS) rans_decode_kernel(const TensorDesc* __restrict__ descs,
+#ifndef CHK_DEC_ZS_MINBLOCKS
+#define CHK_DEC_ZS_MINBLOCKS 10
+#endif
+template <bool kInts, bool ZS>
+__global__ void __launch_bounds__(kTeam, ZS ? CHK_DEC_ZS_MINBLOCKS : CHK_DEC_MINBLOCKS) rans_decode_kernel(const TensorDesc* __restrict__ descs,
                                                             const uint32_t* __restrict__ freq_tables,  // [T][256]
                                                             const uint32_t* __restrict__ cum_tables,   // [T][257]
                                                             const LaneHeader* __restrict__ hdrs,
@@ -1198,11 +1206,11 @@ __global__ void __launch_bounds__(kTeam, CHK_DEC_MINBLOCKS) rans_decode_kernel(c
             continue;
         }
         if (d.es == 4 && d.spe == 2)
-            decode_tensor<2, 2, TL>(d, ti, freq_tables, cum_tables, hdrs, payload, sidecar, check_zero_lanes, status, smem);
+            decode_tensor<2, 2, ZS>(d, ti, freq_tables, cum_tables, hdrs, payload, sidecar, check_zero_lanes, status, smem);
         else if (d.es == 2 && d.spe == 1)
-            decode_tensor<2, 1, TL>(d, ti, freq_tables, cum_tables, hdrs, payload, sidecar, check_zero_lanes, status, smem);
+            decode_tensor<2, 1, ZS>(d, ti, freq_tables, cum_tables, hdrs, payload, sidecar, check_zero_lanes, status, smem);
         else if (kInts)
-            decode_tensor<4, 0, TL>(d, ti, freq_tables, cum_tables, hdrs, payload, sidecar, check_zero_lanes, status, smem);
+            decode_tensor<4, 0, ZS>(d, ti, freq_tables, cum_tables, hdrs, payload, sidecar, check_zero_lanes, status, smem);
         else
             __syncthreads();
     }

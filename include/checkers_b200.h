@@ -85,8 +85,8 @@ int chk_tensor_count(chk_context* ctx, uint64_t* count);
  * "segments" (1..8, default 4: launches the counting of a batch of 512 tensors or
  * more is cut into, so that the tables of one piece are built while the next is
  * counted), "encode_teams_per_sm" / "decode_teams_per_sm" (default 0 = as many as
- * fit: cap on the resident teams per SM), "decode_two_level" (0/1; 5 KiB two-level
- * decode table instead of 16 KiB).  None of the tuning options changes the bytes
+ * fit: cap on the resident teams per SM), "decode_zero_skip" (0/1; float tensors
+ * are decoded with a slot table that leaves out the slots of the zeroed low bytes, 8.5 KiB instead of 16 KiB).  None of the tuning options changes the bytes
  * that are produced.
  * "fast_stats" (0/1, default 0): chk_analyze sums in double over tiles spread over the
  * whole device instead of in the reference's order of float additions: minimum,

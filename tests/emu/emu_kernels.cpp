@@ -216,18 +216,38 @@ void emu_decode(size_t n, uint8_t* const* dsts, const uint64_t* n_bytes, const u
         if (raw[i]) b.descs[i].flags |= kFlagRaw;
     }
     std::memset(status_out, 0, n * 4);
-    std::vector<uint32_t> order(n);
-    for (size_t i = 0; i < n; ++i) order[i] = (uint32_t)(n - 1 - i);
-    uint32_t ticket = 0;
-    if (float_only)
+    // as the library's host side does: float tensors whose table qualifies go to the short-table kernel
+    std::vector<uint32_t> short_order, full_order;
+    bool any_int = false;
+    for (size_t k = 0; k < n; ++k) {
+        const uint32_t i = (uint32_t)(n - 1 - k);
+        const bool is_float = spe[i] * 2 == es[i];
+        if (float_only && is_float && !raw[i] && zero_skip_fits(nf[(size_t)table_idx[i] * 256]))
+            short_order.push_back(i);
+        else {
+            full_order.push_back(i);
+            any_int = any_int || !is_float;
+        }
+    }
+    uint32_t ticket[2] = {0, 0};
+    if (!short_order.empty())
         emu::launch(grid, kTeam, kDecSmemBytes[0][1], [&] {
-            rans_decode_kernel<false, true>(b.descs.data(), nf, cf, (const LaneHeader*)hdrs, payload, sidecar, order.data(),
-                                      &ticket, (uint32_t)n, check_zero_lanes, status_out);
+            rans_decode_kernel<false, true>(b.descs.data(), nf, cf, (const LaneHeader*)hdrs, payload, sidecar,
+                                            short_order.data(), &ticket[0], (uint32_t)short_order.size(), check_zero_lanes,
+                                            status_out);
+        });
+    if (full_order.empty()) return;
+    if (any_int)
+        emu::launch(grid, kTeam, kDecSmemBytes[1][0], [&] {
+            rans_decode_kernel<true, false>(b.descs.data(), nf, cf, (const LaneHeader*)hdrs, payload, sidecar,
+                                            full_order.data(), &ticket[1], (uint32_t)full_order.size(), check_zero_lanes,
+                                            status_out);
         });
     else
-        emu::launch(grid, kTeam, kDecSmemBytes[1][0], [&] {
-            rans_decode_kernel<true, false>(b.descs.data(), nf, cf, (const LaneHeader*)hdrs, payload, sidecar, order.data(),
-                                     &ticket, (uint32_t)n, check_zero_lanes, status_out);
+        emu::launch(grid, kTeam, kDecSmemBytes[0][0], [&] {
+            rans_decode_kernel<false, false>(b.descs.data(), nf, cf, (const LaneHeader*)hdrs, payload, sidecar,
+                                             full_order.data(), &ticket[1], (uint32_t)full_order.size(), check_zero_lanes,
+                                             status_out);
         });
 }
 

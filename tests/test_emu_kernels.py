@@ -215,3 +215,34 @@ def test_plane_split_and_merge(emu, misalign):
     emu.planes(outs, n_elem, es, spe, low_off, plane_off, stride, low, planes, grid=5, merge=True)
     for a, o in zip(tensors, outs):
         assert np.array_equal(a, o)
+
+
+def test_short_decode_table_with_zeros_in_value_lanes(emu, oracle):
+    """The decoder's short slot table leaves out the slots that symbol 0 owns; value lanes that do see zeros
+    (tensors with exact 0.0 entries: all four bytes zero) must decode through its entry 0."""
+    rng = np.random.default_rng(5)
+    tensors, es, spe, dts = make([("f32_master", 30000), ("bf16_weight", 50001)], 12)
+    for a, e in zip(tensors, es):
+        v = a.reshape(-1, e)
+        v[rng.random(v.shape[0]) < 0.3] = 0      # 30 % exact zeros
+    side, hist = emu.split_hist(tensors, es, spe)
+    tabs, masked_all, off, sides = [], [], 0, []
+    for i, a in enumerate(tensors):
+        m, s = oracle.split(a, dts[i])
+        tabs.append(oracle.normalize(oracle.byte_histogram(m), False))
+        assert tabs[-1][0][0] >= 2048      # symbol 0 owns at least half of the slots: the short table is used
+        masked_all.append(m)
+    nf = np.concatenate([t[0] for t in tabs]).astype(np.uint32)
+    cf = np.concatenate([t[1] for t in tabs]).astype(np.uint32)
+    payloads, hdrs, raws = [], [], []
+    for m, t in zip(masked_all, tabs):
+        p, h, r = oracle.compress_tensor(m, t[0], t[1], t[2])
+        payloads.append(p); hdrs.append(h); raws.append(r)
+    poff = np.cumsum([0] + [p.size for p in payloads])[:-1].astype(np.uint64)
+    payload = np.concatenate(payloads + [np.zeros(64, np.uint8)])
+    outs, status = emu.decode([a.size for a in tensors], es, spe, list(range(len(tensors))), nf, cf,
+                              np.concatenate(hdrs).astype(np.uint32), payload, poff, np.array(raws, np.uint8), side,
+                              check_zero=1, float_only=True)
+    assert not status.any()
+    for a, o in zip(tensors, outs):
+        assert np.array_equal(a, o)

@@ -369,3 +369,36 @@ def make_state_v3():
         raw, dt = synth(kind, n, 900 + i)
         names.append(name); host.append(raw.copy()); dtypes.append(dt)
     return names, host, dtypes
+
+
+def test_short_decode_table_option(chk):
+    """decode_zero_skip: float tensors decode through the short slot table, integer and raw-passthrough tensors
+    through the full one (two launches); the restored bytes are the inputs, zeros in value lanes included."""
+    names, host, dtypes = make_state_v3()
+    rng = np.random.default_rng(3)
+    for h, dt in zip(host, dtypes):
+        if dt in (F32, BF16) and h.size > 100000:
+            v = h.reshape(-1, ELEM_SIZE[dt])
+            v[rng.random(v.shape[0]) < 0.25] = 0
+    names.append("noise.i8"); host.append(rng.integers(0, 256, 1 << 18, dtype=np.uint8)); dtypes.append(I8)
+    dev = [dev_bytes(h) for h in host]
+    ctx = chk.Context(device=0)
+    register_all(ctx, names, dev, dtypes)
+    ctx.set_option("decode_zero_skip", 1)
+    ctx.set_option("verify_zero_lanes", 1)
+    ctx.compress(host_images=True)
+    images = [ctx.image(k).copy() for k in range(3)]
+    launches = ctx.kernel_launches()
+    outs = [torch.zeros(h.size, dtype=torch.uint8, device="cuda") for h in host]
+    assert ctx.decompress_resident([o.data_ptr() for o in outs]) == len(names)
+    assert ctx.kernel_launches() - launches >= 2
+    for o, d in zip(outs, dev):
+        assert torch.equal(o, d)
+    fresh = [torch.zeros_like(d) for d in dev]
+    ctx2 = chk.Context(device=0)
+    register_all(ctx2, names, fresh, dtypes)
+    ctx2.set_option("decode_zero_skip", 1)
+    assert ctx2.decompress_images(*images) == len(names)
+    for f, d in zip(fresh, dev):
+        assert torch.equal(f, d)
+    ctx.close(); ctx2.close()
