@@ -492,6 +492,8 @@ def main():
                     help="tensor bytes per chunk of the host-buffer pipeline")
     ap.add_argument("--cpu-sample-elems", type=int, default=32 << 20, help="parameters in the timed CPU sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--analyze-only", action="store_true",
+                    help="run only the statistics pass over the shard (for profiling) and print its time")
     ap.add_argument("--extras", action="store_true",
                     help="after the headline line, print a second JSON line: per-stage codec sweep, statistics pass, Re-Pair")
     ap.add_argument("--seed", type=int, default=0)
@@ -539,6 +541,14 @@ def main():
     dst = np.asarray(dst, dtype=np.uint64)
     shard_bytes = sum(b.numel() * b.element_size() for b in bufs)
     torch.cuda.synchronize()
+
+    if args.analyze_only:
+        ms = []
+        for _ in range(3):
+            ctx.analyze()
+            ms.append(ctx.timing("analyze_stats_ms"))
+        print(json.dumps({"analyze_stats_ms": min(ms), "bytes": shard_bytes, "gbs_of_2B": 2 * shard_bytes / min(ms) / 1e6}))
+        return
 
     lib_stream = torch.cuda.ExternalStream(ctx.stream_handle(), device=device)
 
