@@ -121,6 +121,25 @@ def make_shard_on_host(pieces, n_elems, seed):
     return [weight, master, exp_avg, exp_avg_sq]
 
 
+def bind_to_gpu_cpus(torch, local_rank):
+    """With several ranks on a box, keep this rank's threads -- and so the pinned host memory they touch first -- on
+    the CPUs next to its GPU (read from NVML; nothing is changed on the GPU).  Returns the CPU count or None."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        uuid = str(torch.cuda.get_device_properties(local_rank).uuid)
+        h = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid).encode())
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, (os.cpu_count() + 63) // 64)
+        cpus = {64 * i + b for i, w in enumerate(words) for b in range(64) if (int(w) >> b) & 1}
+        cpus &= os.sched_getaffinity(0)
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+            return len(cpus)
+    except Exception:
+        pass
+    return None
+
+
 def pcie_rates(torch, pinned, device):
     """Plain copies of one pinned host buffer: host->device, device->host, and both at once (GB/s each way)."""
     nbytes = pinned.numel() * pinned.element_size()
@@ -516,6 +535,7 @@ def main():
 
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
+    numa = bind_to_gpu_cpus(torch, local_rank) if world > 1 else None
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
 
@@ -644,15 +664,31 @@ def main():
         e2e_step()
     barrier()
     e2e_s = (time.perf_counter() - t0) / args.e2e_steps
+    e2e_rank_ms = [round(e2e_s * 1e3, 1)]
     if world > 1:
         t = torch.tensor([e2e_s], dtype=torch.float64, device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_s = float(t.item())
+        every = [torch.zeros_like(t) for _ in range(world)]
+        dist.all_gather(every, t)
+        e2e_rank_ms = [round(float(x.item()) * 1e3, 1) for x in every]
+        e2e_s = max(float(x.item()) for x in every)
     e2e_value = e_bytes * world / e2e_s / 1e9
     e2e_engines = {k: round(pipe.timing(k), 2) for k in e2e_keys}   # last step, this rank: busy time per engine
     pipe.close()
+    # the link's own rates: rank 0 alone (the other ranks wait), then all ranks at once (slowest rank counts)
+    barrier()
     pcie = pcie_rates(torch, h_in[1], device) if rank == 0 else None
+    barrier()
+    if world > 1:
+        mine = pcie_rates(torch, h_in[1], device)
+        t = torch.tensor([mine["h2d_gbs"], mine["d2h_gbs"], mine["both_directions_gbs_each"]], dtype=torch.float64,
+                         device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        if pcie:
+            pcie["all_ranks_at_once_min"] = {"h2d_gbs": round(float(t[0]), 1), "d2h_gbs": round(float(t[1]), 1),
+                                             "both_directions_gbs_each": round(float(t[2]), 1)}
     if pcie:
+        if world > 1:
+            pcie["both_directions_gbs_each"] = pcie["all_ranks_at_once_min"]["both_directions_gbs_each"]
         # every step moves h2d_bytes up and d2h_bytes down; with both directions busy the link cannot do better than
         floor_s = max(e_bytes + img_bytes, img_bytes + e_bytes) / (pcie["both_directions_gbs_each"] * 1e9)
         pcie["link_floor_ms_per_step"] = round(floor_s * 1e3, 2)
@@ -763,7 +799,8 @@ def main():
                                   f"in {len(pipe.chunks)} parts over {args.e2e_workers} staging slots with copies and "
                                   "kernels overlapped: H2D, compress, D2H of the file images; then H2D of the images, "
                                   "restore, D2H",
-                        "engine_busy_ms_rank0_last_step": e2e_engines, "pcie_rank0": pcie},
+                        "engine_busy_ms_rank0_last_step": e2e_engines, "pcie_rank0": pcie,
+                        "cpus_bound_rank0": numa, "ms_per_step_by_rank": e2e_rank_ms},
                 "gpu_launches": int(launches), "clocks": clocks}
         print(json.dumps(line), flush=True)
     if args.extras and rank == 0 and world == 1:

@@ -473,15 +473,19 @@ static void compress(Context* c, bool host_images) {
         if (fit < teams) teams = (uint32_t)fit;
     }
 
-    // ---- pieces the batch is counted in (equal bytes; a small batch is one piece)
+    // ---- pieces the batch is counted in (a small batch is one piece).  The tables of the last piece are the
+    // only ones the encode kernel has to wait for, so the last piece is small (1/16 of the bytes) and the
+    // others share the rest equally.
     const size_t n_seg = W >= 512 ? (size_t)c->segments : 1;
     std::vector<size_t> seg_end;
     {
         unsigned long long acc = 0;
+        const unsigned long long body = n_seg > 1 ? bytes_total - bytes_total / 16 : bytes_total;
         for (size_t i = 0; i < W; ++i) {
             acc += c->descs[i].n_bytes;
-            if (seg_end.size() + 1 < n_seg && acc * n_seg >= bytes_total * (seg_end.size() + 1)) seg_end.push_back(i + 1);
+            if (seg_end.size() + 1 < n_seg && acc * (n_seg - 1) >= body * (seg_end.size() + 1)) seg_end.push_back(i + 1);
         }
+        if (!seg_end.empty() && seg_end.back() == W) seg_end.pop_back();
         seg_end.push_back(W);
     }
     const size_t n_win = seg_end.size();
