@@ -662,15 +662,16 @@ def main():
     t0 = time.perf_counter()
     for _ in range(args.e2e_steps):
         e2e_step()
+    own_s = (time.perf_counter() - t0) / args.e2e_steps   # this rank's own steps (each ends with a device synchronise)
     barrier()
     e2e_s = (time.perf_counter() - t0) / args.e2e_steps
-    e2e_rank_ms = [round(e2e_s * 1e3, 1)]
+    e2e_rank_ms = [round(own_s * 1e3, 1)]
     if world > 1:
-        t = torch.tensor([e2e_s], dtype=torch.float64, device=device)
+        t = torch.tensor([e2e_s, own_s], dtype=torch.float64, device=device)
         every = [torch.zeros_like(t) for _ in range(world)]
         dist.all_gather(every, t)
-        e2e_rank_ms = [round(float(x.item()) * 1e3, 1) for x in every]
-        e2e_s = max(float(x.item()) for x in every)
+        e2e_rank_ms = [round(float(x[1].item()) * 1e3, 1) for x in every]
+        e2e_s = max(float(x[0].item()) for x in every)
     e2e_value = e_bytes * world / e2e_s / 1e9
     e2e_engines = {k: round(pipe.timing(k), 2) for k in e2e_keys}   # last step, this rank: busy time per engine
     pipe.close()
