@@ -374,6 +374,17 @@ def extras(args, torch, chk, ctx, shard_bytes, peak):
     out["analyze"]["fast"] = dict(analyze_ms(), kernel="stats_fast_pass1/2_kernel (sums in double, order-free)")
     ctx.set_option("fast_stats", 0)
 
+    # ---- the offline study of shared histograms: one HyperLogLog sketch per tensor, union per cluster of the analysis above
+    ctx.hll_sketch_all()
+    hll_ms = ctx.timing("hll_sketch_ms")
+    ctx.hll_sketch_all()
+    hll_ms = min(hll_ms, ctx.timing("hll_sketch_ms"))
+    own, shared = ctx.shared_vocabulary_report()
+    out["shared_vocabulary"] = {"kernel": "hll_sketch_kernel", "ms": hll_ms, "gbs": shard_bytes / hll_ms / 1e6,
+                                "frac_of_hbm_peak": shard_bytes / hll_ms / 1e6 / peak,
+                                "per_tensor_histogram_bytes": own, "shared_histogram_bytes": shared,
+                                "ratio": shared / own if own else None}
+
     # ---- codec microbenchmark configuration: 1 GiB fp32 ~ N(0, 1e-3) and 1 GiB bf16 ~ N(0, 0.02), seed 1, 4 MiB chunks
     g = torch.Generator(device=dev).manual_seed(1)
     chunk = 4 << 20

@@ -41,6 +41,11 @@ def _load():
         "chk_tensor_count": (C.c_int, [vp, C.POINTER(u64)]),
         "chk_set_option": (C.c_int, [vp, C.c_char_p, C.c_int64]),
         "chk_analyze": (C.c_int, [vp]),
+        "chk_hll_sketch_all": (C.c_int, [vp]),
+        "chk_hll_get": (C.c_int, [vp, u64, C.POINTER(C.c_uint8)]),
+        "chk_hll_merge": (C.c_int, [C.POINTER(C.c_uint8), C.POINTER(C.c_uint8)]),
+        "chk_hll_count": (C.c_int, [C.POINTER(C.c_uint8), C.POINTER(C.c_double)]),
+        "chk_shared_vocabulary_report": (C.c_int, [vp, C.POINTER(u64), C.POINTER(u64)]),
         "chk_get_tensor_stats": (C.c_int, [vp, u64, u32p, f32p, f32p, f32p]),
         "chk_get_cluster_ids": (C.c_int, [vp, C.POINTER(C.c_int32), u64, C.POINTER(C.c_int32)]),
         "chk_get_cluster_anchor": (C.c_int, [vp, C.c_int32, C.c_char_p]),

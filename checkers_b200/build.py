@@ -9,7 +9,7 @@ LIB_DIR = os.path.join(PKG, "lib")
 # CHECKERS_B200_LIB points the package at a library built elsewhere (it is then never rebuilt here)
 LIB = os.environ.get("CHECKERS_B200_LIB") or os.path.join(LIB_DIR, "libcheckers_b200.so")
 SOURCES = ["engine.cu", "repair.cu"]
-HEADERS = ["kernels.cuh", "rans_kernels.cuh", "table_kernels.cuh", "stats_kernels.cuh", "plane_kernels.cuh", "format_v3.inc", "sort_replica.hpp", "host_stream.inc", "tables.hpp", "clusters.hpp",
+HEADERS = ["kernels.cuh", "rans_kernels.cuh", "table_kernels.cuh", "stats_kernels.cuh", "plane_kernels.cuh", "study_kernels.cuh", "format_v3.inc", "sort_replica.hpp", "host_stream.inc", "tables.hpp", "clusters.hpp",
            os.path.join("..", "..", "include", "checkers_b200.h")]
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -92,6 +92,22 @@ class Context:
     def analyze(self):
         check(lib.chk_analyze(self._h))
 
+    # ---- vocabulary sketches (the reference's offline study of shared histograms)
+    def hll_sketch_all(self):
+        """One HyperLogLog sketch (2^14 registers over the 32-bit symbols) per registered tensor, on the device."""
+        check(lib.chk_hll_sketch_all(self._h))
+
+    def hll_sketch(self, index):
+        regs = np.zeros(16384, np.uint8)
+        check(lib.chk_hll_get(self._h, int(index), regs.ctypes.data_as(C.POINTER(C.c_uint8))))
+        return regs
+
+    def shared_vocabulary_report(self):
+        """(bytes of per-tensor histograms, bytes with one histogram per current cluster), as the study prices them."""
+        a, b = C.c_uint64(), C.c_uint64()
+        check(lib.chk_shared_vocabulary_report(self._h, C.byref(a), C.byref(b)))
+        return a.value, b.value
+
     def tensor_stats(self, index):
         hist = np.zeros(256, np.uint32)
         mom, mm, fp = np.zeros(4, np.float32), np.zeros(2, np.float32), np.zeros(5, np.float32)

@@ -116,6 +116,7 @@ struct Context {
     bool have_clusters = false;
     ClusterMap clusters;
     std::vector<StatsOut> stats;
+    std::vector<uint8_t> hll;     // one 2^14-register sketch per registered tensor (chk_hll_sketch_all)
 
     bool repair_tables = false, verify_zero_lanes = false, allow_undecodable = false;
     bool fast_stats = false;      // statistics with order-free sums over the whole device (see stats_kernels.cuh)
@@ -126,7 +127,7 @@ struct Context {
     bool decode_zero_skip = false; // float tensors whose table allows it are decoded with the short slot table (measured slower)
 
     // device buffers (grow-only, from the context's pool)
-    DevBuf d_descs, d_tiles, d_hist, d_sidecar, d_scratch, d_hdrs, d_order, d_ticket, d_psize, d_zslots, d_zregions, d_zslot_of, d_jobs, d_sums, d_stats_part, d_stats_mid, d_poff, d_fileorder,
+    DevBuf d_descs, d_tiles, d_hist, d_sidecar, d_scratch, d_hdrs, d_order, d_ticket, d_psize, d_zslots, d_zregions, d_zslot_of, d_jobs, d_sums, d_stats_part, d_stats_mid, d_poff, d_fileorder, d_hll32, d_hll8,
         d_payload, d_enc, d_freq, d_cum, d_status, d_stats_desc, d_stats_out;
     cudaStream_t side_stream = nullptr;
     std::vector<cudaEvent_t> ev_count, ev_tab;
@@ -473,17 +474,16 @@ static void compress(Context* c, bool host_images) {
         if (fit < teams) teams = (uint32_t)fit;
     }
 
-    // ---- pieces the batch is counted in (a small batch is one piece).  The tables of the last piece are the
-    // only ones the encode kernel has to wait for, so the last piece is small (1/16 of the bytes) and the
-    // others share the rest equally.
+    // ---- pieces the batch is counted in (equal bytes; a small batch is one piece).  The tables of a piece are
+    // built while the next piece is counted, so a piece must take about as long to count as the tables of the
+    // one before take to build: a small last piece (1/16 of the bytes) exposed more table time, not less.
     const size_t n_seg = W >= 512 ? (size_t)c->segments : 1;
     std::vector<size_t> seg_end;
     {
         unsigned long long acc = 0;
-        const unsigned long long body = n_seg > 1 ? bytes_total - bytes_total / 16 : bytes_total;
         for (size_t i = 0; i < W; ++i) {
             acc += c->descs[i].n_bytes;
-            if (seg_end.size() + 1 < n_seg && acc * (n_seg - 1) >= body * (seg_end.size() + 1)) seg_end.push_back(i + 1);
+            if (seg_end.size() + 1 < n_seg && acc * n_seg >= bytes_total * (seg_end.size() + 1)) seg_end.push_back(i + 1);
         }
         if (!seg_end.empty() && seg_end.back() == W) seg_end.pop_back();
         seg_end.push_back(W);
@@ -1134,6 +1134,72 @@ static void analyze(Context* c) {
     c->timing["analyze_cluster_ms"] = wall_ms(t0);
 }
 
+// ------------------------------------------------------------------ vocabulary sketches (offline study)
+// One HyperLogLog sketch per registered tensor, all in one pass (study_kernels.cuh).
+static void hll_sketch_all(Context* c) {
+    CHK_CUDA(cudaSetDevice(c->device));
+    const size_t N = c->tensors.size();
+    c->hll.assign(N * (size_t)kHllRegs, 0);
+    if (N == 0) return;
+    cudaStream_t s = c->stream;
+    std::vector<StatsDesc> d(N);
+    pin_ensure(c->h_tiles, (N + 1) * 4);
+    uint32_t* tile_start = static_cast<uint32_t*>(c->h_tiles.p);
+    unsigned long long tiles = 0;
+    for (size_t i = 0; i < N; ++i) {
+        const Tensor& t = c->tensors[i];
+        const uint32_t es = elem_size(t.dtype);
+        d[i] = StatsDesc{es ? t.ptr : nullptr, t.n_elem, t.dtype, 0};
+        tile_start[i] = (uint32_t)tiles;
+        if (d[i].ptr && d[i].n) tiles += (d[i].n * es + kHllTileBytes - 1) / kHllTileBytes;
+        if (tiles > 0xFFFFFFFFull) throw Error{CHK_ERR_CAPACITY, "too many tiles in one batch"};
+    }
+    tile_start[N] = (uint32_t)tiles;
+    if (!tiles) return;
+    const unsigned long long regs = (unsigned long long)N * kHllRegs;
+    dev_ensure(c, c->d_stats_desc, N * sizeof(StatsDesc));
+    dev_ensure(c, c->d_tiles, (N + 1) * 4);
+    dev_ensure(c, c->d_hll32, regs * 4);
+    dev_ensure(c, c->d_hll8, regs);
+    CHK_CUDA(cudaMemcpyAsync(c->d_stats_desc.p, d.data(), N * sizeof(StatsDesc), cudaMemcpyHostToDevice, s));
+    control_copy(c, c->d_tiles.p, c->h_tiles.p, (N + 1) * 4, s);
+    CHK_CUDA(cudaMemsetAsync(c->d_hll32.p, 0, regs * 4, s));
+    CHK_CUDA(cudaEventRecord(c->ev[0], s));
+    const uint32_t smem = kHllRegs * 4;
+    CHK_CUDA(cudaFuncSetAttribute(hll_sketch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const unsigned long long cap = (unsigned long long)(c->sm_count > 0 ? c->sm_count : 1) * 3;
+    hll_sketch_kernel<<<(uint32_t)(tiles < cap ? tiles : cap), 256, smem, s>>>(
+        static_cast<const StatsDesc*>(c->d_stats_desc.p), static_cast<const uint32_t*>(c->d_tiles.p), (uint32_t)N,
+        (uint32_t)tiles, static_cast<uint32_t*>(c->d_hll32.p));
+    hll_pack_kernel<<<(uint32_t)cap, 256, 0, s>>>(static_cast<const uint32_t*>(c->d_hll32.p),
+                                                  static_cast<uint8_t*>(c->d_hll8.p), regs);
+    CHK_CUDA(cudaGetLastError());
+    c->launches += 2;
+    CHK_CUDA(cudaEventRecord(c->ev[1], s));
+    CHK_CUDA(cudaMemcpyAsync(c->hll.data(), c->d_hll8.p, regs, cudaMemcpyDeviceToHost, s));
+    sync_stream(c, s);
+    c->timing["hll_sketch_ms"] = ms_between(c->ev[0], c->ev[1]);
+}
+
+// Cardinality estimate of one sketch: alpha m^2 / sum 2^-register with the small- and large-range corrections
+// (scripts/llama-3-8b/experiment_2.py:71-82).  The sum is formed over the 19 possible register values, which is
+// exact in double, as is numpy's pairwise sum of the same powers of two.
+static double hll_count(const uint8_t* regs) {
+    unsigned long long by_value[64] = {};
+    for (uint32_t i = 0; i < kHllRegs; ++i) by_value[regs[i] & 63]++;
+    double sum = 0.0;
+    for (int k = 0; k < 64; ++k) sum += (double)by_value[k] * std::ldexp(1.0, -k);
+    const double m = (double)kHllRegs;
+    const double alpha = 0.7213 / (1.0 + 1.079 / m);
+    double raw = alpha * m * m * (1.0 / sum);
+    if (raw <= 2.5 * m) {
+        if (by_value[0] > 0) raw = m * std::log(m / (double)by_value[0]);
+    } else if (raw > (1.0 / 30.0) * 4294967296.0) {
+        raw = -4294967296.0 * std::log(1.0 - raw / 4294967296.0);
+    }
+    return raw;
+}
+
 }  // namespace chk
 
 // ====================================================================== C ABI
@@ -1209,7 +1275,7 @@ int chk_context_destroy(chk_context* c) {
     if (c->stream) cudaStreamSynchronize(c->stream);
     DevBuf* bufs[] = {&c->d_descs, &c->d_tiles, &c->d_hist, &c->d_sidecar, &c->d_scratch, &c->d_hdrs,
                       &c->d_order, &c->d_ticket, &c->d_psize, &c->d_zslots, &c->d_zregions, &c->d_zslot_of, &c->d_jobs, &c->d_sums, &c->d_payload, &c->d_enc,
-                      &c->d_freq, &c->d_cum, &c->d_status, &c->d_stats_desc, &c->d_stats_out, &c->d_stats_part, &c->d_stats_mid, &c->d_poff, &c->d_fileorder};
+                      &c->d_freq, &c->d_cum, &c->d_status, &c->d_stats_desc, &c->d_stats_out, &c->d_stats_part, &c->d_stats_mid, &c->d_poff, &c->d_fileorder, &c->d_hll32, &c->d_hll8};
     for (DevBuf* b : bufs)
         if (b->p) cudaFreeAsync(b->p, c->stream);
     if (c->stream) cudaStreamSynchronize(c->stream);
@@ -1314,6 +1380,69 @@ int chk_analyze(chk_context* c) {
     CHK_API_BEGIN
     CHK_REQUIRE(c, "context is NULL");
     analyze(c);
+    CHK_API_END
+}
+
+int chk_hll_sketch_all(chk_context* c) {
+    CHK_API_BEGIN
+    CHK_REQUIRE(c, "context is NULL");
+    hll_sketch_all(c);
+    CHK_API_END
+}
+
+int chk_hll_get(chk_context* c, uint64_t index, uint8_t regs[16384]) {
+    CHK_API_BEGIN
+    CHK_REQUIRE(c && regs, "NULL argument");
+    CHK_REQUIRE((index + 1) * (uint64_t)kHllRegs <= c->hll.size(), "no sketch for this tensor: call chk_hll_sketch_all");
+    std::memcpy(regs, c->hll.data() + index * kHllRegs, kHllRegs);
+    CHK_API_END
+}
+
+int chk_hll_merge(uint8_t acc[16384], const uint8_t other[16384]) {
+    CHK_API_BEGIN
+    CHK_REQUIRE(acc && other, "NULL argument");
+    for (uint32_t i = 0; i < kHllRegs; ++i) acc[i] = acc[i] > other[i] ? acc[i] : other[i];
+    CHK_API_END
+}
+
+int chk_hll_count(const uint8_t regs[16384], double* estimate) {
+    CHK_API_BEGIN
+    CHK_REQUIRE(regs && estimate, "NULL argument");
+    *estimate = hll_count(regs);
+    CHK_API_END
+}
+
+// Bytes of per-tensor histograms against histograms shared inside the current clusters, as the study prices
+// them: 8 bytes per distinct 32-bit symbol + 64 (scripts/llama-3-8b/experiment_2.py:104, 145, 440-470).
+int chk_shared_vocabulary_report(chk_context* c, uint64_t* per_tensor_bytes, uint64_t* shared_bytes) {
+    CHK_API_BEGIN
+    CHK_REQUIRE(c && per_tensor_bytes && shared_bytes, "NULL argument");
+    const size_t N = c->tensors.size();
+    CHK_REQUIRE(c->hll.size() == N * (size_t)kHllRegs, "no sketches: call chk_hll_sketch_all");
+    uint64_t own = 0, shared = 0;
+    std::map<int, std::vector<uint8_t>> unions;
+    for (size_t i = 0; i < N; ++i) {
+        const Tensor& t = c->tensors[i];
+        if (!t.ptr || t.n_elem == 0 || elem_size(t.dtype) == 0) continue;
+        const uint8_t* r = c->hll.data() + i * kHllRegs;
+        const uint64_t mine = (uint64_t)(hll_count(r) * 8.0) + 64;
+        own += mine;
+        int cid = -1;
+        if (c->have_clusters) {
+            auto it = c->clusters.tensor_to_cluster.find(t.name);
+            if (it != c->clusters.tensor_to_cluster.end()) cid = it->second;
+        }
+        if (cid < 0) {
+            shared += mine;
+            continue;
+        }
+        auto& u = unions[cid];
+        if (u.empty()) u.assign(kHllRegs, 0);
+        for (uint32_t k = 0; k < kHllRegs; ++k) u[k] = u[k] > r[k] ? u[k] : r[k];
+    }
+    for (const auto& kv : unions) shared += (uint64_t)(hll_count(kv.second.data()) * 8.0) + 64;
+    *per_tensor_bytes = own;
+    *shared_bytes = shared;
     CHK_API_END
 }
 

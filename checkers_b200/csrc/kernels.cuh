@@ -624,3 +624,4 @@ __global__ void __launch_bounds__(256) tensor_stats_kernel(const StatsDesc* __re
 
 #include "stats_kernels.cuh"
 #include "plane_kernels.cuh"
+#include "study_kernels.cuh"

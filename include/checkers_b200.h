@@ -107,6 +107,17 @@ int chk_set_option(chk_context* ctx, const char* key, int64_t value);
 int chk_analyze(chk_context* ctx);
 int chk_get_tensor_stats(chk_context* ctx, uint64_t index, uint32_t hist[256], float moments[4], float minmax[2],
                          float fingerprint[5]);
+/* ---- vocabulary sketches: the reference's offline study of shared histograms
+ * (scripts/llama-3-8b/experiment_2.py:31-85, 122-145: HyperLogLog with 2^14 registers over a tensor's 32-bit
+ * symbols, union of a cluster = element-wise maximum).  chk_hll_sketch_all sketches every registered tensor
+ * in one pass on the device; merge and count are host arithmetic on 16 KiB.  chk_shared_vocabulary_report
+ * prices per-tensor histograms against histograms shared inside the current clusters (8 bytes per distinct
+ * symbol + 64, as the study does). */
+int chk_hll_sketch_all(chk_context* ctx);
+int chk_hll_get(chk_context* ctx, uint64_t index, uint8_t regs[16384]);
+int chk_hll_merge(uint8_t acc[16384], const uint8_t other[16384]);
+int chk_hll_count(const uint8_t regs[16384], double* estimate);
+int chk_shared_vocabulary_report(chk_context* ctx, uint64_t* per_tensor_bytes, uint64_t* shared_bytes);
 /* cluster_id[i] for every registered tensor (-1 = singleton); *n_clusters out. */
 int chk_get_cluster_ids(chk_context* ctx, int32_t* cluster_id, uint64_t capacity, int32_t* n_clusters);
 int chk_get_cluster_anchor(chk_context* ctx, int32_t cluster, char name_out[256]);

@@ -321,6 +321,25 @@ void emu_planes(size_t n, void* const* tensors, const uint64_t* n_elem, const ui
         emu::launch(grid, 256, 0, [&] { plane_split_kernel(d.data(), ts.data(), (uint32_t)n, tiles, low, planes); });
 }
 
+// HyperLogLog sketches of n tensors: regs_out n x 16384 words
+void emu_hll(size_t n, const void* const* ptrs, const uint64_t* n_elem, const uint32_t* dtype, uint32_t* regs_out,
+             uint32_t grid) {
+    std::vector<StatsDesc> d(n);
+    std::vector<uint32_t> tile_start(n + 1);
+    uint32_t tiles = 0;
+    for (size_t i = 0; i < n; ++i) {
+        d[i] = StatsDesc{ptrs[i], n_elem[i], dtype[i], 0};
+        tile_start[i] = tiles;
+        if (ptrs[i] && n_elem[i])
+            tiles += (uint32_t)((n_elem[i] * stats_elem_size(dtype[i]) + kHllTileBytes - 1) / kHllTileBytes);
+    }
+    tile_start[n] = tiles;
+    std::memset(regs_out, 0, n * kHllRegs * 4);
+    if (!tiles) return;
+    if (grid > tiles) grid = tiles;
+    emu::launch(grid, 256, kHllRegs * 4, [&] { hll_sketch_kernel(d.data(), tile_start.data(), (uint32_t)n, tiles, regs_out); });
+}
+
 // the host routine the device kernel must agree with
 void emu_host_enc_entries(const uint32_t* nf, const uint32_t* cf, uint32_t* enc_out) {
     FreqTable ft;

@@ -155,6 +155,13 @@ class Emu:
         self.lib.emu_planes(C.c_size_t(n), ptrs, _p(ne, u64p), _p(e, u32p), _p(sp, u32p), _p(lo, u64p), _p(po, u64p),
                             _p(st, u64p), _p(low), _p(planes), C.c_uint32(grid), C.c_uint32(int(merge)))
 
+    def hll(self, tensors, n_elem, dtypes, grid=3):
+        n, ptrs = self._arrays(tensors)
+        ne, dt = np.array(n_elem, np.uint64), np.array(dtypes, np.uint32)
+        out = np.zeros((n, 16384), np.uint32)
+        self.lib.emu_hll(C.c_size_t(n), ptrs, _p(ne, u64p), _p(dt, u32p), _p(out, u32p), C.c_uint32(grid))
+        return out.astype(np.uint8)
+
     def stats(self, tensors, n_elem, dtypes, bins=256, grid=2, fast=False):
         n, ptrs = self._arrays(tensors)
         ne = np.array(n_elem, np.uint64)
