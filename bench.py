@@ -766,7 +766,16 @@ def main():
                 "note": "compress = counting, then one kernel that encodes every tensor and gathers its lanes; tables are "
                         "built on the device while the next piece is counted (table_exposed_ms is what that did not hide)",
                 "table_exposed_ms": float(np.mean(table_ms)),
-                "compress_call_ms": float(np.mean(cwall_ms)), "restore_call_ms": float(np.mean(dwall_ms))}
+                "compress_call_ms": float(np.mean(cwall_ms)), "restore_call_ms": float(np.mean(dwall_ms)),
+                # DRAM bytes per tensor byte of the whole compress call: the counting pass streams (read 1, write the
+                # low bytes), the fused kernel's figure is the ncu one above; against one read, one low-byte write and
+                # one payload write if the tables were known beforehand and a lane's length before it ends
+                "compress_dram_bytes_per_tensor_byte": {
+                    "counting": (shard_bytes + sidecar_bytes) / shard_bytes,
+                    "fused_encode_ncu": NCU_DRAM_BYTES_PER_TENSOR_BYTE["rans_encode_fused_kernel"],
+                    "total": (shard_bytes + sidecar_bytes) / shard_bytes
+                    + NCU_DRAM_BYTES_PER_TENSOR_BYTE["rans_encode_fused_kernel"],
+                    "single_pass_ideal": (shard_bytes + sidecar_bytes + payload_bytes) / shard_bytes}}
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
