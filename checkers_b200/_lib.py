@@ -36,6 +36,7 @@ def _load():
         "chk_context_create_ex": (C.c_int, [C.c_int, C.c_int, C.c_int, u64, C.POINTER(vp)]),
         "chk_context_destroy": (C.c_int, [vp]),
         "chk_reset": (C.c_int, [vp]),
+        "chk_release_workspace": (C.c_int, [vp]),
         "chk_set_histogram_bins": (C.c_int, [vp, C.c_uint32]),
         "chk_register_tensor": (C.c_int, [vp, C.c_char_p, vp, u64, C.c_uint8, C.c_uint8]),
         "chk_tensor_count": (C.c_int, [vp, C.POINTER(u64)]),

@@ -62,6 +62,10 @@ class Context:
         self._keep.clear()
         self.names.clear()
 
+    def release_workspace(self):
+        """Give the context's device memory back to the device (it is otherwise kept and only grows)."""
+        check(lib.chk_release_workspace(self._h))
+
     def set_histogram_bins(self, bins):
         check(lib.chk_set_histogram_bins(self._h, int(bins)))
 

@@ -1267,18 +1267,38 @@ int chk_context_create_ex(int device, int rank, int local_rank, uint64_t workspa
     CHK_API_END
 }
 
+// Every device buffer of the context back to its pool, and the pool's memory back to the device.
+static void release_device_buffers(chk_context* c) {
+    if (c->stream) cudaStreamSynchronize(c->stream);
+    if (c->side_stream) cudaStreamSynchronize(c->side_stream);
+    DevBuf* bufs[] = {&c->d_descs, &c->d_tiles, &c->d_hist, &c->d_sidecar, &c->d_scratch, &c->d_hdrs,
+                      &c->d_order, &c->d_ticket, &c->d_psize, &c->d_zslots, &c->d_zregions, &c->d_zslot_of, &c->d_jobs, &c->d_sums, &c->d_payload, &c->d_enc,
+                      &c->d_freq, &c->d_cum, &c->d_status, &c->d_stats_desc, &c->d_stats_out, &c->d_stats_part, &c->d_stats_mid, &c->d_poff, &c->d_fileorder, &c->d_hll32, &c->d_hll8};
+    for (DevBuf* b : bufs) {
+        if (b->p) cudaFreeAsync(b->p, c->stream);
+        b->p = nullptr;
+        b->cap = 0;
+    }
+    if (c->stream) cudaStreamSynchronize(c->stream);
+    if (c->pool) cudaMemPoolTrimTo(c->pool, 0);
+}
+
+int chk_release_workspace(chk_context* c) {
+    CHK_API_BEGIN
+    CHK_REQUIRE(c, "context is NULL");
+    CHK_CUDA(cudaSetDevice(c->device));
+    v3_destroy(c);
+    release_device_buffers(c);
+    c->have_resident = false;  // the device-resident result lived in those buffers; host images stay
+    CHK_API_END
+}
+
 int chk_context_destroy(chk_context* c) {
     CHK_API_BEGIN
     if (!c) return CHK_OK;
     cudaSetDevice(c->device);
     v3_destroy(c);
-    if (c->stream) cudaStreamSynchronize(c->stream);
-    DevBuf* bufs[] = {&c->d_descs, &c->d_tiles, &c->d_hist, &c->d_sidecar, &c->d_scratch, &c->d_hdrs,
-                      &c->d_order, &c->d_ticket, &c->d_psize, &c->d_zslots, &c->d_zregions, &c->d_zslot_of, &c->d_jobs, &c->d_sums, &c->d_payload, &c->d_enc,
-                      &c->d_freq, &c->d_cum, &c->d_status, &c->d_stats_desc, &c->d_stats_out, &c->d_stats_part, &c->d_stats_mid, &c->d_poff, &c->d_fileorder, &c->d_hll32, &c->d_hll8};
-    for (DevBuf* b : bufs)
-        if (b->p) cudaFreeAsync(b->p, c->stream);
-    if (c->stream) cudaStreamSynchronize(c->stream);
+    release_device_buffers(c);
     PinBuf* pins[] = {&c->h_hdrs, &c->h_poff, &c->h_psize, &c->h_descs, &c->h_status, &c->h_jobs, &c->h_sums, &c->h_freq, &c->h_cum, &c->h_stats, &c->h_order, &c->h_tiles,
                       &c->img[0], &c->img[1], &c->img[2]};
     for (PinBuf* b : pins)

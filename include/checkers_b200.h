@@ -73,6 +73,12 @@ int chk_context_create(int device, int rank, int local_rank, chk_context** out);
 int chk_context_create_ex(int device, int rank, int local_rank, uint64_t workspace_bytes, chk_context** out);
 int chk_context_destroy(chk_context* ctx);
 int chk_reset(chk_context* ctx); /* MemoryManager::reset: forget tensors, clusters, results */
+/* Gives the context's device memory (sidecar section, payload heap, encode workspace, tables, ...) back to
+ * the device.  The buffers are otherwise kept from call to call and only grow; a checkpoint hook calls this
+ * after a save so that the training step gets the memory back.  The device-resident result of the last
+ * chk_compress is gone afterwards; host images and registered tensors stay.  (The reference frees its
+ * per-tensor buffers after every tensor: src/ANSCompressor.cpp:348-388.) */
+int chk_release_workspace(chk_context* ctx);
 int chk_set_histogram_bins(chk_context* ctx, uint32_t bins); /* initialize_context(histogram_bins=) */
 int chk_register_tensor(chk_context* ctx, const char* name, const void* device_ptr, uint64_t num_elements,
                         uint8_t dtype, uint8_t category);

@@ -402,3 +402,31 @@ def test_short_decode_table_option(chk):
     for f, d in zip(fresh, dev):
         assert torch.equal(f, d)
     ctx.close(); ctx2.close()
+
+
+def test_release_workspace_returns_device_memory(chk, tmp_path):
+    """The context keeps its buffers from call to call; release_workspace gives them back to the device, the host
+    images stay, and the next compress works as before."""
+    names, host, dtypes = make_state_v3()
+    dev = [dev_bytes(h) for h in host]
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()
+    ctx = chk.Context(device=0)
+    register_all(ctx, names, dev, dtypes)
+    free0 = torch.cuda.mem_get_info()[0]
+    ctx.compress(host_images=True)
+    first = [ctx.image(k).copy() for k in range(3)]
+    held = free0 - torch.cuda.mem_get_info()[0]
+    assert held > sum(h.size for h in host) // 2          # sidecar section, payload heap, scratch ...
+    ctx.release_workspace()
+    assert free0 - torch.cuda.mem_get_info()[0] <= 4 << 20, "device memory was not given back"
+    assert all(np.array_equal(ctx.image(k), first[k]) for k in range(3))
+    with pytest.raises(chk.CheckersError):
+        ctx.decompress_resident([d.data_ptr() for d in dev])     # the resident result went with the buffers
+    ctx.compress(host_images=True)
+    assert all(np.array_equal(ctx.image(k), first[k]) for k in range(3))
+    ctx.set_option("format_version", 3)
+    ctx.compress(host_images=False)
+    ctx.release_workspace()
+    assert free0 - torch.cuda.mem_get_info()[0] <= 4 << 20
+    ctx.close()
