@@ -42,6 +42,7 @@ def _load():
         "chk_tensor_count": (C.c_int, [vp, C.POINTER(u64)]),
         "chk_set_option": (C.c_int, [vp, C.c_char_p, C.c_int64]),
         "chk_analyze": (C.c_int, [vp]),
+        "chk_shared_model_cost": (C.c_int, [vp, C.POINTER(u64), u64, C.POINTER(C.c_double), C.POINTER(u64)]),
         "chk_hll_sketch_all": (C.c_int, [vp]),
         "chk_hll_get": (C.c_int, [vp, u64, C.POINTER(C.c_uint8)]),
         "chk_hll_merge": (C.c_int, [C.POINTER(C.c_uint8), C.POINTER(C.c_uint8)]),

@@ -106,6 +106,15 @@ class Context:
         check(lib.chk_hll_get(self._h, int(index), regs.ctypes.data_as(C.POINTER(C.c_uint8))))
         return regs
 
+    def shared_model_cost(self, indices):
+        """(stream bytes, vocabulary size) of the registered tensors `indices` coded under one shared model over
+        their 32-bit symbols, as the reference's study prices it; one index = the tensor's own model."""
+        idx = np.ascontiguousarray(indices, dtype=np.uint64)
+        b, v = C.c_double(), C.c_uint64()
+        check(lib.chk_shared_model_cost(self._h, idx.ctypes.data_as(C.POINTER(C.c_uint64)), idx.size, C.byref(b),
+                                        C.byref(v)))
+        return b.value, v.value
+
     def shared_vocabulary_report(self):
         """(bytes of per-tensor histograms, bytes with one histogram per current cluster), as the study prices them."""
         a, b = C.c_uint64(), C.c_uint64()

@@ -127,7 +127,7 @@ struct Context {
     bool decode_zero_skip = false; // float tensors whose table allows it are decoded with the short slot table (measured slower)
 
     // device buffers (grow-only, from the context's pool)
-    DevBuf d_descs, d_tiles, d_hist, d_sidecar, d_scratch, d_hdrs, d_order, d_ticket, d_psize, d_zslots, d_zregions, d_zslot_of, d_jobs, d_sums, d_stats_part, d_stats_mid, d_poff, d_fileorder, d_hll32, d_hll8,
+    DevBuf d_descs, d_tiles, d_hist, d_sidecar, d_scratch, d_hdrs, d_order, d_ticket, d_psize, d_zslots, d_zregions, d_zslot_of, d_jobs, d_sums, d_stats_part, d_stats_mid, d_poff, d_fileorder, d_hll32, d_hll8, d_symkeys, d_symcounts,
         d_payload, d_enc, d_freq, d_cum, d_status, d_stats_desc, d_stats_out;
     cudaStream_t side_stream = nullptr;
     std::vector<cudaEvent_t> ev_count, ev_tab;
@@ -1181,6 +1181,95 @@ static void hll_sketch_all(Context* c) {
     c->timing["hll_sketch_ms"] = ms_between(c->ev[0], c->ev[1]);
 }
 
+// Bytes of the group's tensors coded under one shared 32-bit model, and the size of the model's vocabulary
+// (cluster_cost_worker, scripts/llama-3-8b/experiment_2_1.py:273-330; a group of one tensor gives the own-model
+// figures of tensor_stats_worker, :129-184).
+static void shared_model_cost(Context* c, const uint64_t* index, size_t n, double* stream_bytes, uint64_t* vocab) {
+    CHK_CUDA(cudaSetDevice(c->device));
+    *stream_bytes = 0.0;
+    *vocab = 0;
+    cudaStream_t s = c->stream;
+    std::vector<StatsDesc> d;
+    std::vector<uint32_t> tiles_before;
+    unsigned long long tiles = 0, symbols = 0;
+    for (size_t k = 0; k < n; ++k) {
+        if (index[k] >= c->tensors.size()) throw Error{CHK_ERR_INVALID, "tensor index out of range"};
+        const Tensor& t = c->tensors[index[k]];
+        const uint32_t es = elem_size(t.dtype);
+        if (!t.ptr || !t.n_elem || !es) continue;
+        d.push_back(StatsDesc{t.ptr, t.n_elem, t.dtype, 0});
+        tiles_before.push_back((uint32_t)tiles);
+        tiles += (t.n_elem * es + kHllTileBytes - 1) / kHllTileBytes;
+        symbols += t.n_elem;
+        if (tiles > 0xFFFFFFFFull) throw Error{CHK_ERR_CAPACITY, "too many tiles in one group"};
+    }
+    if (!symbols) return;
+    tiles_before.push_back((uint32_t)tiles);
+    // a table with at least twice as many slots as there are symbols (all of them may be distinct)
+    unsigned long long capacity = 1024;
+    while (capacity < 2 * symbols) capacity <<= 1;
+    if (capacity > (1ull << 31)) throw Error{CHK_ERR_CAPACITY, "group too large for the symbol table (2^30 symbols at most)"};
+    const size_t N = d.size();
+    const uint32_t blocks = (uint32_t)(c->sm_count > 0 ? c->sm_count : 1) * 8;
+    dev_ensure(c, c->d_stats_desc, N * sizeof(StatsDesc));
+    dev_ensure(c, c->d_tiles, (N + 1) * 4);
+    dev_ensure(c, c->d_symkeys, capacity * 8);
+    dev_ensure(c, c->d_symcounts, capacity * 4);
+    dev_ensure(c, c->d_stats_part, 64 + (size_t)blocks * 16);
+    CHK_CUDA(cudaMemcpyAsync(c->d_stats_desc.p, d.data(), N * sizeof(StatsDesc), cudaMemcpyHostToDevice, s));
+    CHK_CUDA(cudaMemcpyAsync(c->d_tiles.p, tiles_before.data(), (N + 1) * 4, cudaMemcpyHostToDevice, s));
+    CHK_CUDA(cudaMemsetAsync(c->d_symkeys.p, 0, capacity * 8, s));
+    CHK_CUDA(cudaMemsetAsync(c->d_symcounts.p, 0, capacity * 4, s));
+    CHK_CUDA(cudaMemsetAsync(c->d_stats_part.p, 0, 64, s));
+    auto* keys = static_cast<unsigned long long*>(c->d_symkeys.p);
+    auto* counts = static_cast<uint32_t*>(c->d_symcounts.p);
+    auto* head = static_cast<unsigned long long*>(c->d_stats_part.p);  // [0] vocabulary, [1] best, [2] overflow
+    auto* partial = reinterpret_cast<double*>(head + 8);
+    CHK_CUDA(cudaEventRecord(c->ev[0], s));
+    symbol_count_kernel<<<(uint32_t)(tiles < blocks ? tiles : blocks), 256, 0, s>>>(
+        static_cast<const StatsDesc*>(c->d_stats_desc.p), static_cast<const uint32_t*>(c->d_tiles.p), (uint32_t)N,
+        (uint32_t)tiles, keys, counts, (uint32_t)(capacity - 1), reinterpret_cast<uint32_t*>(head + 2));
+    model_scan_kernel<<<blocks, 256, 0, s>>>(keys, counts, (uint32_t)capacity, head);
+    CHK_CUDA(cudaGetLastError());
+    unsigned long long h[3] = {};
+    CHK_CUDA(cudaMemcpyAsync(h, head, sizeof(h), cudaMemcpyDeviceToHost, s));
+    sync_stream(c, s);
+    if (h[2]) throw Error{CHK_ERR_CAPACITY, "internal: symbol table overflow"};
+    const unsigned long long n_vocab = h[0];
+    const double c_max = (double)(h[1] >> 32);
+    const unsigned long long max_key = kSymUsed | (0xFFFFFFFFull - (h[1] & 0xFFFFFFFFull));
+    // _build_model (:52-75): scale = 2^p > 2 * vocabulary, p >= 14; norm = max(floor(count * scale / total), 1);
+    // the drift goes onto the most frequent symbol
+    int p = 14;
+    {
+        int need = 1;
+        while ((1ull << need) < (n_vocab > 2 ? n_vocab : 2)) ++need;  // ceil(log2(max(n_vocab, 2)))
+        if (need + 1 > p) p = need + 1;
+    }
+    const double scale = std::ldexp(1.0, p);
+    const double factor = scale / (double)symbols;
+    model_cost_kernel<<<blocks, 256, 0, s>>>(keys, counts, (uint32_t)capacity, factor, scale, max_key, partial);
+    CHK_CUDA(cudaGetLastError());
+    CHK_CUDA(cudaEventRecord(c->ev[1], s));
+    std::vector<double> part((size_t)blocks * 2);
+    CHK_CUDA(cudaMemcpyAsync(part.data(), partial, part.size() * 8, cudaMemcpyDeviceToHost, s));
+    sync_stream(c, s);
+    c->launches += 3;
+    double norm_sum = 0.0, bits = 0.0;
+    for (uint32_t b = 0; b < blocks; ++b) {
+        norm_sum += part[2 * b];
+        bits += part[2 * b + 1];
+    }
+    double norm_max = std::floor(c_max * factor);
+    if (norm_max < 1.0) norm_max = 1.0;
+    norm_max += scale - (norm_sum + norm_max);
+    if (norm_max < 1.0) norm_max = 1.0;
+    bits += c_max * std::log2(scale / norm_max);
+    *stream_bytes = bits / 8.0;
+    *vocab = n_vocab;
+    c->timing["model_cost_ms"] = ms_between(c->ev[0], c->ev[1]);
+}
+
 // Cardinality estimate of one sketch: alpha m^2 / sum 2^-register with the small- and large-range corrections
 // (scripts/llama-3-8b/experiment_2.py:71-82).  The sum is formed over the 19 possible register values, which is
 // exact in double, as is numpy's pairwise sum of the same powers of two.
@@ -1273,7 +1362,7 @@ static void release_device_buffers(chk_context* c) {
     if (c->side_stream) cudaStreamSynchronize(c->side_stream);
     DevBuf* bufs[] = {&c->d_descs, &c->d_tiles, &c->d_hist, &c->d_sidecar, &c->d_scratch, &c->d_hdrs,
                       &c->d_order, &c->d_ticket, &c->d_psize, &c->d_zslots, &c->d_zregions, &c->d_zslot_of, &c->d_jobs, &c->d_sums, &c->d_payload, &c->d_enc,
-                      &c->d_freq, &c->d_cum, &c->d_status, &c->d_stats_desc, &c->d_stats_out, &c->d_stats_part, &c->d_stats_mid, &c->d_poff, &c->d_fileorder, &c->d_hll32, &c->d_hll8};
+                      &c->d_freq, &c->d_cum, &c->d_status, &c->d_stats_desc, &c->d_stats_out, &c->d_stats_part, &c->d_stats_mid, &c->d_poff, &c->d_fileorder, &c->d_hll32, &c->d_hll8, &c->d_symkeys, &c->d_symcounts};
     for (DevBuf* b : bufs) {
         if (b->p) cudaFreeAsync(b->p, c->stream);
         b->p = nullptr;
@@ -1400,6 +1489,13 @@ int chk_analyze(chk_context* c) {
     CHK_API_BEGIN
     CHK_REQUIRE(c, "context is NULL");
     analyze(c);
+    CHK_API_END
+}
+
+int chk_shared_model_cost(chk_context* c, const uint64_t* index, uint64_t n, double* stream_bytes, uint64_t* vocabulary) {
+    CHK_API_BEGIN
+    CHK_REQUIRE(c && (index || n == 0) && stream_bytes && vocabulary, "NULL argument");
+    shared_model_cost(c, index, (size_t)n, stream_bytes, vocabulary);
     CHK_API_END
 }
 

@@ -124,6 +124,12 @@ int chk_hll_get(chk_context* ctx, uint64_t index, uint8_t regs[16384]);
 int chk_hll_merge(uint8_t acc[16384], const uint8_t other[16384]);
 int chk_hll_count(const uint8_t regs[16384], double* estimate);
 int chk_shared_vocabulary_report(chk_context* ctx, uint64_t* per_tensor_bytes, uint64_t* shared_bytes);
+/* The reference's second study (scripts/llama-3-8b/experiment_2_1.py:52-75, 217-330): the registered tensors
+ * index[0..n) coded under ONE model over their 32-bit symbols -- counts quantised to a power-of-two scale, every
+ * occurrence costs log2(scale / norm[symbol]) bits.  Returns the stream bytes and the size of the shared
+ * vocabulary (the model costs 8 bytes per entry); a group of one tensor gives the tensor's own-model figures. */
+int chk_shared_model_cost(chk_context* ctx, const uint64_t* index, uint64_t n, double* stream_bytes,
+                          uint64_t* vocabulary);
 /* cluster_id[i] for every registered tensor (-1 = singleton); *n_clusters out. */
 int chk_get_cluster_ids(chk_context* ctx, int32_t* cluster_id, uint64_t capacity, int32_t* n_clusters);
 int chk_get_cluster_anchor(chk_context* ctx, int32_t cluster, char name_out[256]);

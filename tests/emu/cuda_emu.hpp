@@ -245,6 +245,11 @@ static inline unsigned atomicOr(unsigned* p, unsigned v) {
     *p = old | v;
     return old;
 }
+static inline unsigned long long atomicMax(unsigned long long* p, unsigned long long v) {
+    unsigned long long old = *p;
+    *p = std::max(old, v);
+    return old;
+}
 static inline unsigned atomicMax(unsigned* p, unsigned v) {
     unsigned old = *p;
     *p = std::max(old, v);

@@ -340,6 +340,42 @@ void emu_hll(size_t n, const void* const* ptrs, const uint64_t* n_elem, const ui
     emu::launch(grid, 256, kHllRegs * 4, [&] { hll_sketch_kernel(d.data(), tile_start.data(), (uint32_t)n, tiles, regs_out); });
 }
 
+// shared-model cost: the three kernels over n tensors; out = {vocabulary, packed best, overflow, norm sum, bits}
+void emu_model_cost(size_t n, const void* const* ptrs, const uint64_t* n_elem, const uint32_t* dtype, uint32_t capacity,
+                    double factor_scale_log2, uint32_t grid, double* out) {
+    std::vector<StatsDesc> d(n);
+    std::vector<uint32_t> tile_start(n + 1);
+    uint32_t tiles = 0;
+    uint64_t symbols = 0;
+    for (size_t i = 0; i < n; ++i) {
+        d[i] = StatsDesc{ptrs[i], n_elem[i], dtype[i], 0};
+        tile_start[i] = tiles;
+        tiles += (uint32_t)((n_elem[i] * stats_elem_size(dtype[i]) + kHllTileBytes - 1) / kHllTileBytes);
+        symbols += n_elem[i];
+    }
+    tile_start[n] = tiles;
+    std::vector<unsigned long long> keys(capacity, 0), head(8, 0);
+    std::vector<uint32_t> counts(capacity, 0);
+    uint32_t g1 = grid > tiles ? tiles : grid;
+    emu::launch(g1, 256, 0, [&] {
+        symbol_count_kernel(d.data(), tile_start.data(), (uint32_t)n, tiles, keys.data(), counts.data(), capacity - 1,
+                            (uint32_t*)&head[2]);
+    });
+    emu::launch(grid, 256, 0, [&] { model_scan_kernel(keys.data(), counts.data(), capacity, head.data()); });
+    const double scale = std::ldexp(1.0, (int)factor_scale_log2), factor = scale / (double)symbols;
+    const unsigned long long max_key = kSymUsed | (0xFFFFFFFFull - (head[1] & 0xFFFFFFFFull));
+    std::vector<double> partial(2 * grid, 0.0);
+    emu::launch(grid, 256, 0, [&] { model_cost_kernel(keys.data(), counts.data(), capacity, factor, scale, max_key, partial.data()); });
+    out[0] = (double)head[0];
+    out[1] = (double)(head[1] >> 32);
+    out[2] = (double)(uint32_t)head[2];
+    out[3] = out[4] = 0.0;
+    for (uint32_t b = 0; b < grid; ++b) {
+        out[3] += partial[2 * b];
+        out[4] += partial[2 * b + 1];
+    }
+}
+
 // the host routine the device kernel must agree with
 void emu_host_enc_entries(const uint32_t* nf, const uint32_t* cf, uint32_t* enc_out) {
     FreqTable ft;

@@ -155,6 +155,15 @@ class Emu:
         self.lib.emu_planes(C.c_size_t(n), ptrs, _p(ne, u64p), _p(e, u32p), _p(sp, u32p), _p(lo, u64p), _p(po, u64p),
                             _p(st, u64p), _p(low), _p(planes), C.c_uint32(grid), C.c_uint32(int(merge)))
 
+    def model_cost(self, tensors, n_elem, dtypes, capacity, scale_log2, grid=4):
+        """vocabulary, largest count, overflow, sum of the quantised counts and bits without the most frequent symbol"""
+        n, ptrs = self._arrays(tensors)
+        ne, dt = np.array(n_elem, np.uint64), np.array(dtypes, np.uint32)
+        out = np.zeros(5, np.float64)
+        self.lib.emu_model_cost(C.c_size_t(n), ptrs, _p(ne, u64p), _p(dt, u32p), C.c_uint32(capacity),
+                                C.c_double(scale_log2), C.c_uint32(grid), _p(out, C.POINTER(C.c_double)))
+        return out
+
     def hll(self, tensors, n_elem, dtypes, grid=3):
         n, ptrs = self._arrays(tensors)
         ne, dt = np.array(n_elem, np.uint64), np.array(dtypes, np.uint32)
