@@ -70,6 +70,7 @@ def _load():
         "chk_kernel_launches": (C.c_int, [vp, C.POINTER(u64)]),
         "chk_get_stream": (C.c_int, [vp, C.POINTER(vp)]),
         "chk_stream_create": (C.c_int, [C.c_int, C.c_int, u64, C.c_int, C.POINTER(vp)]),
+        "chk_stream_set_option": (C.c_int, [vp, C.c_char_p, C.c_int64]),
         "chk_stream_destroy": (C.c_int, [vp]),
         "chk_stream_add_tensor": (C.c_int, [vp, C.c_char_p, vp, u64, C.c_uint8]),
         "chk_stream_compress": (C.c_int, [vp]),

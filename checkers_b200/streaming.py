@@ -75,12 +75,16 @@ class ChunkedHostPipeline:
     pipeline.restore(out_tensors)  # decode the parts back into host tensors
     """
 
-    def __init__(self, host_tensors, device=0, rank=0, chunk_bytes=1 << 30, workers=3):
+    def __init__(self, host_tensors, device=0, rank=0, chunk_bytes=1 << 30, workers=3, options=None):
+        """options: library options (as Context.set_option) for every context of the pipeline, e.g.
+        {"format_version": 3}."""
         self.tensors = list(host_tensors)
         self.device, self.rank = int(device), int(rank)
         self._h = C.c_void_p()
         check(lib.chk_stream_create(self.device, self.rank, int(chunk_bytes), max(1, min(int(workers), 8)),
                                     C.byref(self._h)))
+        for key, value in (options or {}).items():
+            check(lib.chk_stream_set_option(self._h, str(key).encode(), int(value)))
         for t in self.tensors:
             check(lib.chk_stream_add_tensor(self._h, t.name.encode(), C.c_void_p(t.tensor.data_ptr()), t.numel, t.dtype))
         n = C.c_uint64()

@@ -244,6 +244,9 @@ int chk_repair_apply(int device, const void* h_raw, uint64_t numel, uint32_t sto
  * restore_kernel_ms, restore_d2h_ms, restore_wall_ms. */
 typedef struct chk_stream chk_stream;
 int chk_stream_create(int device, int rank, uint64_t chunk_bytes, int slots, chk_stream** out);
+/* An option of chk_set_option for every context the pipeline uses (e.g. "format_version" = 3); before the first
+ * compress or load. */
+int chk_stream_set_option(chk_stream* s, const char* key, int64_t value);
 int chk_stream_destroy(chk_stream* s);
 int chk_stream_add_tensor(chk_stream* s, const char* name, void* host_ptr, uint64_t num_elements, uint8_t dtype);
 int chk_stream_compress(chk_stream* s);

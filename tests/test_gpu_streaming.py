@@ -62,3 +62,46 @@ def test_parts_match_oracle_and_round_trip(oracle, tmp_path, workers):
     for o, h, t in zip(outs, host, tensors):
         assert np.array_equal(o.numpy(), h), t.name
     pipe.close()
+
+
+def test_pipeline_with_container_version3(tmp_path):
+    """The host pipeline with every context set to container version 3: smaller parts, lossless through memory
+    and through files."""
+    torch = pytest.importorskip("torch")
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from checkers_b200.streaming import ChunkedHostPipeline, HostTensor
+    from oracle_lib import synth
+    tensors, outs = [], []
+    for i in range(24):
+        kind = ("bf16_weight", "f32_master", "f32_exp_avg", "f32_exp_avg_sq_lognormal")[i % 4]
+        # a few large tensors: their copy to the device takes milliseconds, and the kernels must wait for it
+        raw, dt = synth(kind, (3 << 20) + 5 if i in (1, 2, 9) else 100000 + 17 * i, 500 + i)
+        t = torch.from_numpy(raw.copy()).pin_memory()
+        tensors.append(HostTensor(f"optimizer.exp_avg::w.{i}" if i % 4 == 2 else f"w.{i}", t, dt))
+        outs.append(torch.zeros_like(t).pin_memory())
+    sizes = {}
+    for version in (2, 3):
+        pipe = ChunkedHostPipeline(tensors, device=0, rank=0, chunk_bytes=2 << 20, workers=3,
+                                   options={"format_version": version})
+        pipe.compress()
+        s = pipe.summary()
+        sizes[version] = s["states_bytes"] + s["mantissa_bytes"]
+        for o in outs:
+            o.zero_()
+        pipe.restore(outs)
+        for t, o in zip(tensors, outs):
+            assert torch.equal(t.tensor, o), (version, t.name)
+        d = str(tmp_path / f"v{version}")
+        pipe.save(d)
+        pipe.close()
+        again = ChunkedHostPipeline(tensors, device=0, rank=0, chunk_bytes=2 << 20, workers=2,
+                                    options={"format_version": version})
+        again.load(d)
+        for o in outs:
+            o.zero_()
+        again.restore(outs)
+        for t, o in zip(tensors, outs):
+            assert torch.equal(t.tensor, o), (version, t.name, "from files")
+        again.close()
+    assert sizes[3] < 0.93 * sizes[2]
