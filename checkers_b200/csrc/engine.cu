@@ -120,6 +120,7 @@ struct Context {
 
     bool repair_tables = false, verify_zero_lanes = false, allow_undecodable = false;
     bool fast_stats = false;      // statistics with order-free sums over the whole device (see stats_kernels.cuh)
+    bool precounted = false;      // the caller filled d_hist (one row per work item) itself: compress() does not count
     int format_version = 2;       // 2: the reference's container; 3: byte planes with a table each (format_v3.inc)
     uint32_t file_version[3] = {kStatesVersion, kMantVersion, kDictVersion};  // written to and expected in the headers
     struct V3State* v3 = nullptr;
@@ -477,7 +478,7 @@ static void compress(Context* c, bool host_images) {
     // ---- pieces the batch is counted in (equal bytes; a small batch is one piece).  The tables of a piece are
     // built while the next piece is counted, so a piece must take about as long to count as the tables of the
     // one before take to build: a small last piece (1/16 of the bytes) exposed more table time, not less.
-    const size_t n_seg = W >= 512 ? (size_t)c->segments : 1;
+    const size_t n_seg = W >= 512 && !c->precounted ? (size_t)c->segments : 1;
     std::vector<size_t> seg_end;
     {
         unsigned long long acc = 0;
@@ -545,7 +546,7 @@ static void compress(Context* c, bool host_images) {
     control_copy(c, c->d_tiles.p, c->h_tiles.p, (W + 1) * 4, s);
     control_copy(c, c->d_jobs.p, c->h_jobs.p, T * sizeof(TableJob), s);
     control_copy(c, c->d_order.p, c->h_order.p, W * 4, s);
-    control_zero(c, c->d_hist.p, W * 1024, s);
+    if (!c->precounted) control_zero(c, c->d_hist.p, W * 1024, s);
     control_zero(c, c->d_ticket.p, 256, s);  // word 0: ticket counter; words 2-3: the 64-bit heap cursor
     control_zero(c, c->d_zslots.p, z_slots * sizeof(ZeroSlot), s);
 
@@ -555,12 +556,14 @@ static void compress(Context* c, bool host_images) {
         const size_t b = seg_end[g], n = b - a;
         const uint32_t tiles = tile_start[b] - tile_start[a];
         const uint32_t grid1 = tiles < sms * 8u ? tiles : sms * 8u;
-        split_hist_kernel<<<grid1, 256, 0, s>>>(static_cast<const TensorDesc*>(c->d_descs.p) + a,
-                                                static_cast<const uint32_t*>(c->d_tiles.p) + a, (uint32_t)n, tile_start[a],
-                                                tiles, static_cast<uint8_t*>(c->d_sidecar.p),
-                                                static_cast<uint32_t*>(c->d_hist.p) + a * 256);
-        CHK_CUDA(cudaGetLastError());
-        c->launches++;
+        if (!c->precounted) {
+            split_hist_kernel<<<grid1, 256, 0, s>>>(static_cast<const TensorDesc*>(c->d_descs.p) + a,
+                                                    static_cast<const uint32_t*>(c->d_tiles.p) + a, (uint32_t)n, tile_start[a],
+                                                    tiles, static_cast<uint8_t*>(c->d_sidecar.p),
+                                                    static_cast<uint32_t*>(c->d_hist.p) + a * 256);
+            CHK_CUDA(cudaGetLastError());
+            c->launches++;
+        }
         CHK_CUDA(cudaEventRecord(c->ev_count[g], s));
         // tables owned inside this piece: table numbers follow the work order, so they are a range
         size_t tab_hi = tab_done;

@@ -321,6 +321,38 @@ void emu_planes(size_t n, void* const* tensors, const uint64_t* n_elem, const ui
         emu::launch(grid, 256, 0, [&] { plane_split_kernel(d.data(), ts.data(), (uint32_t)n, tiles, low, planes); });
 }
 
+// the split that also counts every plane's bytes: hist = 256 counters per plane, planes numbered through the tensors
+void emu_planes_count(size_t n, void* const* tensors, const uint64_t* n_elem, const uint32_t* es, const uint32_t* spe,
+                      const uint64_t* low_off, const uint64_t* plane_off, const uint64_t* stride, uint8_t* low,
+                      uint8_t* planes, uint32_t* hist, uint32_t grid) {
+    std::vector<PlaneDesc> d(n);
+    std::vector<uint32_t> ts(n + 1);
+    uint32_t tiles = 0, row = 0;
+    for (size_t i = 0; i < n; ++i) {
+        d[i] = PlaneDesc{};
+        d[i].tensor = (uint8_t*)tensors[i];
+        d[i].n_elem = n_elem[i];
+        d[i].low_off = low_off[i];
+        d[i].plane_off = plane_off[i];
+        d[i].plane_stride = stride[i];
+        d[i].es = es[i];
+        d[i].spe = spe[i];
+        d[i].vector_ok = ((uintptr_t)tensors[i] & 15) == 0 && (low_off[i] & 15) == 0 && ((uintptr_t)low & 15) == 0 &&
+                         ((uintptr_t)planes & 15) == 0;
+        d[i].hist_row = row;
+        row += es[i] - spe[i];
+        ts[i] = tiles;
+        tiles += (uint32_t)((n_elem[i] * es[i] + kPlaneTileBytes - 1) / kPlaneTileBytes);
+    }
+    ts[n] = tiles;
+    std::memset(hist, 0, (size_t)row * 1024);
+    if (!tiles) return;
+    if (grid > tiles) grid = tiles;
+    emu::launch(grid, 256, kPlaneCountSmem, [&] {
+        plane_split_count_kernel(d.data(), ts.data(), (uint32_t)n, tiles, low, planes, hist);
+    });
+}
+
 // HyperLogLog sketches of n tensors: regs_out n x 16384 words
 void emu_hll(size_t n, const void* const* ptrs, const uint64_t* n_elem, const uint32_t* dtype, uint32_t* regs_out,
              uint32_t grid) {

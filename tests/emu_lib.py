@@ -155,6 +155,16 @@ class Emu:
         self.lib.emu_planes(C.c_size_t(n), ptrs, _p(ne, u64p), _p(e, u32p), _p(sp, u32p), _p(lo, u64p), _p(po, u64p),
                             _p(st, u64p), _p(low), _p(planes), C.c_uint32(grid), C.c_uint32(int(merge)))
 
+    def planes_count(self, tensors, n_elem, es, spe, low_off, plane_off, stride, low, planes, grid=3):
+        n, ptrs = self._arrays(tensors)
+        a = lambda x, t: np.array(x, t)
+        ne, e, sp = a(n_elem, np.uint64), a(es, np.uint32), a(spe, np.uint32)
+        lo, po, st = a(low_off, np.uint64), a(plane_off, np.uint64), a(stride, np.uint64)
+        hist = np.zeros((int(sum(x - y for x, y in zip(es, spe))), 256), np.uint32)
+        self.lib.emu_planes_count(C.c_size_t(n), ptrs, _p(ne, u64p), _p(e, u32p), _p(sp, u32p), _p(lo, u64p), _p(po, u64p),
+                                  _p(st, u64p), _p(low), _p(planes), _p(hist, u32p), C.c_uint32(grid))
+        return hist
+
     def model_cost(self, tensors, n_elem, dtypes, capacity, scale_log2, grid=4):
         """vocabulary, largest count, overflow, sum of the quantised counts and bits without the most frequent symbol"""
         n, ptrs = self._arrays(tensors)

@@ -206,6 +206,18 @@ def test_plane_split_and_merge(emu, misalign):
             assert np.array_equal(planes[p0:p0 + n_elem[i]], m[:, spe[i] + k]), (i, k)
             assert np.all(planes[p0 + n_elem[i]:p0 + stride[i]] == 0xBB), (i, k)
     assert np.all(low[lo:] == 0xAA)
+    # the same split with the planes' byte histograms counted in the pass
+    low2, planes2 = aligned(lo + 64), aligned(po + 64)
+    hist = emu.planes_count(tensors, n_elem, es, spe, low_off, plane_off, stride, low2, planes2, grid=4)
+    assert np.array_equal(low2[:lo], low[:lo])
+    row = 0
+    for i, a in enumerate(tensors):
+        m = a.reshape(n_elem[i], es[i])
+        for k in range(es[i] - spe[i]):
+            p0 = plane_off[i] + k * stride[i]
+            assert np.array_equal(planes2[p0:p0 + n_elem[i]], m[:, spe[i] + k]), (i, k)
+            assert np.array_equal(hist[row], np.bincount(m[:, spe[i] + k], minlength=256)), (i, k)
+            row += 1
     outs = []
     for a in tensors:
         off = (a.ctypes.data & 15)
