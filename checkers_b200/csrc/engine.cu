@@ -121,6 +121,10 @@ struct Context {
     bool repair_tables = false, verify_zero_lanes = false, allow_undecodable = false;
     bool fast_stats = false;      // statistics with order-free sums over the whole device (see stats_kernels.cuh)
     bool precounted = false;      // the caller filled d_hist (one row per work item) itself: compress() does not count
+    bool v3_fused_decode = true;  // container version 3: decode planes straight into whole elements (no merge pass)
+    bool skip_decode = false;     // decompress_images stops after parsing and uploading: the caller decodes (format_v3.inc)
+    std::vector<TensorDesc> last_run;       // with skip_decode: the parsed entries, in upload order (lane headers k at k * 4096)
+    std::vector<size_t> last_run_tensor;    // and the registry index of each
     int format_version = 2;       // 2: the reference's container; 3: byte planes with a table each (format_v3.inc)
     uint32_t file_version[3] = {kStatesVersion, kMantVersion, kDictVersion};  // written to and expected in the headers
     struct V3State* v3 = nullptr;
@@ -905,6 +909,8 @@ static void decompress_resident(Context* c, void* const* dst) {
 static void decompress_images(Context* c, const uint8_t* st, size_t st_n, const uint8_t* mt, size_t mt_n,
                               const uint8_t* dc, size_t dc_n) {
     if (c->format_version == 3) return v3_decompress_images(c, st, st_n, mt, mt_n, dc, dc_n);
+    c->last_run.clear();
+    c->last_run_tensor.clear();
     const auto t_total = std::chrono::steady_clock::now();
     CHK_CUDA(cudaSetDevice(c->device));
     c->restored = 0;
@@ -1026,6 +1032,11 @@ static void decompress_images(Context* c, const uint8_t* st, size_t st_n, const 
     if (payload_total) CHK_CUDA(cudaMemcpyAsync(c->d_payload.p, st + st_data, payload_total, cudaMemcpyHostToDevice, s));
     if (sidecar_total) CHK_CUDA(cudaMemcpyAsync(c->d_sidecar.p, mt + mt_data, sidecar_total, cudaMemcpyHostToDevice, s));
     CHK_CUDA(cudaEventRecord(c->ev[3], s));
+    if (c->skip_decode) {
+        c->last_run = run;
+        c->last_run_tensor = tensor_of;
+        return;
+    }
     run_decode(c, W, static_cast<const uint8_t*>(c->d_payload.p), static_cast<const uint8_t*>(c->d_sidecar.p),
                static_cast<const uint32_t*>(c->d_freq.p), static_cast<const uint32_t*>(c->d_cum.p),
                static_cast<const LaneHeader*>(c->d_hdrs.p), tensor_of);
@@ -1460,6 +1471,8 @@ int chk_set_option(chk_context* c, const char* key, int64_t value) {
         c->verify_zero_lanes = value != 0;
     else if (k == "fast_stats")
         c->fast_stats = value != 0;
+    else if (k == "v3_fused_decode")
+        c->v3_fused_decode = value != 0;
     else if (k == "format_version") {
         if (value != 2 && value != 3) throw chk::Error{CHK_ERR_INVALID, "format_version must be 2 or 3"};
         if (c->format_version != (int)value) c->have_resident = c->have_images = false;

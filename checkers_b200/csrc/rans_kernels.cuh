@@ -17,6 +17,8 @@
 // scheduler instruction-level parallelism across the serial state updates.
 #pragma once
 
+#include <type_traits>
+
 namespace chk {
 
 constexpr uint32_t kTeam = 64;  // threads per tensor
@@ -1219,6 +1221,250 @@ __global__ void __launch_bounds__(kTeam, ZS ? CHK_DEC_ZS_MINBLOCKS : CHK_DEC_MIN
             decode_tensor<4, 0, ZS>(d, ti, freq_tables, cum_tables, hdrs, payload, sidecar, check_zero_lanes, status, smem);
         else
             __syncthreads();
+    }
+}
+
+}  // namespace chk
+
+// ------------------------------------------------------------------ container version 3: planes -> whole elements
+// A floating-point tensor of container version 3 is stored as one 8-bit stream per high byte plane plus raw low
+// bytes (plane_kernels.cuh).  rans_decode_planes_kernel restores it without writing the planes to memory.  A team
+// has 64 threads per plane (kPlanes = 2: 4-byte elements, 1: 2-byte elements); a thread decodes four
+// neighbouring lanes 4c..4c+3 of its plane exactly as the 8-bit path of rans_decode_kernel does.  With two planes
+// the threads of a warp are split 16 + 16: lane l and lane l + 16 hold the two high bytes of the SAME four
+// elements, swap their words with one shuffle per row, and each writes two whole elements (its own low bytes,
+// both high bytes) -- no barrier and no shared-memory staging inside the loop, stores coalesced.  A plane
+// stored raw (passthrough rule) is read instead of decoded.
+namespace chk {
+
+struct PlaneItem {                  // one stored plane
+    unsigned long long payload_off; // start of its payload in the payload section
+    uint32_t hdr_index;             // its lane headers are hdrs[hdr_index * 256 ...]
+    uint32_t table_idx;
+    uint32_t raw;                   // payload is the plane itself
+    uint32_t status_index;          // where a failed stream check is recorded
+};
+struct PlaneGroup {                 // one tensor
+    uint8_t* dst;
+    const uint8_t* low;             // its low bytes (n * spe)
+    unsigned long long n_elem;
+    PlaneItem plane[2];             // [0] the lower plane, [kPlanes - 1] the sign/exponent plane
+};
+
+template <int kPlanes>
+struct PlaneDecSmem {
+    uint32_t dtab[kPlanes][kM];
+    uint32_t ring[4 * kPlanes * kTeam * kRingWords];  // per chain index and warp: 17 words x 32 lanes, interleaved
+    uint32_t cum[kPlanes][260];
+};
+
+template <int kPlanes>
+__device__ __forceinline__ void decode_plane_group(const PlaneGroup& g, const uint32_t* __restrict__ cum_tables,
+                                                   const LaneHeader* __restrict__ hdrs,
+                                                   const uint8_t* __restrict__ payload, uint32_t* __restrict__ status,
+                                                   unsigned char* smem_raw) {
+    constexpr uint32_t kThreads = kPlanes * kTeam;
+    constexpr uint32_t kWarps = kThreads / 32;
+    constexpr uint32_t ES = kPlanes * 2;         // element size: low bytes and high bytes are half each
+    PlaneDecSmem<kPlanes>* sm = reinterpret_cast<PlaneDecSmem<kPlanes>*>(smem_raw);
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // plane of this thread and its column c: it decodes lanes 4c .. 4c+3 of that plane
+    const uint32_t h = kPlanes == 2 ? lane >> 4 : 0u;
+    const uint32_t c = kPlanes == 2 ? (warp << 4) | (lane & 15u) : tid;
+    const PlaneItem it = g.plane[h];
+    const unsigned long long B = g.n_elem;       // bytes of a plane
+
+    // ---- the slot tables (threads t, t + kThreads, ... of the team build both)
+    for (uint32_t p = 0; p < (uint32_t)kPlanes; ++p) {
+        if (g.plane[p].raw) continue;
+        const uint32_t* cq = cum_tables + (size_t)g.plane[p].table_idx * 257;
+        for (uint32_t i = tid; i < 257; i += kThreads) sm->cum[p][i] = cq[i];
+    }
+    __syncthreads();
+    for (uint32_t p = 0; p < (uint32_t)kPlanes; ++p) {
+        if (g.plane[p].raw) continue;
+        for (uint32_t slot = tid; slot < kM; slot += kThreads) {
+            uint32_t lo = 0, hi = 256;  // last s with cum[s] <= slot
+            while (hi - lo > 1) {
+                const uint32_t mid = (lo + hi) >> 1;
+                if (sm->cum[p][mid] <= slot) lo = mid; else hi = mid;
+            }
+            sm->dtab[p][slot] = lo | ((sm->cum[p][lo + 1] - sm->cum[p][lo] - 1) << 8) | ((slot - sm->cum[p][lo]) << 20);
+        }
+    }
+
+    DecChain ch[4];
+    uint32_t* ringw[4];
+    const uint8_t* ringb[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const uint32_t t = 4 * c + k;
+        LaneHeader lh{kL, 0, 0, 0};
+        if (!it.raw) lh = hdrs[(size_t)it.hdr_index * kLanes + t];
+        const unsigned long long p_abs = it.payload_off + lh.buf_offset;
+        ch[k].x = lh.final_state;
+        ch[k].blk0 = p_abs >> 5;
+        ch[k].rel = (uint32_t)(p_abs & 31);
+        ch[k].rel_end = ch[k].rel + lh.byte_count;
+        ch[k].max_blocks = ((ch[k].rel_end + 31) >> 5) + 1;
+        ch[k].loaded = 0;
+        ch[k].has_pend = false;
+        ringw[k] = sm->ring + (size_t)(k * kWarps + warp) * (kRingWords * 32) + lane;
+        ringb[k] = reinterpret_cast<const uint8_t*>(ringw[k]);
+        if (!it.raw && B > t) {
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                dec_request(ch[k], payload);
+                dec_commit(ch[k], ringw[k]);
+            }
+        }
+    }
+    __syncthreads();  // tables complete
+
+    const unsigned long long full_rows = B >> 8;
+    const uint32_t tail = (uint32_t)(B & 255);
+    const uint32_t* const dtab = sm->dtab[h];
+    const uint8_t* raw_col = payload + it.payload_off + 4 * c;  // a raw plane: the thread's word of every row
+    const bool raw4 = (reinterpret_cast<uintptr_t>(raw_col) & 3) == 0;
+    const bool dst_ok = (reinterpret_cast<uintptr_t>(g.dst) & 7) == 0, low_ok = (reinterpret_cast<uintptr_t>(g.low) & 3) == 0;
+    // the elements this thread writes in a row: two planes -> 4c + 2h, 4c + 2h + 1; one plane -> 4c .. 4c + 3
+    const uint32_t e0 = kPlanes == 2 ? 4 * c + 2 * h : 4 * c;
+
+    // the four bytes of this thread's plane in row r (kRaw: the plane may be a stored-raw one)
+    auto row_word = [&](unsigned long long r, auto may_be_raw) -> uint32_t {
+        if (decltype(may_be_raw)::value && it.raw) return load_row_word(raw_col + (r << 8), raw4);
+        uint32_t acc = 0;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) acc = put_byte(acc, dec_step<false>(ch[k], dtab, 0, ringb[k]), k);
+        return acc;
+    };
+    // the low bytes of the thread's elements in row r: four bytes either way
+    auto low_word = [&](unsigned long long r) -> uint32_t {
+        const uint8_t* lp = g.low + ((r << 8) + e0) * (ES / 2);
+        return low_ok ? *reinterpret_cast<const uint32_t*>(lp)
+                      : ((uint32_t)lp[0] | ((uint32_t)lp[1] << 8) | ((uint32_t)lp[2] << 16) | ((uint32_t)lp[3] << 24));
+    };
+    // whole elements of row r from the thread's plane word, its partner's, and the low bytes: 8 bytes
+    auto assemble = [&](uint32_t w, uint32_t lw) -> uint2 {
+        uint2 o;
+        if (kPlanes == 2) {
+            const uint32_t pw = __shfl_xor_sync(0xffffffffu, w, 16);
+            const uint32_t p2 = h ? pw : w, p3 = h ? w : pw;            // the lower and the upper high byte
+            const uint32_t a = h ? p2 >> 16 : p2, b = h ? p3 >> 16 : p3;  // this thread's two elements
+            o.x = (lw & 0xFFFFu) | ((a & 0xFFu) << 16) | ((b & 0xFFu) << 24);
+            o.y = (lw >> 16) | (((a >> 8) & 0xFFu) << 16) | (((b >> 8) & 0xFFu) << 24);
+        } else {
+            o.x = __byte_perm(lw, w, 0x5140);
+            o.y = __byte_perm(lw, w, 0x7362);
+        }
+        return o;
+    };
+    auto store_row = [&](unsigned long long r, uint2 o) {
+        uint8_t* dp = g.dst + ((r << 8) + e0) * ES;
+        if (dst_ok) {
+            *reinterpret_cast<uint2*>(dp) = o;
+        } else {
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                dp[b] = (uint8_t)(o.x >> (8 * b));
+                dp[4 + b] = (uint8_t)(o.y >> (8 * b));
+            }
+        }
+    };
+
+    unsigned long long r = 0;
+    // groups of 8 rows; the loop exists twice so that a team without a raw plane carries no test for one
+    auto groups_of_8 = [&](auto may_be_raw) {
+        uint32_t lw_next[8];
+        if (8 <= full_rows) {
+#pragma unroll
+            for (int u = 0; u < 8; ++u) lw_next[u] = low_word(u);
+        }
+        while (r + 8 <= full_rows) {
+            uint32_t lw[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) lw[u] = lw_next[u];
+            if (r + 16 <= full_rows) {  // low bytes of the next group, requested ahead of use
+#pragma unroll
+                for (int u = 0; u < 8; ++u) lw_next[u] = low_word(r + 8 + u);
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) store_row(r + u, assemble(row_word(r + u, may_be_raw), lw[u]));
+            if (!(decltype(may_be_raw)::value && it.raw)) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    dec_commit(ch[k], ringw[k]);
+                    if (ch[k].rel >= (ch[k].loaded - 1) * 32) dec_request(ch[k], payload);
+                }
+            }
+            r += 8;
+        }
+    };
+    bool any_raw = false;
+    for (uint32_t p = 0; p < (uint32_t)kPlanes; ++p) any_raw = any_raw || g.plane[p].raw;
+    if (any_raw) groups_of_8(std::true_type{}); else groups_of_8(std::false_type{});
+    if (!it.raw) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) dec_commit(ch[k], ringw[k]);
+    }
+    // remaining full rows (at most 7)
+    for (; r < full_rows; ++r) store_row(r, assemble(row_word(r, std::true_type{}), low_word(r)));
+    // the partial row: elements r*256 .. r*256 + tail, byte by byte
+    if (tail) {
+        uint32_t acc = 0;
+        if (it.raw) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                if (4 * c + k < tail) acc |= (uint32_t)payload[it.payload_off + (r << 8) + 4 * c + k] << (8 * k);
+        } else {
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                if (4 * c + k < tail) acc = put_byte(acc, dec_step<false>(ch[k], dtab, 0, ringb[k]), k);
+        }
+        uint32_t p2 = acc, p3 = 0;  // one plane: its bytes 0..3 belong to elements 4c..4c+3
+        if (kPlanes == 2) {
+            const uint32_t pw = __shfl_xor_sync(0xffffffffu, acc, 16);
+            p2 = h ? pw >> 16 : acc;  // bytes 0, 1: the thread's two elements
+            p3 = h ? acc >> 16 : pw;
+        }
+        const uint32_t mine = kPlanes == 2 ? 2u : 4u;
+        for (uint32_t q = 0; q < mine; ++q) {
+            const uint32_t e = e0 + q;
+            if (e >= tail) break;
+            const unsigned long long ge = (r << 8) + e;
+            uint8_t* dp = g.dst + ge * ES;
+            for (uint32_t b = 0; b < ES / 2; ++b) dp[b] = g.low[ge * (ES / 2) + b];
+            dp[ES / 2] = (uint8_t)(p2 >> (8 * q));
+            if (kPlanes == 2) dp[ES / 2 + 1] = (uint8_t)(p3 >> (8 * q));
+        }
+    }
+
+    if (!it.raw) {
+        uint32_t err = 0;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            if (ch[k].x != kL) err |= kErrEndState;
+            if (ch[k].rel != ch[k].rel_end) err |= kErrEndPointer;
+        }
+        if (err) atomicOr(&status[it.status_index], err);
+    }
+    __syncthreads();  // tables and rings are reused by the next tensor
+}
+
+template <int kPlanes>
+__global__ void __launch_bounds__(kPlanes * kTeam, kPlanes == 2 ? 3 : 6) rans_decode_planes_kernel(const PlaneGroup* __restrict__ groups,
+                                                                            const uint32_t* __restrict__ cum_tables,
+                                                                            const LaneHeader* __restrict__ hdrs,
+                                                                            const uint8_t* __restrict__ payload,
+                                                                            const uint32_t* __restrict__ order,
+                                                                            uint32_t* __restrict__ ticket, uint32_t n_groups,
+                                                                            uint32_t* __restrict__ status) {
+    CHK_DYN_SMEM(smem);
+    CHK_SHARED uint32_t s_ticket;
+    for (;;) {
+        const uint32_t tk = next_ticket(ticket, &s_ticket);
+        if (tk >= n_groups) break;
+        decode_plane_group<kPlanes>(groups[order[tk]], cum_tables, hdrs, payload, status, smem);
     }
 }
 

@@ -104,7 +104,9 @@ int chk_tensor_count(chk_context* ctx, uint64_t* count);
  * floating-point element becomes a byte plane that is coded as an 8-bit tensor of its
  * own ("<name>#b<byte>") with its own table, by the same coder; low bytes stay raw.
  * The three files keep their layouts and carry version 3 in their headers; a context
- * reads only the version it is set to.  Cluster-shared tables are not used. */
+ * reads only the version it is set to.  Cluster-shared tables are not used.
+ * "v3_fused_decode" (0/1, default 1): version-3 restore of float-only state decodes the planes straight into
+ * whole elements; 0 = planes to memory, then a merge pass (the route state with integer tensors always takes). */
 int chk_set_option(chk_context* ctx, const char* key, int64_t value);
 
 /* ---- analysis: checkers::analyze_tensors, src/api.cpp:1033-1253 ----------

@@ -408,6 +408,36 @@ void emu_model_cost(size_t n, const void* const* ptrs, const uint64_t* n_elem, c
     }
 }
 
+// container version 3 restore without a merge pass: n groups of `planes` planes each (1: 2-byte elements, 2: 4-byte)
+// item arrays are indexed [group * planes + plane]
+void emu_decode_planes(size_t n, uint32_t planes, uint8_t* const* dsts, const uint8_t* const* lows, const uint64_t* n_elem,
+                       const uint64_t* payload_off, const uint32_t* raw, const uint32_t* cf, const uint32_t* hdrs,
+                       const uint8_t* payload, uint32_t* status_out, uint32_t grid) {
+    std::vector<PlaneGroup> g(n);
+    std::vector<uint32_t> order(n);
+    for (size_t i = 0; i < n; ++i) {
+        g[i] = PlaneGroup{};
+        g[i].dst = dsts[i];
+        g[i].low = lows[i];
+        g[i].n_elem = n_elem[i];
+        for (uint32_t p = 0; p < planes; ++p) {
+            const uint32_t k = (uint32_t)(i * planes + p);
+            g[i].plane[p] = PlaneItem{payload_off[k], k, k, raw[k], k};
+        }
+        order[i] = (uint32_t)(n - 1 - i);
+    }
+    std::memset(status_out, 0, n * planes * 4);
+    uint32_t ticket = 0;
+    if (planes == 2)
+        emu::launch(grid, 2 * kTeam, sizeof(PlaneDecSmem<2>), [&] {
+            rans_decode_planes_kernel<2>(g.data(), cf, (const LaneHeader*)hdrs, payload, order.data(), &ticket, (uint32_t)n, status_out);
+        });
+    else
+        emu::launch(grid, kTeam, sizeof(PlaneDecSmem<1>), [&] {
+            rans_decode_planes_kernel<1>(g.data(), cf, (const LaneHeader*)hdrs, payload, order.data(), &ticket, (uint32_t)n, status_out);
+        });
+}
+
 // the host routine the device kernel must agree with
 void emu_host_enc_entries(const uint32_t* nf, const uint32_t* cf, uint32_t* enc_out) {
     FreqTable ft;

@@ -155,6 +155,19 @@ class Emu:
         self.lib.emu_planes(C.c_size_t(n), ptrs, _p(ne, u64p), _p(e, u32p), _p(sp, u32p), _p(lo, u64p), _p(po, u64p),
                             _p(st, u64p), _p(low), _p(planes), C.c_uint32(grid), C.c_uint32(int(merge)))
 
+    def decode_planes(self, planes, dsts, lows, n_elem, payload_off, raw, cf, hdrs, payload, grid=2):
+        n = len(dsts)
+        dp = (C.c_void_p * n)(*[d.ctypes.data for d in dsts])
+        lp = (C.c_void_p * n)(*[l.ctypes.data for l in lows])
+        ne = np.array(n_elem, np.uint64)
+        po, rw = np.array(payload_off, np.uint64), np.array(raw, np.uint32)
+        cf = np.ascontiguousarray(cf, np.uint32)
+        hdrs = np.ascontiguousarray(hdrs, np.uint32)
+        status = np.zeros(n * planes, np.uint32)
+        self.lib.emu_decode_planes(C.c_size_t(n), C.c_uint32(planes), dp, lp, _p(ne, u64p), _p(po, u64p), _p(rw, u32p),
+                                   _p(cf, u32p), _p(hdrs, u32p), _p(payload), _p(status, u32p), C.c_uint32(grid))
+        return status
+
     def planes_count(self, tensors, n_elem, es, spe, low_off, plane_off, stride, low, planes, grid=3):
         n, ptrs = self._arrays(tensors)
         a = lambda x, t: np.array(x, t)

@@ -258,3 +258,44 @@ def test_short_decode_table_with_zeros_in_value_lanes(emu, oracle):
     assert not status.any()
     for a, o in zip(tensors, outs):
         assert np.array_equal(a, o)
+
+
+@pytest.mark.parametrize("kind,es", [("f32_master", 4), ("bf16_weight", 2), ("f32_exp_avg_sq_lognormal", 4)])
+def test_plane_decoder_writes_whole_elements(emu, oracle, kind, es):
+    """Container version 3 restore without a merge pass: every plane compressed by the oracle as an 8-bit tensor,
+    the team decodes the planes of a tensor side by side and writes whole elements; sizes with full groups of
+    8 rows, leftover rows, a partial row, next to nothing; one plane stored raw (uniform bytes)."""
+    rng = np.random.default_rng(3)
+    planes = es // 2
+    sizes = [8 * 256 * 3 + 5 * 256 + 77, 4096, 255, 1, 256 * 9]
+    dsts, lows, want, n_elem, poff, raws, cfs, hdrs, payloads = [], [], [], [], [], [], [], [], []
+    at = 0
+    for gi, n in enumerate(sizes):
+        raw, dt = synth(kind, n, 70 + gi)
+        m = raw.reshape(n, es).copy()
+        if gi == 1:
+            flat = np.tile(np.arange(256, dtype=np.uint8), n // 256)        # every value equally often: incompressible
+            rng.shuffle(flat)
+            m[:, es - 2 if planes == 2 else es - 1] = flat
+        want.append(m.reshape(-1).copy())
+        low = aligned(n * (es // 2) + 16)[:n * (es // 2)]
+        low[:] = m[:, :es // 2].reshape(-1)
+        lows.append(low)
+        dsts.append(aligned(n * es + 16)[:n * es])
+        n_elem.append(n)
+        for p in range(planes):
+            plane = np.ascontiguousarray(m[:, es // 2 + p])
+            nf, cf, xm, _ = oracle.normalize(oracle.byte_histogram(plane), False)
+            pay, h, is_raw = oracle.compress_tensor(plane, nf, cf, xm)
+            pad = (-at) % 32
+            payloads.append(np.zeros(pad, np.uint8)); at += pad
+            poff.append(at); raws.append(int(is_raw)); cfs.append(cf); hdrs.append(h); payloads.append(pay)
+            at += pay.size
+    assert any(raws), "the raw-plane case is not exercised"
+    payload = np.concatenate(payloads + [np.zeros(64, np.uint8)])
+    for d in dsts:
+        d[:] = 0xEE
+    status = emu.decode_planes(planes, dsts, lows, n_elem, poff, raws, np.concatenate(cfs), np.concatenate(hdrs), payload)
+    assert not status.any()
+    for d, w in zip(dsts, want):
+        assert np.array_equal(d, w)

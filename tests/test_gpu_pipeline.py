@@ -430,3 +430,47 @@ def test_release_workspace_returns_device_memory(chk, tmp_path):
     ctx.release_workspace()
     assert free0 - torch.cuda.mem_get_info()[0] <= 4 << 20
     ctx.close()
+
+
+@pytest.mark.parametrize("fused", [1, 0])
+def test_container_version3_float_only_restore_paths(chk, oracle, tmp_path, fused):
+    """Float tensors only: restore decodes the planes straight into whole elements (one kernel, no plane buffers);
+    with the switch off, planes are decoded to memory and merged.  Both from the device-resident result and from
+    files, into misaligned targets too; an incompressible plane (stored raw) among them."""
+    names, host, dtypes = [], [], []
+    for n_, h_, d_ in zip(*make_state_v3()):
+        if d_ in (F32, BF16) or n_ == "half.w":
+            names.append(n_); host.append(h_); dtypes.append(d_)
+    rng = np.random.default_rng(11)
+    noise = host[1].copy().reshape(-1, 4)            # fp32: make the lower high byte uniform -> that plane is stored raw
+    noise[:, 2] = rng.permutation(np.tile(np.arange(256, dtype=np.uint8), noise.shape[0] // 256 + 1)[:noise.shape[0]])
+    names.append("noise.f32"); host.append(noise.reshape(-1).copy()); dtypes.append(F32)
+    dev = [dev_bytes(h) for h in host]
+    ctx = chk.Context(device=0, rank=1)
+    register_all(ctx, names, dev, dtypes)
+    ctx.set_option("format_version", 3)
+    ctx.set_option("v3_fused_decode", fused)
+    out = str(tmp_path / "v3")
+    ctx.compress_and_save(out)
+    # targets off a 16-byte boundary for every second tensor
+    bufs = [torch.zeros(h.size + 32, dtype=torch.uint8, device="cuda") for h in host]
+    targets = [b[(2 if i % 2 else 0):][:h.size] for i, (b, h) in enumerate(zip(bufs, host))]
+    assert ctx.decompress_resident([t.data_ptr() for t in targets]) == len(names)
+    for t, d in zip(targets, dev):
+        assert torch.equal(t, d)
+    fresh = [torch.zeros_like(d) for d in dev]
+    ctx2 = chk.Context(device=0, rank=1)
+    register_all(ctx2, names, fresh, dtypes)
+    ctx2.set_option("format_version", 3)
+    ctx2.set_option("v3_fused_decode", fused)
+    assert ctx2.load_and_decompress(out) == len(names)
+    for f, d in zip(fresh, dev):
+        assert torch.equal(f, d)
+    # a damaged stream is reported, not restored silently
+    st_path = os.path.join(out, "rank_1_states.ansc")
+    blob = bytearray(open(st_path, "rb").read())
+    blob[-100] ^= 0x5A
+    open(st_path, "wb").write(bytes(blob))
+    with pytest.raises(chk.CheckersError):
+        ctx2.load_and_decompress(out)
+    ctx.close(); ctx2.close()
