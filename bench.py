@@ -522,13 +522,13 @@ def main():
     ap.add_argument("--world-shards", type=int, default=8, help="flat-index shards of the model; one per rank")
     ap.add_argument("--chunk-elems", type=int, default=1 << 20, help="elements per registered tensor")
     ap.add_argument("--limit-elems", type=int, default=0, help="use only this many parameters of the shard (tests)")
-    ap.add_argument("--e2e-elems", type=int, default=128 << 20,
+    ap.add_argument("--e2e-elems", type=int, default=256 << 20,
                     help="parameters per GPU in the host-buffer end-to-end leg (14 bytes each; the same at every N)")
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--c4-elems", type=int, default=512 << 20,
                     help="--extras: parameters of the 70B-shaped shard streamed from host memory (14 bytes each)")
     ap.add_argument("--e2e-workers", type=int, default=4, help="staging slots (and host threads) of the chunk pipeline")
-    ap.add_argument("--e2e-chunk-bytes", type=int, default=256 << 20,
+    ap.add_argument("--e2e-chunk-bytes", type=int, default=512 << 20,
                     help="tensor bytes per chunk of the host-buffer pipeline")
     ap.add_argument("--cpu-sample-elems", type=int, default=32 << 20, help="parameters in the timed CPU sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
