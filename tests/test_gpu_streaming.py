@@ -105,3 +105,45 @@ def test_pipeline_with_container_version3(tmp_path):
             assert torch.equal(t.tensor, o), (version, t.name, "from files")
         again.close()
     assert sizes[3] < 0.93 * sizes[2]
+
+
+def test_pipeline_with_tensors_sliced_from_one_buffer():
+    """Tensors that are slices of one pinned buffer (moved by merged copies): registered out of address order, with
+    gaps, one of them twice, odd sizes; restored into slices of another buffer laid out differently."""
+    torch = pytest.importorskip("torch")
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from checkers_b200.streaming import ChunkedHostPipeline, HostTensor
+    from oracle_lib import synth, ELEM_SIZE
+    rng = np.random.default_rng(8)
+    specs = [("bf16_weight", 200001), ("f32_master", 150000), ("f32_exp_avg", 99999), ("i8", 12345), ("bf16_weight", 64),
+             ("f32_exp_avg_sq_lognormal", 300000), ("f16_weight", 77777)]
+    raws = [synth(k, n, 900 + i) for i, (k, n) in enumerate(specs)]
+    total = sum(r.size for r, _ in raws)
+    src = torch.zeros(total + 4096, dtype=torch.uint8).pin_memory()
+    dst = torch.zeros(2 * total + 8192, dtype=torch.uint8).pin_memory()
+    offs, at = [], 0
+    for i, (r, dt) in enumerate(raws):
+        at += 0 if i % 2 else 3 * ELEM_SIZE[dt]          # every second tensor follows its neighbour without a gap
+        at = (at + ELEM_SIZE[dt] - 1) // ELEM_SIZE[dt] * ELEM_SIZE[dt]
+        offs.append(at)
+        src[at:at + r.size] = torch.from_numpy(r.copy())
+        at += r.size
+    order = [3, 0, 6, 1, 5, 2, 4, 1]                      # out of address order; tensor 1 twice
+    tensors, targets, want = [], [], []
+    d_at = 0
+    for j, i in enumerate(order):
+        r, dt = raws[i]
+        tensors.append(HostTensor(f"t{j}.{i}", src[offs[i]:offs[i] + r.size], dt))
+        d_at = (d_at + 7) // 8 * 8 + (8 if j % 3 == 0 else 0)
+        targets.append(dst[d_at:d_at + r.size])
+        d_at += r.size
+        want.append(torch.from_numpy(r.copy()))
+    for chunk in (1 << 20, 300000):
+        pipe = ChunkedHostPipeline(tensors, device=0, rank=0, chunk_bytes=chunk, workers=3)
+        pipe.compress()
+        dst.zero_()
+        pipe.restore(targets)
+        for t, w, ht in zip(targets, want, tensors):
+            assert torch.equal(t, w), (chunk, ht.name)
+        pipe.close()
