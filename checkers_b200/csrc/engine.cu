@@ -1156,43 +1156,50 @@ static void hll_sketch_all(Context* c) {
     c->hll.assign(N * (size_t)kHllRegs, 0);
     if (N == 0) return;
     cudaStream_t s = c->stream;
-    std::vector<StatsDesc> d(N);
-    pin_ensure(c->h_tiles, (N + 1) * 4);
-    uint32_t* tile_start = static_cast<uint32_t*>(c->h_tiles.p);
-    unsigned long long tiles = 0;
-    for (size_t i = 0; i < N; ++i) {
-        const Tensor& t = c->tensors[i];
-        const uint32_t es = elem_size(t.dtype);
-        d[i] = StatsDesc{es ? t.ptr : nullptr, t.n_elem, t.dtype, 0};
-        tile_start[i] = (uint32_t)tiles;
-        if (d[i].ptr && d[i].n) tiles += (d[i].n * es + kHllTileBytes - 1) / kHllTileBytes;
-        if (tiles > 0xFFFFFFFFull) throw Error{CHK_ERR_CAPACITY, "too many tiles in one batch"};
-    }
-    tile_start[N] = (uint32_t)tiles;
-    if (!tiles) return;
-    const unsigned long long regs = (unsigned long long)N * kHllRegs;
-    dev_ensure(c, c->d_stats_desc, N * sizeof(StatsDesc));
-    dev_ensure(c, c->d_tiles, (N + 1) * 4);
-    dev_ensure(c, c->d_hll32, regs * 4);
-    dev_ensure(c, c->d_hll8, regs);
-    CHK_CUDA(cudaMemcpyAsync(c->d_stats_desc.p, d.data(), N * sizeof(StatsDesc), cudaMemcpyHostToDevice, s));
-    control_copy(c, c->d_tiles.p, c->h_tiles.p, (N + 1) * 4, s);
-    CHK_CUDA(cudaMemsetAsync(c->d_hll32.p, 0, regs * 4, s));
-    CHK_CUDA(cudaEventRecord(c->ev[0], s));
     const uint32_t smem = kHllRegs * 4;
     CHK_CUDA(cudaFuncSetAttribute(hll_sketch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const unsigned long long cap = (unsigned long long)(c->sm_count > 0 ? c->sm_count : 1) * 3;
-    hll_sketch_kernel<<<(uint32_t)(tiles < cap ? tiles : cap), 256, smem, s>>>(
-        static_cast<const StatsDesc*>(c->d_stats_desc.p), static_cast<const uint32_t*>(c->d_tiles.p), (uint32_t)N,
-        (uint32_t)tiles, static_cast<uint32_t*>(c->d_hll32.p));
-    hll_pack_kernel<<<(uint32_t)cap, 256, 0, s>>>(static_cast<const uint32_t*>(c->d_hll32.p),
-                                                  static_cast<uint8_t*>(c->d_hll8.p), regs);
-    CHK_CUDA(cudaGetLastError());
-    c->launches += 2;
-    CHK_CUDA(cudaEventRecord(c->ev[1], s));
-    CHK_CUDA(cudaMemcpyAsync(c->hll.data(), c->d_hll8.p, regs, cudaMemcpyDeviceToHost, s));
-    sync_stream(c, s);
-    c->timing["hll_sketch_ms"] = ms_between(c->ev[0], c->ev[1]);
+    double ms = 0.0;
+    // batches of at most kBatch tensors: the registers of a batch take 80 KiB per tensor on the device
+    constexpr size_t kBatch = 8192;
+    for (size_t first = 0; first < N; first += kBatch) {
+        const size_t n = std::min(kBatch, N - first);
+        std::vector<StatsDesc> d(n);
+        pin_ensure(c->h_tiles, (n + 1) * 4);
+        uint32_t* tile_start = static_cast<uint32_t*>(c->h_tiles.p);
+        unsigned long long tiles = 0;
+        for (size_t i = 0; i < n; ++i) {
+            const Tensor& t = c->tensors[first + i];
+            const uint32_t es = elem_size(t.dtype);
+            d[i] = StatsDesc{es ? t.ptr : nullptr, t.n_elem, t.dtype, 0};
+            tile_start[i] = (uint32_t)tiles;
+            if (d[i].ptr && d[i].n) tiles += (d[i].n * es + kHllTileBytes - 1) / kHllTileBytes;
+            if (tiles > 0xFFFFFFFFull) throw Error{CHK_ERR_CAPACITY, "too many tiles in one batch"};
+        }
+        tile_start[n] = (uint32_t)tiles;
+        if (!tiles) continue;
+        const unsigned long long regs = (unsigned long long)n * kHllRegs;
+        dev_ensure(c, c->d_stats_desc, n * sizeof(StatsDesc));
+        dev_ensure(c, c->d_tiles, (n + 1) * 4);
+        dev_ensure(c, c->d_hll32, regs * 4);
+        dev_ensure(c, c->d_hll8, regs);
+        CHK_CUDA(cudaMemcpyAsync(c->d_stats_desc.p, d.data(), n * sizeof(StatsDesc), cudaMemcpyHostToDevice, s));
+        control_copy(c, c->d_tiles.p, c->h_tiles.p, (n + 1) * 4, s);
+        CHK_CUDA(cudaMemsetAsync(c->d_hll32.p, 0, regs * 4, s));
+        CHK_CUDA(cudaEventRecord(c->ev[0], s));
+        hll_sketch_kernel<<<(uint32_t)(tiles < cap ? tiles : cap), 256, smem, s>>>(
+            static_cast<const StatsDesc*>(c->d_stats_desc.p), static_cast<const uint32_t*>(c->d_tiles.p), (uint32_t)n,
+            (uint32_t)tiles, static_cast<uint32_t*>(c->d_hll32.p));
+        hll_pack_kernel<<<(uint32_t)cap, 256, 0, s>>>(static_cast<const uint32_t*>(c->d_hll32.p),
+                                                      static_cast<uint8_t*>(c->d_hll8.p), regs);
+        CHK_CUDA(cudaGetLastError());
+        c->launches += 2;
+        CHK_CUDA(cudaEventRecord(c->ev[1], s));
+        CHK_CUDA(cudaMemcpyAsync(c->hll.data() + first * kHllRegs, c->d_hll8.p, regs, cudaMemcpyDeviceToHost, s));
+        sync_stream(c, s);  // the descriptors on the host stack and the pinned tile table are reused by the next batch
+        ms += ms_between(c->ev[0], c->ev[1]);
+    }
+    c->timing["hll_sketch_ms"] = ms;
 }
 
 // Bytes of the group's tensors coded under one shared 32-bit model, and the size of the model's vocabulary

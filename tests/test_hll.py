@@ -108,3 +108,13 @@ def test_device_sketches_and_report():
     assert own2 == own
     assert shared2 == own - sum(H.shared_histogram_bytes(H.count(s)) for s in sk[-2:]) + union
     ctx.close()
+    # more tensors than one batch of the sketch pass holds
+    big = torch.arange(9000 * 16, dtype=torch.int32, device="cuda")
+    ctx = chk.Context(device=0)
+    for i in range(9000):
+        ctx.register_pointer(f"s{i}", big.data_ptr() + i * 64, 16, chk.I32)
+    ctx.hll_sketch_all()
+    for i in (0, 8191, 8192, 8999):
+        want = H.sketch(np.arange(i * 16, i * 16 + 16, dtype=np.uint32))
+        assert np.array_equal(ctx.hll_sketch(i), want), i
+    ctx.close()
