@@ -142,7 +142,7 @@ def _timing(key, ms):
 
 
 def initialize_context(model_engine, optimizer=None, histogram_bins=256, background_threads=1, *,
-                       shared_tables="reference", analysis_mode="reference"):
+                       shared_tables="reference", analysis_mode="reference", container_version=2):
     """Registers the rank's tensors.  `model_engine` may be an engine/module with
     named_parameters(), or a dict / list of (name, CUDA tensor) pairs.
     `background_threads` is accepted for signature compatibility; registration
@@ -152,6 +152,10 @@ def initialize_context(model_engine, optimizer=None, histogram_bins=256, backgro
     whose shared table the reference's normalisation leaves undecodable (every bf16 cluster):
     "reference" refuses to write such files (compress_and_save raises), "reference_bytes" writes the
     reference's exact, unrestorable bytes, "repair" renormalises shared tables so they decode.
+
+    container_version (an addition): 2 = the reference's files (default); 3 = the byte-plane container (about a
+    fifth smaller on optimizer state, not readable by the reference's layout; load_and_decompress of the same
+    context reads what it wrote).
 
     analysis_mode (an addition): "reference" computes the statistics of analyze_tensors() in the
     reference's order of float additions (bit-identical results, one thread block per tensor); "fast"
@@ -170,6 +174,8 @@ def initialize_context(model_engine, optimizer=None, histogram_bins=256, backgro
             raise RuntimeError("shared_tables must be 'reference', 'reference_bytes' or 'repair'")
         if analysis_mode not in ("reference", "fast"):
             raise RuntimeError("analysis_mode must be 'reference' or 'fast'")
+        if container_version not in (2, 3):
+            raise RuntimeError("container_version must be 2 or 3")
         rank = _env_rank(model_engine, "global_rank", "RANK")
         local_rank = _env_rank(model_engine, "local_rank", "LOCAL_RANK")
         t1 = time.perf_counter()
@@ -193,6 +199,7 @@ def initialize_context(model_engine, optimizer=None, histogram_bins=256, backgro
         _ctx.set_option("repair_tables", int(shared_tables == "repair"))
         _ctx.set_option("allow_undecodable", int(shared_tables == "reference_bytes"))
         _ctx.set_option("fast_stats", int(analysis_mode == "fast"))
+        _ctx.set_option("format_version", int(container_version))
         for name, t in pairs:
             if not getattr(t, "is_cuda", False):
                 continue  # no local device storage on this rank
